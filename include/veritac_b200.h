@@ -1,0 +1,119 @@
+/* veritac_b200 — C ABI of the B200 (sm_100a) GEMM backend for VeriTac's CodeGen hot path.
+ *
+ * The reference (CuteCake/VeriTac) has no FFI: its two GEMM back ends are Python modules that
+ * interpret or compile-and-run the computation on the CPU.  Each entry point below names the
+ * reference interface whose execution it replaces.  Everything is plain pointers and sizes;
+ * matrices are dense row-major with no padding (lda = K, ldb = N, ldc = N) and C is overwritten
+ * (beta = 0), matching the reference, which poisons C and demands that every cell be written
+ * (specializations/gemmini_gemm/backend.py:558-561, :756-760).
+ *
+ * Conventions
+ *   - Every function returns VT_OK (0) or a negative VT_ERR_* code and never aborts the process;
+ *     the text for the calling thread's last failure is vt_last_error().
+ *   - `dev` is a CUDA device ordinal.  The library keeps one context per device (a stream, a status
+ *     word, grow-only workspace) created on first use and freed by vt_shutdown().
+ *   - `where`: VT_HOST  = A, B, C are host pointers; the call copies in, computes, copies out and
+ *                         returns when C is complete (pinned memory from vt_host_alloc makes the
+ *                         copies run at full PCIe rate).
+ *              VT_DEVICE = A, B, C are device pointers on `dev`; the call only enqueues work on
+ *                         `stream` (a cudaStream_t, or NULL for the library's own stream) and
+ *                         returns; vt_sync() waits and reports kernel status.
+ *   - One host thread per device at a time; different devices may be driven concurrently.
+ */
+#ifndef VERITAC_B200_H
+#define VERITAC_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+  VT_OK = 0,
+  VT_ERR_INVALID = -1,     /* bad argument: null pointer, shape outside the Gemmini plan domain, ... */
+  VT_ERR_CUDA = -2,        /* a CUDA runtime/driver call failed; text in vt_last_error() */
+  VT_ERR_DEVICE_WAIT = -3, /* a bounded device-side wait expired; the kernel returned early */
+  VT_ERR_UNSUPPORTED = -4, /* variant not available for these arguments */
+  VT_ERR_OVERFLOW = -5,    /* tile program could leave the int32 accumulator range */
+  VT_ERR_PROGRAM = -6      /* malformed tile program */
+};
+
+enum { VT_HOST = 0, VT_DEVICE = 1 };
+
+/* Tile visiting order of the int8 GEMM = the loop order of the Gemmini schedule it stands for.
+ * The order affects cache reuse only; results are identical for all of them. */
+enum {
+  VT_RASTER_BASELINE = 0, /* gen_baseline i,j,k   (backend.py:278-302): row-major output tiles      */
+  VT_RASTER_REUSE_B = 1,  /* gen_reuse_b  j,k,i   (backend.py:305-333): column-major output tiles   */
+  VT_RASTER_BATCHED = 2,  /* gen_batched_reuse_b  (lowering.py:18-40): batch_rows 16-row tiles of one
+                             column block stay live together; columns swept per row batch         */
+  VT_RASTER_AUTO = 3      /* grouped order tuned for L2 reuse on B200                               */
+};
+
+/* int8 kernel variants (VT_I8_AUTO picks the fastest verified one). */
+enum { VT_I8_AUTO = 0, VT_I8_B_AS_STORED = 1, VT_I8_B_RELAYOUT = 2, VT_I8_CTA_PAIR = 3 };
+
+/* fp32 kernel variants. */
+enum { VT_SGEMM_AUTO = 0, VT_SGEMM_TILE128 = 1, VT_SGEMM_TILE64 = 2, VT_SGEMM_SKINNY = 3 };
+
+/* Number of CUDA devices visible, or a negative VT_ERR_* code. */
+int vt_device_count(void);
+
+/* Text of the calling thread's last error ("" if none). */
+const char* vt_last_error(void);
+
+/* Exact int8 x int8 -> int32 GEMM, C = A(MxK) * B(KxN).
+ * Replaces the execution inside run_commands() (specializations/gemmini_gemm/backend.py:433-562,
+ * the 16x16x16 compute at :490-529) and scalar_matmul() (:569-580) for streams that compute a
+ * full GEMM.  Domain = the reference plan domain (validate_plan, backend.py:107-149): M, N, K >= 16
+ * and multiples of 16, K*16384 <= 2^31-1; anything else is VT_ERR_INVALID.  Bit-exact.
+ *   raster      VT_RASTER_*;  batch_rows = accumulator_rows/16 for VT_RASTER_BATCHED (else ignored)
+ *   variant     VT_I8_* */
+int vt_i8gemm(int dev, const int8_t* A, const int8_t* B, int32_t* C, int64_t M, int64_t N, int64_t K, int raster,
+              int batch_rows, int variant, int where, void* stream);
+
+/* Batched B-reuse GEMM: `batch` independent A_i (MxK each, stacked contiguously) against one
+ * shared B (KxN); C_i (MxN each) stacked likewise.  Replaces executing
+ * gen_batched_reuse_b(plan, batch_rows) (specializations/gemmini_gemm/lowering.py:18-40) once per
+ * A_i with the same B.  acc_rows is the plan's accumulator_rows (a multiple of 16, 16..1024). */
+int vt_i8gemm_shared_b(int dev, const int8_t* A, const int8_t* B, int32_t* C, int64_t batch, int64_t M, int64_t N,
+                       int64_t K, int acc_rows, int where, void* stream);
+
+/* Tile program: the arithmetic content of an arbitrary, already validated Gemmini command stream.
+ * Output tile t (16x16 int32 at element offset c_off[t], row stride ldc) receives
+ * sum_{j in [term_begin[t], term_begin[t+1])} Atile(a_off[j]) * Btile(b_off[j]), where a tile is 16x16
+ * int8 at an element offset with row stride lda / ldb.  Replaces the compute/mvout part of
+ * run_commands() (backend.py:490-553) for streams that are not a plain GEMM.  All arrays are host
+ * pointers; A, B, C follow `where`.  VT_ERR_OVERFLOW if a tile has more than 8191 terms. */
+int vt_i8_tile_program(int dev, const int8_t* A, int64_t a_elems, const int8_t* B, int64_t b_elems, int32_t* C,
+                       int64_t c_elems, int64_t lda, int64_t ldb, int64_t ldc, int64_t n_tiles,
+                       const int64_t* c_off, const int64_t* term_begin, const int64_t* a_off,
+                       const int64_t* b_off, int where, void* stream);
+
+/* fp32 GEMM, C = A(MxK) * B(KxN), any positive M, N, K.
+ * Replaces running the generated `matmul()` of benchmark_matmul() (specializations/cpu_gemm/
+ * runner.py:111-190; loop nest emitted by emit_c.py:83-155).  The reference computes in double;
+ * this computes in fp32 (relative Frobenius error <= 1e-5 against float64 is the contract). */
+int vt_sgemm(int dev, const float* A, const float* B, float* C, int64_t M, int64_t N, int64_t K, int variant,
+             int where, void* stream);
+
+/* Waits for `stream` (NULL = the library's stream) on `dev` and returns VT_ERR_DEVICE_WAIT if any
+ * kernel since the last check gave up on a bounded wait, VT_ERR_CUDA on an asynchronous CUDA error. */
+int vt_sync(int dev, void* stream);
+
+/* Pinned host memory for VT_HOST calls. */
+void* vt_host_alloc(size_t bytes);
+int vt_host_free(void* p);
+
+/* Number of kernels this library has launched in this process (all devices, all threads). */
+int64_t vt_launch_count(void);
+
+/* Frees every device context (streams, workspace).  Safe to call more than once. */
+int vt_shutdown(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* VERITAC_B200_H */

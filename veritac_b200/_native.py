@@ -1,0 +1,142 @@
+"""ctypes binding of libveritac_b200.so (the C ABI in include/veritac_b200.h).
+
+There is no CPU fallback: if the shared library is missing or a call fails, a `NativeError` is
+raised.  The library is built in-tree by `python -m veritac_b200.build`.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_char_p, c_int, c_int64, c_size_t, c_void_p
+from pathlib import Path
+
+LIB_PATH = Path(__file__).resolve().parent / "libveritac_b200.so"
+
+VT_OK = 0
+VT_ERR_INVALID = -1
+VT_ERR_CUDA = -2
+VT_ERR_DEVICE_WAIT = -3
+VT_ERR_UNSUPPORTED = -4
+VT_ERR_OVERFLOW = -5
+VT_ERR_PROGRAM = -6
+
+VT_HOST = 0
+VT_DEVICE = 1
+
+VT_RASTER_BASELINE = 0
+VT_RASTER_REUSE_B = 1
+VT_RASTER_BATCHED = 2
+VT_RASTER_AUTO = 3
+
+VT_I8_AUTO = 0
+VT_I8_B_AS_STORED = 1
+VT_I8_B_RELAYOUT = 2
+VT_I8_CTA_PAIR = 3
+
+VT_SGEMM_AUTO = 0
+VT_SGEMM_TILE128 = 1
+VT_SGEMM_TILE64 = 2
+VT_SGEMM_SKINNY = 3
+
+# Every symbol include/veritac_b200.h declares, with its ctypes signature.
+SIGNATURES = {
+    "vt_device_count": (c_int, []),
+    "vt_last_error": (c_char_p, []),
+    "vt_i8gemm": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_int, c_int,
+                          c_int, c_void_p]),
+    "vt_i8gemm_shared_b": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int,
+                                   c_int, c_void_p]),
+    "vt_i8_tile_program": (c_int, [c_int, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int64, c_int64,
+                                   c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p]),
+    "vt_sgemm": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_int, c_void_p]),
+    "vt_sync": (c_int, [c_int, c_void_p]),
+    "vt_host_alloc": (c_void_p, [c_size_t]),
+    "vt_host_free": (c_int, [c_void_p]),
+    "vt_launch_count": (c_int64, []),
+    "vt_shutdown": (c_int, []),
+}
+
+
+class NativeError(RuntimeError):
+    """A C-ABI call failed; `.code` is the VT_ERR_* value."""
+
+    def __init__(self, code: int, message: str):
+        super().__init__("veritac_b200 native call failed (%d): %s" % (code, message))
+        self.code = code
+        self.message = message
+
+
+_lib = None
+
+
+def lib() -> ctypes.CDLL:
+    """The loaded shared library; raises NativeError if it has not been built."""
+    global _lib
+    if _lib is None:
+        if not LIB_PATH.is_file():
+            raise NativeError(VT_ERR_UNSUPPORTED,
+                              "%s is missing: run `python -m veritac_b200.build` (there is no CPU fallback)"
+                              % LIB_PATH)
+        handle = ctypes.CDLL(str(LIB_PATH))
+        for name, (restype, argtypes) in SIGNATURES.items():
+            fn = getattr(handle, name)
+            fn.restype = restype
+            fn.argtypes = argtypes
+        _lib = handle
+    return _lib
+
+
+def last_error() -> str:
+    return (lib().vt_last_error() or b"").decode("utf-8", "replace")
+
+
+def check(code: int) -> int:
+    if code < 0:
+        raise NativeError(code, last_error())
+    return code
+
+
+def device_count() -> int:
+    return check(lib().vt_device_count())
+
+
+def launch_count() -> int:
+    return int(lib().vt_launch_count())
+
+
+def _ptr(x) -> int:
+    """Address of a numpy array's or torch tensor's first element."""
+    if hasattr(x, "data_ptr"):
+        return int(x.data_ptr())
+    if hasattr(x, "ctypes"):
+        return int(x.ctypes.data)
+    return int(x)
+
+
+def i8gemm(A, B, C, M: int, N: int, K: int, *, dev: int = 0, raster: int = VT_RASTER_AUTO, batch_rows: int = 1,
+           variant: int = VT_I8_AUTO, where: int = VT_HOST, stream: int = 0) -> None:
+    check(lib().vt_i8gemm(dev, _ptr(A), _ptr(B), _ptr(C), M, N, K, raster, batch_rows, variant, where, stream))
+
+
+def i8gemm_shared_b(A, B, C, batch: int, M: int, N: int, K: int, *, dev: int = 0, acc_rows: int = 16,
+                    where: int = VT_HOST, stream: int = 0) -> None:
+    check(lib().vt_i8gemm_shared_b(dev, _ptr(A), _ptr(B), _ptr(C), batch, M, N, K, acc_rows, where, stream))
+
+
+def i8_tile_program(A, a_elems, B, b_elems, C, c_elems, lda, ldb, ldc, c_off, term_begin, a_off, b_off, *,
+                    dev: int = 0, where: int = VT_HOST, stream: int = 0) -> None:
+    n_tiles = len(c_off)
+    check(lib().vt_i8_tile_program(dev, _ptr(A), a_elems, _ptr(B), b_elems, _ptr(C), c_elems, lda, ldb, ldc,
+                                   n_tiles, _ptr(c_off), _ptr(term_begin), _ptr(a_off), _ptr(b_off), where, stream))
+
+
+def sgemm(A, B, C, M: int, N: int, K: int, *, dev: int = 0, variant: int = VT_SGEMM_AUTO, where: int = VT_HOST,
+          stream: int = 0) -> None:
+    check(lib().vt_sgemm(dev, _ptr(A), _ptr(B), _ptr(C), M, N, K, variant, where, stream))
+
+
+def sync(dev: int = 0, stream: int = 0) -> None:
+    check(lib().vt_sync(dev, stream))
+
+
+def shutdown() -> None:
+    check(lib().vt_shutdown())

@@ -1,0 +1,277 @@
+// extern "C" entry points declared in include/veritac_b200.h: argument checking in the
+// reference's plan domain, host<->device staging for host-pointer calls, launch, status.
+#include <cstring>
+#include <vector>
+
+#include "runtime.h"
+
+using namespace vt;
+
+namespace {
+
+// The reference plan domain (validate_plan, specializations/gemmini_gemm/backend.py:121-136).
+int check_i8_domain(int64_t M, int64_t N, int64_t K) {
+  const int64_t d[3] = {M, N, K};
+  const char* nm[3] = {"m", "n", "k"};
+  for (int i = 0; i < 3; ++i) {
+    if (d[i] < 16) return fail(VT_ERR_INVALID, "%s=%lld must be >= dim=16", nm[i], (long long)d[i]);
+    if (d[i] % 16) return fail(VT_ERR_INVALID, "%s=%lld must be divisible by dim=16", nm[i], (long long)d[i]);
+    if (d[i] > 0x7fffffffLL) return fail(VT_ERR_INVALID, "%s=%lld exceeds the 32-bit TMA extent", nm[i], (long long)d[i]);
+  }
+  if (K * 16384 > 2147483647LL)
+    return fail(VT_ERR_INVALID, "overflow bound violated: k*16384 = %lld > 2147483647", (long long)(K * 16384));
+  return VT_OK;
+}
+
+void raster_for(int raster, int batch_rows, int64_t M, int* mode, int* group) {
+  switch (raster) {
+    case VT_RASTER_BASELINE: *mode = 0; *group = 1; break;
+    case VT_RASTER_REUSE_B: *mode = 1; *group = 1; break;
+    case VT_RASTER_BATCHED: {
+      // batch_rows 16-row Gemmini tiles live together = ceil(batch_rows*16 / 128) CTA tile-rows.
+      const int64_t rows = int64_t(batch_rows < 1 ? 1 : batch_rows) * 16;
+      *mode = 2;
+      *group = int((rows + 127) / 128);
+      break;
+    }
+    default: *mode = 2; *group = 16; break;
+  }
+  (void)M;
+}
+
+int resolve_i8_variant(int variant) { return variant == VT_I8_AUTO ? VT_I8_B_AS_STORED : variant; }
+
+cudaStream_t pick_stream(DeviceCtx* c, void* stream) { return stream ? static_cast<cudaStream_t>(stream) : c->stream; }
+
+// Host-pointer int8 GEMM: B and the first row block of A go in, then row blocks are computed
+// while the next block of A streams in and the previous block of C streams out.
+int i8gemm_from_host(DeviceCtx* c, const int8_t* A, const int8_t* B, int32_t* C, int64_t M, int64_t N, int64_t K,
+                     int mode, int group, int variant) {
+  int8_t* dA = static_cast<int8_t*>(ctx_workspace(c, 0, size_t(M) * K));
+  int8_t* dB = static_cast<int8_t*>(ctx_workspace(c, 1, size_t(K) * N));
+  int32_t* dC = static_cast<int32_t*>(ctx_workspace(c, 2, size_t(M) * N * sizeof(int32_t)));
+  if (!dA || !dB || !dC) return VT_ERR_CUDA;
+  // Row blocks: a multiple of 128 rows, at least 1024, about 8 blocks for large M.
+  int64_t rows = ((M / 8 + 127) / 128) * 128;
+  if (rows < 1024) rows = 1024;
+  if (variant == VT_I8_B_RELAYOUT) rows = M;  // the re-layout pass runs once per launch; keep one launch
+  cudaEvent_t ev_b = c->ev[0], ev_in = c->ev[1], ev_k = c->ev[2], ev_done = c->ev[3];
+  VT_CUDA(cudaMemcpyAsync(dB, B, size_t(K) * N, cudaMemcpyHostToDevice, c->copy_in));
+  VT_CUDA(cudaEventRecord(ev_b, c->copy_in));
+  VT_CUDA(cudaStreamWaitEvent(c->stream, ev_b, 0));
+  for (int64_t r0 = 0; r0 < M; r0 += rows) {
+    const int64_t r = (M - r0 < rows) ? (M - r0) : rows;
+    VT_CUDA(cudaMemcpyAsync(dA + r0 * K, A + r0 * K, size_t(r) * K, cudaMemcpyHostToDevice, c->copy_in));
+    VT_CUDA(cudaEventRecord(ev_in, c->copy_in));
+    VT_CUDA(cudaStreamWaitEvent(c->stream, ev_in, 0));
+    int rc = launch_i8gemm(c, dA + r0 * K, dB, dC + r0 * N, r, N, K, mode, group, variant, c->stream);
+    if (rc) return rc;
+    VT_CUDA(cudaEventRecord(ev_k, c->stream));
+    VT_CUDA(cudaStreamWaitEvent(c->copy_out, ev_k, 0));
+    VT_CUDA(cudaMemcpyAsync(C + r0 * N, dC + r0 * N, size_t(r) * N * sizeof(int32_t), cudaMemcpyDeviceToHost,
+                            c->copy_out));
+  }
+  VT_CUDA(cudaEventRecord(ev_done, c->copy_out));
+  VT_CUDA(cudaStreamWaitEvent(c->stream, ev_done, 0));
+  return ctx_check_status(c, c->stream);
+}
+
+}  // namespace
+
+extern "C" {
+
+int vt_device_count(void) {
+  int n = 0;
+  cudaError_t e = cudaGetDeviceCount(&n);
+  if (e != cudaSuccess) return fail_cuda(e, "cudaGetDeviceCount");
+  return n;
+}
+
+const char* vt_last_error(void) { return last_error_text(); }
+
+int vt_i8gemm(int dev, const int8_t* A, const int8_t* B, int32_t* C, int64_t M, int64_t N, int64_t K, int raster,
+              int batch_rows, int variant, int where, void* stream) {
+  clear_error_text();
+  if (!A || !B || !C) return fail(VT_ERR_INVALID, "null operand");
+  if (where != VT_HOST && where != VT_DEVICE) return fail(VT_ERR_INVALID, "where must be VT_HOST or VT_DEVICE");
+  if (raster < VT_RASTER_BASELINE || raster > VT_RASTER_AUTO) return fail(VT_ERR_INVALID, "unknown raster %d", raster);
+  if (raster == VT_RASTER_BATCHED && (batch_rows < 1 || batch_rows > 64))
+    return fail(VT_ERR_INVALID, "batch_rows must be in 1..64 (accumulator rows 16..1024)");
+  int rc = check_i8_domain(M, N, K);
+  if (rc) return rc;
+  DeviceCtx* c = ctx_for(dev);
+  if (!c) return VT_ERR_CUDA;
+  int mode, group;
+  raster_for(raster, batch_rows, M, &mode, &group);
+  variant = resolve_i8_variant(variant);
+  if (where == VT_HOST) return i8gemm_from_host(c, A, B, C, M, N, K, mode, group, variant);
+  return launch_i8gemm(c, A, B, C, M, N, K, mode, group, variant, pick_stream(c, stream));
+}
+
+int vt_i8gemm_shared_b(int dev, const int8_t* A, const int8_t* B, int32_t* C, int64_t batch, int64_t M, int64_t N,
+                       int64_t K, int acc_rows, int where, void* stream) {
+  clear_error_text();
+  if (batch < 1) return fail(VT_ERR_INVALID, "batch must be positive");
+  if (acc_rows < 16 || acc_rows > 1024 || acc_rows % 16)
+    return fail(VT_ERR_INVALID, "accumulator_rows=%d must be a multiple of 16 in 16..1024", acc_rows);
+  int rc = check_i8_domain(M, N, K);
+  if (rc) return rc;
+  if (batch * M > 0x7fffffffLL) return fail(VT_ERR_INVALID, "batch*M exceeds the 32-bit TMA extent");
+  // One A_i never shares an output row with another, and M is a multiple of 16, so the stacked
+  // (batch*M) x K matrix against B is exactly the batch of products; B is fetched once per
+  // column sweep for all A_i that are resident together.
+  return vt_i8gemm(dev, A, B, C, batch * M, N, K, VT_RASTER_BATCHED, acc_rows / 16 > 64 ? 64 : acc_rows / 16,
+                   VT_I8_AUTO, where, stream);
+}
+
+int vt_i8_tile_program(int dev, const int8_t* A, int64_t a_elems, const int8_t* B, int64_t b_elems, int32_t* C,
+                       int64_t c_elems, int64_t lda, int64_t ldb, int64_t ldc, int64_t n_tiles,
+                       const int64_t* c_off, const int64_t* term_begin, const int64_t* a_off,
+                       const int64_t* b_off, int where, void* stream) {
+  clear_error_text();
+  if (!A || !B || !C || !c_off || !term_begin) return fail(VT_ERR_INVALID, "null operand");
+  if (where != VT_HOST && where != VT_DEVICE) return fail(VT_ERR_INVALID, "where must be VT_HOST or VT_DEVICE");
+  if (n_tiles < 1 || n_tiles > 0x7fffffffLL) return fail(VT_ERR_PROGRAM, "tile count out of range");
+  if (lda < 16 || ldb < 16 || ldc < 16) return fail(VT_ERR_PROGRAM, "row strides must be >= 16");
+  if (term_begin[0] != 0) return fail(VT_ERR_PROGRAM, "term_begin[0] must be 0");
+  const int64_t n_terms = term_begin[n_tiles];
+  if (n_terms > 0 && (!a_off || !b_off)) return fail(VT_ERR_INVALID, "null term arrays");
+  for (int64_t t = 0; t < n_tiles; ++t) {
+    const int64_t cnt = term_begin[t + 1] - term_begin[t];
+    if (cnt < 0) return fail(VT_ERR_PROGRAM, "term_begin must be non-decreasing");
+    if (cnt > 8191) return fail(VT_ERR_OVERFLOW, "tile %lld sums %lld products; more than 8191 can leave int32",
+                                (long long)t, (long long)cnt);
+    if (c_off[t] < 0 || c_off[t] + 15 * ldc + 16 > c_elems) return fail(VT_ERR_PROGRAM, "output tile %lld out of bounds", (long long)t);
+  }
+  for (int64_t j = 0; j < n_terms; ++j) {
+    if (a_off[j] < 0 || a_off[j] + 15 * lda + 16 > a_elems) return fail(VT_ERR_PROGRAM, "A tile of term %lld out of bounds", (long long)j);
+    if (b_off[j] < 0 || b_off[j] + 15 * ldb + 16 > b_elems) return fail(VT_ERR_PROGRAM, "B tile of term %lld out of bounds", (long long)j);
+  }
+  DeviceCtx* c = ctx_for(dev);
+  if (!c) return VT_ERR_CUDA;
+  cudaStream_t s = where == VT_HOST ? c->stream : pick_stream(c, stream);
+
+  // Program tables: one packed upload into workspace slot 3.
+  const size_t n_c = size_t(n_tiles), n_tb = size_t(n_tiles) + 1, n_t = size_t(n_terms);
+  const size_t table_elems = n_c + n_tb + 2 * n_t;
+  std::vector<int64_t> packed(table_elems);
+  std::memcpy(packed.data(), c_off, n_c * 8);
+  std::memcpy(packed.data() + n_c, term_begin, n_tb * 8);
+  if (n_t) {
+    std::memcpy(packed.data() + n_c + n_tb, a_off, n_t * 8);
+    std::memcpy(packed.data() + n_c + n_tb + n_t, b_off, n_t * 8);
+  }
+  int64_t* d_tab = static_cast<int64_t*>(ctx_workspace(c, 3, table_elems * 8));
+  if (!d_tab) return VT_ERR_CUDA;
+  VT_CUDA(cudaMemcpyAsync(d_tab, packed.data(), table_elems * 8, cudaMemcpyHostToDevice, s));
+  VT_CUDA(cudaStreamSynchronize(s));  // `packed` is pageable and dies with this frame
+
+  const int8_t* dA = A;
+  const int8_t* dB = B;
+  int32_t* dC = C;
+  if (where == VT_HOST) {
+    int8_t* wa = static_cast<int8_t*>(ctx_workspace(c, 0, size_t(a_elems)));
+    int8_t* wb = static_cast<int8_t*>(ctx_workspace(c, 1, size_t(b_elems)));
+    int32_t* wc = static_cast<int32_t*>(ctx_workspace(c, 2, size_t(c_elems) * 4));
+    if (!wa || !wb || !wc) return VT_ERR_CUDA;
+    VT_CUDA(cudaMemcpyAsync(wa, A, size_t(a_elems), cudaMemcpyHostToDevice, s));
+    VT_CUDA(cudaMemcpyAsync(wb, B, size_t(b_elems), cudaMemcpyHostToDevice, s));
+    // Cells no tile covers keep the caller's contents.
+    VT_CUDA(cudaMemcpyAsync(wc, C, size_t(c_elems) * 4, cudaMemcpyHostToDevice, s));
+    dA = wa; dB = wb; dC = wc;
+  }
+  int rc = launch_i8_tile_program(c, dA, dB, dC, lda, ldb, ldc, n_tiles, d_tab, d_tab + n_c, d_tab + n_c + n_tb,
+                                  d_tab + n_c + n_tb + n_t, s);
+  if (rc) return rc;
+  if (where == VT_HOST) {
+    VT_CUDA(cudaMemcpyAsync(C, dC, size_t(c_elems) * 4, cudaMemcpyDeviceToHost, s));
+    return ctx_check_status(c, s);
+  }
+  return VT_OK;
+}
+
+int vt_sgemm(int dev, const float* A, const float* B, float* C, int64_t M, int64_t N, int64_t K, int variant,
+             int where, void* stream) {
+  clear_error_text();
+  if (!A || !B || !C) return fail(VT_ERR_INVALID, "null operand");
+  if (where != VT_HOST && where != VT_DEVICE) return fail(VT_ERR_INVALID, "where must be VT_HOST or VT_DEVICE");
+  if (M < 1 || N < 1 || K < 1) return fail(VT_ERR_INVALID, "dimensions must be positive");
+  if (M > 0x7fffffffLL || N > 0x7fffffffLL || K > 0x7fffffffLL) return fail(VT_ERR_INVALID, "dimension overflows int");
+  if (variant < VT_SGEMM_AUTO || variant > VT_SGEMM_SKINNY) return fail(VT_ERR_INVALID, "unknown sgemm variant %d", variant);
+  DeviceCtx* c = ctx_for(dev);
+  if (!c) return VT_ERR_CUDA;
+  cudaStream_t s = where == VT_HOST ? c->stream : pick_stream(c, stream);
+
+  const float* dA = A;
+  const float* dB = B;
+  float* dC = C;
+  if (where == VT_HOST) {
+    float* wa = static_cast<float*>(ctx_workspace(c, 0, size_t(M) * K * 4));
+    float* wb = static_cast<float*>(ctx_workspace(c, 1, size_t(K) * N * 4));
+    float* wc = static_cast<float*>(ctx_workspace(c, 2, size_t(M) * N * 4));
+    if (!wa || !wb || !wc) return VT_ERR_CUDA;
+    VT_CUDA(cudaMemcpyAsync(wa, A, size_t(M) * K * 4, cudaMemcpyHostToDevice, s));
+    VT_CUDA(cudaMemcpyAsync(wb, B, size_t(K) * N * 4, cudaMemcpyHostToDevice, s));
+    dA = wa; dB = wb; dC = wc;
+  }
+  const bool skinny_ok = M <= 16 && N % 4 == 0 &&
+                         ((reinterpret_cast<uintptr_t>(dB) | reinterpret_cast<uintptr_t>(dC)) & 15) == 0;
+  if (variant == VT_SGEMM_AUTO && skinny_ok && N >= 512 && K >= 512) variant = VT_SGEMM_SKINNY;
+  int rc;
+  if (variant == VT_SGEMM_SKINNY) {
+    if (!skinny_ok) return fail(VT_ERR_UNSUPPORTED, "skinny kernel needs M <= 16, N %% 4 == 0 and 16-byte aligned B, C");
+    int ksplit = 1;
+    const size_t pbytes = sgemm_skinny_partials_bytes(M, N, K, c->sm_count, &ksplit);
+    float* partials = nullptr;
+    if (pbytes) {
+      partials = static_cast<float*>(ctx_workspace(c, 3, pbytes));
+      if (!partials) return VT_ERR_CUDA;
+    }
+    rc = launch_sgemm_skinny(c, dA, dB, dC, partials, M, N, K, ksplit, s);
+  } else {
+    rc = launch_sgemm(c, dA, dB, dC, M, N, K, variant, s);
+  }
+  if (rc) return rc;
+  if (where == VT_HOST) {
+    VT_CUDA(cudaMemcpyAsync(C, dC, size_t(M) * N * 4, cudaMemcpyDeviceToHost, s));
+    return ctx_check_status(c, s);
+  }
+  return VT_OK;
+}
+
+int vt_sync(int dev, void* stream) {
+  clear_error_text();
+  DeviceCtx* c = ctx_for(dev);
+  if (!c) return VT_ERR_CUDA;
+  cudaStream_t s = pick_stream(c, stream);
+  VT_CUDA(cudaStreamSynchronize(s));
+  return ctx_check_status(c, s);
+}
+
+void* vt_host_alloc(size_t bytes) {
+  clear_error_text();
+  void* p = nullptr;
+  cudaError_t e = cudaMallocHost(&p, bytes ? bytes : 1);
+  if (e != cudaSuccess) {
+    fail_cuda(e, "cudaMallocHost");
+    return nullptr;
+  }
+  return p;
+}
+
+int vt_host_free(void* p) {
+  clear_error_text();
+  if (!p) return VT_OK;
+  VT_CUDA(cudaFreeHost(p));
+  return VT_OK;
+}
+
+int64_t vt_launch_count(void) { return launch_count(); }
+
+int vt_shutdown(void) {
+  clear_error_text();
+  ctx_destroy_all();
+  return VT_OK;
+}
+
+}  // extern "C"

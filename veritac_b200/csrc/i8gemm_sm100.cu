@@ -1,0 +1,325 @@
+// Exact int8 x int8 -> int32 GEMM for sm_100a: C[M,N] = A[M,K] * B[K,N], all row-major.
+//
+// This is the arithmetic of the Gemmini full-tile GEMM (a DIM=16 systolic array that overwrites an
+// accumulator tile at the first K tile and accumulates onto it afterwards, reference
+// specializations/gemmini_gemm/backend.py:490-529) executed on the 5th-generation tensor cores.
+// Under the plan's bound k*16384 <= 2^31-1 no partial sum can leave int32, so summation order is
+// unobservable and the result is bit-exact for every schedule (VeriTac/GemminiExact.lean:62-75).
+//
+// Structure (one persistent CTA per SM, 192 threads):
+//   warp 0      TMA producer: 128x128 int8 tile of A (K-major, 128-byte swizzle) and a 128(K)x256(N)
+//               slab of B exactly as stored (N contiguous => "MN-major" operand, two 128-column boxes),
+//               into a 4-stage shared-memory ring guarded by full/empty mbarriers.
+//   warp 1      MMA issuer: one thread issues tcgen05.mma.kind::i8 (M=128, N=256, K=32) four times per
+//               stage into one of two 256-column TMEM accumulators; tcgen05.commit releases the stage
+//               and, after the last K block, publishes the accumulator.
+//   warps 2..5  epilogue: tcgen05.ld the accumulator quarter owned by (warp % 4), 16-byte stores of
+//               int32 rows to HBM, then hand the accumulator back so the next tile's MMAs overlap.
+// Tiles are visited in the order the Gemmini schedule implies (row-major for baseline i,j,k,
+// column-major for reuse_b j,k,i, grouped for the batched B-reuse lowering); the order changes L2
+// reuse only, never results.
+#include "ptx_sm100.cuh"
+#include "runtime.h"
+
+namespace vt {
+namespace {
+
+constexpr int BM = 128;
+constexpr int BN = 256;
+constexpr int BK = 128;  // int8 elements == bytes: one 128-byte swizzle row of K
+constexpr int UMMA_K = 32;
+constexpr int STAGES = 4;
+constexpr int A_STAGE_BYTES = BM * BK;              // 16 KiB
+constexpr int B_STAGE_BYTES = BN * BK;              // 32 KiB
+constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+constexpr int B_BOX_BYTES = 128 * BK;               // one 128-column box of the B slab
+constexpr int NUM_THREADS = 192;
+constexpr int TMEM_COLS = 512;                      // two 256-column int32 accumulators
+
+struct TileRaster {
+  int mt, nt;  // tile counts along M and N
+  int mode;    // 0 row-major, 1 column-major, 2 grouped
+  int group;   // tile-rows per column sweep (mode 2)
+};
+
+struct PipeState {
+  uint64_t full[STAGES];
+  uint64_t empty[STAGES];
+  uint64_t tmem_full[2];
+  uint64_t tmem_empty[2];
+  uint32_t tmem_base;
+  int abort_word;
+};
+
+constexpr size_t SMEM_BYTES = 1024 + size_t(STAGES) * STAGE_BYTES + sizeof(PipeState);
+
+__device__ __forceinline__ void tile_coords(const TileRaster& rs, int t, int& mi, int& ni) {
+  if (rs.mode == 0) {
+    mi = t / rs.nt;
+    ni = t - mi * rs.nt;
+  } else if (rs.mode == 1) {
+    ni = t / rs.mt;
+    mi = t - ni * rs.mt;
+  } else {
+    const int per = rs.group * rs.nt;
+    const int g = t / per;
+    const int w = t - g * per;
+    const int rows = min(rs.group, rs.mt - g * rs.group);
+    ni = w / rows;
+    mi = g * rs.group + (w - ni * rows);
+  }
+}
+
+// kBT == false: tmB describes B as stored (inner = N, outer = K).
+// kBT == true : tmB describes B re-laid out as N x K (inner = K, outer = N).
+template <bool kBT>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+i8gemm_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                   int32_t* __restrict__ C, int M, int N, int K, TileRaster rs, int* __restrict__ status) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  PipeState* ps = reinterpret_cast<PipeState*>(tiles + size_t(STAGES) * STAGE_BYTES);
+  volatile int* abort_word = &ps->abort_word;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int num_tiles = rs.mt * rs.nt;
+  const int kblocks = (K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&ps->full[s], 1);
+      mbar_init(&ps->empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&ps->tmem_full[b], 1);
+      mbar_init(&ps->tmem_empty[b], 4);  // one arrival per epilogue warp
+    }
+    ps->abort_word = 0;
+    fence_mbar_init();
+    fence_proxy_async_smem();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc<1>(&ps->tmem_base, TMEM_COLS);
+    tmem_relinquish<1>();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = ps->tmem_base;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      uint32_t filled = 0, fill_parity = 0;  // per-stage bookkeeping for the abort drain
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        int mi, ni;
+        tile_coords(rs, t, mi, ni);
+        const int m0 = mi * BM, n0 = ni * BN;
+        for (int kb = 0; kb < kblocks; ++kb) {
+          if (!mbar_wait(&ps->empty[stage], phase ^ 1, abort_word, KSTAT_WAIT_EXPIRED_PRODUCER)) {
+            ok = false;
+            break;
+          }
+          uint64_t* full = &ps->full[stage];
+          uint8_t* a_s = tiles + size_t(stage) * STAGE_BYTES;
+          uint8_t* b_s = a_s + A_STAGE_BYTES;
+          mbar_arrive_expect_tx(full, STAGE_BYTES);
+          tma_load_2d(a_s, &tmA, full, kb * BK, m0);
+          if constexpr (kBT) {
+            tma_load_2d(b_s, &tmB, full, kb * BK, n0);
+          } else {
+            tma_load_2d(b_s, &tmB, full, n0, kb * BK);
+            tma_load_2d(b_s + B_BOX_BYTES, &tmB, full, n0 + 128, kb * BK);
+          }
+          filled |= 1u << stage;
+          fill_parity = (fill_parity & ~(1u << stage)) | (phase << stage);
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+      if (ok) {
+        // Tail: every stage released => every MMA that reads shared memory has retired and every
+        // commit arrival has landed before the CTA gives its shared memory back.
+        for (int s = 0; s < STAGES; ++s) {
+          if (!mbar_wait(&ps->empty[stage], phase ^ 1, abort_word, KSTAT_WAIT_EXPIRED_PRODUCER)) break;
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+      if (*abort_word != 0) {
+        // Aborting: wait (bounded, ignoring the abort word) for copies already issued to land.
+        for (int s = 0; s < STAGES; ++s)
+          if (filled & (1u << s)) mbar_wait_drain(&ps->full[s], (fill_parity >> s) & 1u);
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer ------------------------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_instr_desc(UMMA_D_S32, UMMA_AB_S8, false, !kBT, BM, BN);
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        if (!mbar_wait(&ps->tmem_empty[acc], acc_phase ^ 1, abort_word, KSTAT_WAIT_EXPIRED_MMA)) break;
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + uint32_t(acc * BN);
+        for (int kb = 0; kb < kblocks; ++kb) {
+          if (!mbar_wait(&ps->full[stage], phase, abort_word, KSTAT_WAIT_EXPIRED_MMA)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          const uint32_t a_addr = smem_u32(tiles + size_t(stage) * STAGE_BYTES);
+          const uint32_t b_addr = a_addr + A_STAGE_BYTES;
+#pragma unroll
+          for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+            // A (and re-laid-out B): K-major, rows of 128 bytes, 8-row groups 1024 bytes apart;
+            // a K step of 32 moves 32 bytes inside the swizzle row.
+            const uint64_t a_desc = umma_smem_desc_sw128(a_addr + kk * UMMA_K, 16, 1024);
+            // B as stored: N contiguous.  128-column blocks are one TMA box (16 KiB) apart,
+            // 8-row K groups 1024 bytes apart; a K step of 32 rows moves 4096 bytes.
+            const uint64_t b_desc = kBT ? umma_smem_desc_sw128(b_addr + kk * UMMA_K, 16, 1024)
+                                        : umma_smem_desc_sw128(b_addr + kk * UMMA_K * 128, B_BOX_BYTES, 1024);
+            umma_i8<1>(d_tmem, a_desc, b_desc, idesc, uint32_t((kb | kk) != 0));
+          }
+          umma_commit(&ps->empty[stage]);
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (!ok) break;
+        umma_commit(&ps->tmem_full[acc]);
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1;
+      }
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------ epilogue ------------------------------
+    const int q = warp & 3;  // TMEM lane quarter this warp may read
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+      int mi, ni;
+      tile_coords(rs, t, mi, ni);
+      const int m0 = mi * BM, n0 = ni * BN;
+      const bool ready = mbar_wait(&ps->tmem_full[acc], acc_phase, abort_word, KSTAT_WAIT_EXPIRED_EPILOGUE);
+      if (!__all_sync(0xffffffffu, ready)) break;
+      tc_fence_after_sync();
+      const int row = m0 + q * 32 + lane;
+      int32_t* crow = C + size_t(row) * size_t(N) + n0;
+      const uint32_t t_row = tmem_base + (uint32_t(q * 32) << 16) + uint32_t(acc * BN);
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(t_row + uint32_t(c * 32), r);
+        tmem_ld_wait();
+        if (row < M) {
+#pragma unroll
+          for (int v = 0; v < 8; ++v) {
+            const int col = n0 + c * 32 + v * 4;
+            if (col < N) st_global_v4(crow + c * 32 + v * 4, r[4 * v], r[4 * v + 1], r[4 * v + 2], r[4 * v + 3]);
+          }
+        }
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&ps->tmem_empty[acc]);
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1;
+    }
+    __syncwarp();
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc<1>(tmem_base, TMEM_COLS);
+  if (threadIdx.x == 0 && ps->abort_word != 0) atomicCAS(status, 0, ps->abort_word);
+}
+
+// B[K,N] -> Bt[N,K], 64x64 byte tiles through shared memory (only the K-major-B variant uses it).
+__global__ void __launch_bounds__(256) i8_transpose_kernel(const int8_t* __restrict__ B, int8_t* __restrict__ Bt,
+                                                           int K, int N) {
+  __shared__ int8_t tile[64][65];
+  const int n0 = blockIdx.x * 64, k0 = blockIdx.y * 64;
+  for (int i = threadIdx.x; i < 64 * 64; i += 256) {
+    const int r = i >> 6, c = i & 63;
+    const int k = k0 + r, n = n0 + c;
+    tile[r][c] = (k < K && n < N) ? B[size_t(k) * N + n] : int8_t(0);
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < 64 * 64; i += 256) {
+    const int r = i >> 6, c = i & 63;  // r: n within tile, c: k within tile
+    const int n = n0 + r, k = k0 + c;
+    if (n < N && k < K) Bt[size_t(n) * K + k] = tile[c][r];
+  }
+}
+
+}  // namespace
+
+int launch_i8gemm(DeviceCtx* c, const int8_t* A, const int8_t* B, int32_t* C, int64_t M, int64_t N, int64_t K,
+                  int raster_mode, int group, int variant, cudaStream_t s) {
+  if (variant != VT_I8_B_AS_STORED && variant != VT_I8_B_RELAYOUT)
+    return fail(VT_ERR_UNSUPPORTED, "i8gemm variant %d is not built", variant);
+  if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(C)) & 15)
+    return fail(VT_ERR_INVALID, "i8gemm operands must be 16-byte aligned");
+
+  TileRaster rs;
+  rs.mt = int((M + BM - 1) / BM);
+  rs.nt = int((N + BN - 1) / BN);
+  rs.mode = raster_mode;
+  rs.group = group < 1 ? 1 : (group > rs.mt ? rs.mt : group);
+  if (rs.mode < 0 || rs.mode > 2) return fail(VT_ERR_INVALID, "raster mode %d out of range", raster_mode);
+  const long long tiles = 1LL * rs.mt * rs.nt;
+  if (tiles > 0x7fffffffLL) return fail(VT_ERR_INVALID, "tile count overflows int");
+
+  CUtensorMap tmA, tmB;
+  int rc = encode_tmap_2d(&tmA, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, A, uint64_t(K), uint64_t(M), uint64_t(K), BK, BM);
+  if (rc) return rc;
+
+  const int grid = int(tiles < c->sm_count ? tiles : c->sm_count);
+  if (variant == VT_I8_B_AS_STORED) {
+    rc = encode_tmap_2d(&tmB, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, B, uint64_t(N), uint64_t(K), uint64_t(N), 128, BK);
+    if (rc) return rc;
+    if (!(c->func_attr_mask & 1u)) {
+      VT_CUDA(cudaFuncSetAttribute(i8gemm_umma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   int(SMEM_BYTES)));
+      c->func_attr_mask |= 1u;
+    }
+    i8gemm_umma_kernel<false><<<grid, NUM_THREADS, SMEM_BYTES, s>>>(tmA, tmB, C, int(M), int(N), int(K), rs, c->status);
+    count_launch();
+  } else {
+    int8_t* Bt = static_cast<int8_t*>(ctx_workspace(c, 3, size_t(N) * size_t(K)));
+    if (!Bt) return VT_ERR_CUDA;
+    dim3 tg(unsigned((N + 63) / 64), unsigned((K + 63) / 64));
+    i8_transpose_kernel<<<tg, 256, 0, s>>>(B, Bt, int(K), int(N));
+    count_launch();
+    rc = encode_tmap_2d(&tmB, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, Bt, uint64_t(K), uint64_t(N), uint64_t(K), BK, BN);
+    if (rc) return rc;
+    if (!(c->func_attr_mask & 2u)) {
+      VT_CUDA(cudaFuncSetAttribute(i8gemm_umma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   int(SMEM_BYTES)));
+      c->func_attr_mask |= 2u;
+    }
+    i8gemm_umma_kernel<true><<<grid, NUM_THREADS, SMEM_BYTES, s>>>(tmA, tmB, C, int(M), int(N), int(K), rs, c->status);
+    count_launch();
+  }
+  VT_CUDA(cudaGetLastError());
+  return VT_OK;
+}
+
+}  // namespace vt

@@ -1,0 +1,74 @@
+// Host-side runtime shared by the kernels' launchers and the C-ABI: per-device context (stream,
+// status word, grow-only workspace), error reporting, the driver entry point used to encode TMA
+// tensor maps, and the launch counter that the benchmark reports.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+#include "../../include/veritac_b200.h"
+
+namespace vt {
+
+struct DeviceCtx {
+  int dev = -1;
+  bool ready = false;
+  int sm_count = 0;
+  size_t smem_optin = 0;
+  cudaStream_t stream = nullptr;       // library-owned stream used when the caller passes none
+  cudaStream_t copy_in = nullptr;      // host->device staging for the host-pointer entry points
+  cudaStream_t copy_out = nullptr;     // device->host staging
+  int* status = nullptr;               // device word kernels write a KSTAT_* code into
+  int* status_host = nullptr;          // pinned mirror
+  // grow-only device workspace for host-pointer calls and operand re-layouts
+  void* ws[4] = {nullptr, nullptr, nullptr, nullptr};
+  size_t ws_bytes[4] = {0, 0, 0, 0};
+  cudaEvent_t ev[8] = {};
+  uint32_t func_attr_mask = 0;         // which kernels already had their shared-memory opt-in set here
+};
+
+// Error text for the calling thread; returns `code` so call sites can `return fail(...)`.
+int fail(int code, const char* fmt, ...);
+int fail_cuda(cudaError_t e, const char* what);
+const char* last_error_text();
+void clear_error_text();
+long long launch_count();
+void ctx_destroy_all();
+
+// Makes `dev` current and returns its context, creating it on first use; nullptr + error set on failure.
+DeviceCtx* ctx_for(int dev);
+// Grow-only workspace slot; returns nullptr (error set) on allocation failure.
+void* ctx_workspace(DeviceCtx* c, int slot, size_t bytes);
+// Reads and clears the device status word after the stream has drained.
+int ctx_check_status(DeviceCtx* c, cudaStream_t s);
+void count_launch(int n = 1);
+
+// cuTensorMapEncodeTiled for a row-major 2-D byte/word matrix: `inner` contiguous elements per
+// row, `outer` rows, 128-byte swizzle, zero fill outside the matrix.
+int encode_tmap_2d(CUtensorMap* out, CUtensorMapDataType dtype, int elem_bytes, const void* base, uint64_t inner,
+                   uint64_t outer, uint64_t row_pitch_bytes, uint32_t box_inner, uint32_t box_outer);
+
+#define VT_CUDA(expr)                                   \
+  do {                                                  \
+    cudaError_t _e = (expr);                            \
+    if (_e != cudaSuccess) return vt::fail_cuda(_e, #expr); \
+  } while (0)
+
+// ---- kernel launchers (device pointers only) ------------------------------------------------
+// raster_mode: 0 row-major tiles, 1 column-major tiles, 2 grouped (group = tile-rows per sweep).
+// variant: VT_I8_B_AS_STORED (B consumed as K x N row-major, an MN-major operand),
+// VT_I8_B_RELAYOUT (B re-laid out to N x K first, a K-major operand), VT_I8_CTA_PAIR.
+int launch_i8gemm(DeviceCtx* c, const int8_t* A, const int8_t* B, int32_t* C, int64_t M, int64_t N, int64_t K,
+                  int raster_mode, int group, int variant, cudaStream_t s);
+int launch_sgemm(DeviceCtx* c, const float* A, const float* B, float* C, int64_t M, int64_t N, int64_t K,
+                 int variant, cudaStream_t s);
+int launch_sgemm_skinny(DeviceCtx* c, const float* A, const float* B, float* C, float* partials, int64_t M,
+                        int64_t N, int64_t K, int ksplit, cudaStream_t s);
+size_t sgemm_skinny_partials_bytes(int64_t M, int64_t N, int64_t K, int sm_count, int* ksplit_out);
+int launch_i8_tile_program(DeviceCtx* c, const int8_t* A, const int8_t* B, int32_t* C, int64_t lda, int64_t ldb,
+                           int64_t ldc, int64_t n_tiles, const int64_t* d_c_off, const int64_t* d_term_begin,
+                           const int64_t* d_a_off, const int64_t* d_b_off, cudaStream_t s);
+
+}  // namespace vt

@@ -1,0 +1,332 @@
+// fp32 GEMM C[M,N] = A[M,K] * B[K,N] (row-major, C overwritten): the matmul loop nest that the
+// reference emits as OpenMP C (specializations/cpu_gemm/emit_c.py:83-155 generates the nest,
+// specializations/cpu_gemm/runner.py:155-190 times it), executed on the FP32 pipe.
+//
+//   sgemm_tile_kernel<RM,RN>  register-tiled FFMA kernel.  256 threads as a 16x16 grid; each thread
+//       owns (4*RM)x(4*RN) outputs as RM x RN blocks of 4x4 spaced 64 apart, so a CTA covers
+//       (64*RM)x(64*RN).  K is consumed 16 at a time through two shared-memory buffers: global loads
+//       for step t+1 are issued into registers before the FFMAs of step t and stored (A transposed
+//       so the inner loop reads float4s along M) after them, one __syncthreads per step.
+//   sgemm_skinny_kernel       M <= 16 ("decode-like"): HBM-bound, B is streamed exactly once.  A CTA owns
+//       128 columns and a K range; its 8 warps take interleaved 8-row slices of each 64-row chunk,
+//       keep 16x4 accumulators per thread, and fold through shared memory.  With a K split the
+//       per-split partial tiles go to scratch memory and a second kernel sums them in split order
+//       (deterministic, no atomics).
+#include "runtime.h"
+
+namespace vt {
+namespace {
+
+constexpr int SG_THREADS = 256;
+constexpr int SG_BK = 16;
+
+template <int RM, int RN, bool kGuard>
+__global__ void __launch_bounds__(SG_THREADS, (RM * RN >= 4) ? 2 : 3)
+sgemm_tile_kernel(const float* __restrict__ A, const float* __restrict__ B, float* __restrict__ C, int M, int N,
+                  int K, int tiles_m, int tiles_n, int group) {
+  constexpr int BM = 64 * RM, BN = 64 * RN;
+  constexpr int LDA = BM + 4;
+  __shared__ __align__(16) float As[2][SG_BK][LDA];
+  __shared__ __align__(16) float Bs[2][SG_BK][BN];
+
+  // Grouped tile order: sweep all tile-columns for `group` tile-rows at a time (L2 reuse of B).
+  int tm, tn;
+  {
+    const int t = blockIdx.x;
+    const int per = group * tiles_n;
+    const int g = t / per;
+    const int w = t - g * per;
+    const int rows = min(group, tiles_m - g * group);
+    tn = w / rows;
+    tm = g * group + (w - tn * rows);
+  }
+  const int m0 = tm * BM, n0 = tn * BN;
+  const int tid = threadIdx.x;
+  const int tx = tid & 15, ty = tid >> 4;
+
+  const int a_row = tid >> 2;        // 0..63 (+64 per pass)
+  const int a_k = (tid & 3) * 4;     // 0,4,8,12
+  constexpr int B_F4_PER_ROW = 16 * RN;
+  constexpr int B_ROWS_PER_PASS = SG_THREADS / B_F4_PER_ROW;  // 16 / RN
+  const int b_k = tid / B_F4_PER_ROW;
+  const int b_n = (tid % B_F4_PER_ROW) * 4;
+
+  float4 pa[RM], pb[RN];
+  // Running pointers for the unguarded path (advanced once per K step).
+  const float* a_ptr = A + size_t(m0 + a_row) * K + a_k;
+  const float* b_ptr = B + size_t(b_k) * N + n0 + b_n;
+  const size_t a_pass = size_t(64) * K, b_pass = size_t(B_ROWS_PER_PASS) * N;
+
+  auto load_tile = [&](int k0) {
+#pragma unroll
+    for (int i = 0; i < RM; ++i) {
+      const int row = m0 + a_row + 64 * i;
+      const int k = k0 + a_k;
+      if constexpr (!kGuard) {
+        pa[i] = __ldg(reinterpret_cast<const float4*>(a_ptr + i * a_pass));
+      } else {
+        float v[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) v[j] = (row < M && k + j < K) ? A[size_t(row) * K + k + j] : 0.f;
+        pa[i] = make_float4(v[0], v[1], v[2], v[3]);
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < RN; ++i) {
+      const int k = k0 + b_k + B_ROWS_PER_PASS * i;
+      const int col = n0 + b_n;
+      if constexpr (!kGuard) {
+        pb[i] = __ldg(reinterpret_cast<const float4*>(b_ptr + i * b_pass));
+      } else {
+        float v[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) v[j] = (k < K && col + j < N) ? B[size_t(k) * N + col + j] : 0.f;
+        pb[i] = make_float4(v[0], v[1], v[2], v[3]);
+      }
+    }
+    if constexpr (!kGuard) {
+      a_ptr += SG_BK;
+      b_ptr += size_t(SG_BK) * N;
+    }
+  };
+  auto store_tile = [&](int buf) {
+#pragma unroll
+    for (int i = 0; i < RM; ++i) {
+      const int r = a_row + 64 * i;
+      As[buf][a_k + 0][r] = pa[i].x;
+      As[buf][a_k + 1][r] = pa[i].y;
+      As[buf][a_k + 2][r] = pa[i].z;
+      As[buf][a_k + 3][r] = pa[i].w;
+    }
+#pragma unroll
+    for (int i = 0; i < RN; ++i)
+      *reinterpret_cast<float4*>(&Bs[buf][b_k + B_ROWS_PER_PASS * i][b_n]) = pb[i];
+  };
+
+  float acc[4 * RM][4 * RN];
+#pragma unroll
+  for (int i = 0; i < 4 * RM; ++i)
+#pragma unroll
+    for (int j = 0; j < 4 * RN; ++j) acc[i][j] = 0.f;
+
+  const int ktiles = (K + SG_BK - 1) / SG_BK;
+  load_tile(0);
+  store_tile(0);
+  __syncthreads();
+
+  for (int kt = 0; kt < ktiles; ++kt) {
+    const int buf = kt & 1;
+    if (kt + 1 < ktiles) load_tile((kt + 1) * SG_BK);
+#pragma unroll
+    for (int k = 0; k < SG_BK; ++k) {
+      float a[4 * RM], b[4 * RN];
+#pragma unroll
+      for (int i = 0; i < RM; ++i) {
+        const float4 v = *reinterpret_cast<const float4*>(&As[buf][k][64 * i + ty * 4]);
+        a[4 * i + 0] = v.x; a[4 * i + 1] = v.y; a[4 * i + 2] = v.z; a[4 * i + 3] = v.w;
+      }
+#pragma unroll
+      for (int j = 0; j < RN; ++j) {
+        const float4 v = *reinterpret_cast<const float4*>(&Bs[buf][k][64 * j + tx * 4]);
+        b[4 * j + 0] = v.x; b[4 * j + 1] = v.y; b[4 * j + 2] = v.z; b[4 * j + 3] = v.w;
+      }
+#pragma unroll
+      for (int i = 0; i < 4 * RM; ++i)
+#pragma unroll
+        for (int j = 0; j < 4 * RN; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+    }
+    if (kt + 1 < ktiles) store_tile(buf ^ 1);
+    __syncthreads();
+  }
+
+#pragma unroll
+  for (int i = 0; i < 4 * RM; ++i) {
+    const int row = m0 + 64 * (i >> 2) + ty * 4 + (i & 3);
+#pragma unroll
+    for (int j = 0; j < RN; ++j) {
+      const int col = n0 + 64 * j + tx * 4;
+      if constexpr (!kGuard) {
+        *reinterpret_cast<float4*>(C + size_t(row) * N + col) =
+            make_float4(acc[i][4 * j], acc[i][4 * j + 1], acc[i][4 * j + 2], acc[i][4 * j + 3]);
+      } else {
+        if (row < M) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e)
+            if (col + e < N) C[size_t(row) * N + col + e] = acc[i][4 * j + e];
+        }
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Skinny: M <= 16, N % 4 == 0.  grid = (N/128 rounded up, ksplit).
+// ---------------------------------------------------------------------------------------------
+constexpr int SK_M = 16;
+constexpr int SK_COLS = 128;   // columns per CTA: 32 lanes x float4
+constexpr int SK_WARPS = 8;
+constexpr int SK_RW = 8;       // B rows each warp keeps in flight per step
+constexpr int SK_KC = SK_WARPS * SK_RW;  // K rows staged per step
+
+__global__ void __launch_bounds__(SK_WARPS * 32, 2)
+sgemm_skinny_kernel(const float* __restrict__ A, const float* __restrict__ B, float* __restrict__ out, int M, int N,
+                    int K, int k_per_split) {
+  __shared__ __align__(16) float As[SK_KC][SK_M];          // A chunk, transposed: [k][m]
+  __shared__ __align__(16) float red[SK_M][SK_COLS];       // cross-warp fold
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n = blockIdx.x * SK_COLS + lane * 4;
+  const bool col_ok = n < N;  // N % 4 == 0: the float4 is entirely in or out
+  const int kbeg = blockIdx.y * k_per_split;
+  const int kend = min(K, kbeg + k_per_split);
+
+  float acc[SK_M][4];
+#pragma unroll
+  for (int m = 0; m < SK_M; ++m)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[m][j] = 0.f;
+
+  for (int k0 = kbeg; k0 < kend; k0 += SK_KC) {
+    __syncthreads();  // previous chunk fully consumed
+    for (int i = threadIdx.x; i < SK_KC * SK_M; i += SK_WARPS * 32) {
+      const int m = i / SK_KC, kk = i - m * SK_KC;  // consecutive threads walk K: coalesced reads of A
+      const int k = k0 + kk;
+      As[kk][m] = (m < M && k < kend) ? A[size_t(m) * K + k] : 0.f;
+    }
+    __syncthreads();
+    const int kw = k0 + warp * SK_RW;
+    float4 bv[SK_RW];
+#pragma unroll
+    for (int r = 0; r < SK_RW; ++r) {
+      const int k = kw + r;
+      bv[r] = (col_ok && k < kend) ? __ldcs(reinterpret_cast<const float4*>(B + size_t(k) * N + n))
+                                   : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+#pragma unroll
+    for (int r = 0; r < SK_RW; ++r) {
+      const float* arow = &As[warp * SK_RW + r][0];
+#pragma unroll
+      for (int mq = 0; mq < SK_M / 4; ++mq) {
+        const float4 av = *reinterpret_cast<const float4*>(arow + 4 * mq);
+        const float am[4] = {av.x, av.y, av.z, av.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          acc[4 * mq + e][0] = fmaf(am[e], bv[r].x, acc[4 * mq + e][0]);
+          acc[4 * mq + e][1] = fmaf(am[e], bv[r].y, acc[4 * mq + e][1]);
+          acc[4 * mq + e][2] = fmaf(am[e], bv[r].z, acc[4 * mq + e][2]);
+          acc[4 * mq + e][3] = fmaf(am[e], bv[r].w, acc[4 * mq + e][3]);
+        }
+      }
+    }
+  }
+
+  // Fold the 8 warps' partial tiles in warp order (fixed order => reproducible bits).
+  for (int w = 0; w < SK_WARPS; ++w) {
+    __syncthreads();
+    if (warp == w) {
+#pragma unroll
+      for (int m = 0; m < SK_M; ++m) {
+        float4* p = reinterpret_cast<float4*>(&red[m][lane * 4]);
+        float4 v = (w == 0) ? make_float4(0.f, 0.f, 0.f, 0.f) : *p;
+        v.x += acc[m][0]; v.y += acc[m][1]; v.z += acc[m][2]; v.w += acc[m][3];
+        *p = v;
+      }
+    }
+  }
+  __syncthreads();
+  // out is C itself (no K split) or the partial tile of this split: [split][M][N].
+  float* dst = out + size_t(blockIdx.y) * size_t(M) * size_t(N);
+  for (int i = threadIdx.x; i < SK_M * (SK_COLS / 4); i += SK_WARPS * 32) {
+    const int m = i / (SK_COLS / 4), c4 = i - m * (SK_COLS / 4);
+    const int col = blockIdx.x * SK_COLS + c4 * 4;
+    if (m < M && col < N)
+      *reinterpret_cast<float4*>(dst + size_t(m) * N + col) = *reinterpret_cast<const float4*>(&red[m][c4 * 4]);
+  }
+}
+
+__global__ void __launch_bounds__(256)
+sgemm_skinny_reduce_kernel(const float* __restrict__ partials, float* __restrict__ C, int64_t mn4, int ksplit) {
+  const int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= mn4) return;
+  const float4* p = reinterpret_cast<const float4*>(partials);
+  float4 s = p[i];
+  for (int k = 1; k < ksplit; ++k) {
+    const float4 v = p[int64_t(k) * mn4 + i];
+    s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+  }
+  reinterpret_cast<float4*>(C)[i] = s;
+}
+
+template <int RM, int RN>
+int launch_tile(const float* A, const float* B, float* C, int M, int N, int K, cudaStream_t s) {
+  constexpr int BM = 64 * RM, BN = 64 * RN;
+  const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + BN - 1) / BN;
+  const long long tiles = 1LL * tiles_m * tiles_n;
+  if (tiles > 0x7fffffffLL) return fail(VT_ERR_INVALID, "sgemm tile count overflows int");
+  const int group = tiles_m < 8 ? tiles_m : 8;
+  const bool aligned =
+      ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(C)) & 15) == 0;
+  const bool full = aligned && M % BM == 0 && N % BN == 0 && K % SG_BK == 0;
+  if (full)
+    sgemm_tile_kernel<RM, RN, false><<<unsigned(tiles), SG_THREADS, 0, s>>>(A, B, C, M, N, K, tiles_m, tiles_n, group);
+  else
+    sgemm_tile_kernel<RM, RN, true><<<unsigned(tiles), SG_THREADS, 0, s>>>(A, B, C, M, N, K, tiles_m, tiles_n, group);
+  count_launch();
+  VT_CUDA(cudaGetLastError());
+  return VT_OK;
+}
+
+}  // namespace
+
+size_t sgemm_skinny_partials_bytes(int64_t M, int64_t N, int64_t K, int sm_count, int* ksplit_out) {
+  // Enough CTAs for ~4 per SM, never a split shorter than 8 chunks of SK_KC rows, and splits of
+  // (nearly) equal chunk counts.
+  const int64_t col_ctas = (N + SK_COLS - 1) / SK_COLS;
+  const int64_t chunks = (K + SK_KC - 1) / SK_KC;
+  int64_t want = (4LL * sm_count + col_ctas - 1) / col_ctas;
+  const int64_t max_split = chunks / 8 > 0 ? chunks / 8 : 1;
+  if (want > max_split) want = max_split;
+  if (want < 1) want = 1;
+  if (want > 64) want = 64;
+  const int64_t per = (chunks + want - 1) / want;
+  want = (chunks + per - 1) / per;
+  if (ksplit_out) *ksplit_out = int(want);
+  return want > 1 ? size_t(want) * size_t(M) * size_t(N) * sizeof(float) : 0;
+}
+
+int launch_sgemm_skinny(DeviceCtx* c, const float* A, const float* B, float* C, float* partials, int64_t M,
+                        int64_t N, int64_t K, int ksplit, cudaStream_t s) {
+  (void)c;
+  if (M > SK_M || N % 4 != 0) return fail(VT_ERR_UNSUPPORTED, "skinny kernel needs M <= 16 and N %% 4 == 0");
+  if ((reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(C) | reinterpret_cast<uintptr_t>(partials)) & 15)
+    return fail(VT_ERR_INVALID, "skinny kernel operands must be 16-byte aligned");
+  if (ksplit < 1) ksplit = 1;
+  if (ksplit > 1 && !partials) return fail(VT_ERR_INVALID, "K split needs a partials buffer");
+  const int64_t chunks = (K + SK_KC - 1) / SK_KC;
+  const int k_per_split = int((chunks + ksplit - 1) / ksplit) * SK_KC;
+  dim3 grid(unsigned((N + SK_COLS - 1) / SK_COLS), unsigned(ksplit));
+  float* out = ksplit > 1 ? partials : C;
+  sgemm_skinny_kernel<<<grid, SK_WARPS * 32, 0, s>>>(A, B, out, int(M), int(N), int(K), k_per_split);
+  count_launch();
+  if (ksplit > 1) {
+    const int64_t mn4 = M * N / 4;
+    sgemm_skinny_reduce_kernel<<<unsigned((mn4 + 255) / 256), 256, 0, s>>>(partials, C, mn4, ksplit);
+    count_launch();
+  }
+  VT_CUDA(cudaGetLastError());
+  return VT_OK;
+}
+
+int launch_sgemm(DeviceCtx* c, const float* A, const float* B, float* C, int64_t M, int64_t N, int64_t K,
+                 int variant, cudaStream_t s) {
+  if (M > 0x7fffffffLL || N > 0x7fffffffLL || K > 0x7fffffffLL) return fail(VT_ERR_INVALID, "dimension overflows int");
+  if (variant == 0) {
+    // Large problems: 128x128 tiles.  When that grid cannot fill the GPU use 64x64 tiles.
+    const long long big_tiles = ((M + 127) / 128) * ((N + 127) / 128);
+    variant = big_tiles >= c->sm_count ? 1 : 2;
+  }
+  if (variant == 1) return launch_tile<2, 2>(A, B, C, int(M), int(N), int(K), s);
+  if (variant == 2) return launch_tile<1, 1>(A, B, C, int(M), int(N), int(K), s);
+  return fail(VT_ERR_UNSUPPORTED, "sgemm variant %d is not built", variant);
+}
+
+}  // namespace vt

@@ -16,8 +16,9 @@
  *                         returns when C is complete (pinned memory from vt_host_alloc makes the
  *                         copies run at full PCIe rate).
  *              VT_DEVICE = A, B, C are device pointers on `dev`; the call only enqueues work on
- *                         `stream` (a cudaStream_t, or NULL for the library's own stream) and
- *                         returns; vt_sync() waits and reports kernel status.
+ *                         `stream` (a cudaStream_t, or NULL for the library's own stream; the
+ *                         legacy default stream is cudaStreamLegacy, (void*)1) and returns;
+ *                         vt_sync() waits and reports kernel status.
  *   - One host thread per device at a time; different devices may be driven concurrently.
  */
 #ifndef VERITAC_B200_H

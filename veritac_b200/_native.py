@@ -112,6 +112,17 @@ def _ptr(x) -> int:
     return int(x)
 
 
+def torch_stream() -> int:
+    """Handle of torch's current CUDA stream in the form the C ABI takes.
+
+    The ABI reads NULL as "the library's own stream", so torch's legacy default stream (handle 0)
+    is passed as cudaStreamLegacy (0x1).
+    """
+    import torch
+
+    return int(torch.cuda.current_stream().cuda_stream) or 1
+
+
 def i8gemm(A, B, C, M: int, N: int, K: int, *, dev: int = 0, raster: int = VT_RASTER_AUTO, batch_rows: int = 1,
            variant: int = VT_I8_AUTO, where: int = VT_HOST, stream: int = 0) -> None:
     check(lib().vt_i8gemm(dev, _ptr(A), _ptr(B), _ptr(C), M, N, K, raster, batch_rows, variant, where, stream))

@@ -1,0 +1,1 @@
+"""cpu_gemm specialization (B200 back end); implementations are loaded explicitly."""

@@ -1,0 +1,227 @@
+"""Parity of the CUDA int8 path with the oracle and with the reference's recorded results.
+Everything goes through the C ABI (ctypes) or the drop-in Python entry points above it."""
+import hashlib
+import json
+
+import numpy as np
+import pytest
+
+import gemmini_oracle as go
+from conftest import commands_from_dicts
+
+pytestmark = pytest.mark.gpu
+
+
+def sha(obj):
+    return hashlib.sha256(json.dumps(obj).encode()).hexdigest()
+
+
+@pytest.fixture(scope="module")
+def g(native):
+    from veritac_b200.CodeGen import gemmini
+    return gemmini
+
+
+@pytest.fixture(scope="module")
+def lowering(native):
+    from veritac_b200.CodeGen import gemmini_lowering
+    return gemmini_lowering
+
+
+def gemm(native, a, b, m, n, k, **kw):
+    c = np.full(m * n, -2**31, dtype=np.int32)   # poison: every cell must be written
+    native.i8gemm(np.ascontiguousarray(a), np.ascontiguousarray(b), c, m, n, k, **kw)
+    return c
+
+
+def test_spike_recorded_outputs_bit_exact(native, g, golden_gemmini):
+    """The 24 matrices upstream Gemmini Spike produced, through the C ABI and through run_commands."""
+    for case in golden_gemmini["spike_outputs"]:
+        p = case["plan"]
+        for mode in case["modes"]:
+            a, b = go.raw_fill_inputs(mode["mode"], case["size_a"], case["size_b"])
+            assert gemm(native, a, b, p["m"], p["n"], p["k"]).tolist() == mode["C"]
+            got, _ = g.run_commands(commands_from_dicts(case["commands"]), p, a.tolist(), b.tolist())
+            assert got == mode["C"]
+
+
+def test_recorded_output_hashes(native, g, golden_gemmini):
+    """30 recorded sha256(json.dumps(C)) of accepted programs, reproduced by run_commands on the GPU."""
+    for run in golden_gemmini["recorded_hashes"]:
+        p = run["plan"]
+        cmds = commands_from_dicts(run["commands"])
+        for case in run["cases"]:
+            A, B = g.deterministic_inputs(p["m"], p["n"], p["k"], case["seed"], case["mode"])
+            C, stats = g.run_commands(cmds, p, A, B)
+            assert sha(C) == case["output_sha256"] and stats == case["stats"]
+
+
+def test_generator_streams_match_reference_interpreter(native, g, lowering, golden_gemmini):
+    for e in golden_gemmini["generators"]:
+        if "runs" not in e:
+            continue
+        plan, b = e["plan"], e["batch_rows"]
+        cmds = g.gen_commands(plan) if b is None else lowering.gen_batched_reuse_b(plan, b)
+        for run in e["runs"]:
+            A, B = g.deterministic_inputs(plan["m"], plan["n"], plan["k"], run["seed"], run["mode"])
+            assert sha(A) == run["a_sha256"] and sha(B) == run["b_sha256"]
+            C, stats = g.run_commands(cmds, plan, A, B)
+            assert sha(C) == run["output_sha256"] and stats == run["stats"]
+            assert C == g.scalar_matmul(A, B, plan["m"], plan["n"], plan["k"])
+            C2, stats2 = g.run_plan(plan, A, B, batch_rows=b)
+            assert C2 == C and stats2 == stats
+
+
+def test_reference_differential_cases(native, g):
+    """tests/test_gemmini.py:52-75 of the reference: shapes x schedules x input modes."""
+    cases = [((16, 16, 16), (("lcg", 7), ("max", 0), ("minmax", 0))),
+             ((32, 32, 32), (("lcg", 1), ("lcg", 987654321), ("max", 0), ("minmax", 0))),
+             ((48, 32, 64), (("lcg", 42), ("max", 0), ("minmax", 0))), ((64, 64, 64), (("lcg", 3), ("min", 0)))]
+    for (m, n, k), modes in cases:
+        for schedule in g.SUPPORTED_SCHEDULES:
+            for mode, seed in modes:
+                A, B = g.deterministic_inputs(m, n, k, seed, mode)
+                plan = g.make_plan(m, n, k, schedule)
+                C, stats = g.run_commands(g.gen_commands(plan), plan, A, B)
+                assert C == go.scalar_matmul(A, B, m, n, k)
+                assert stats["macs"] == m * n * k
+    winner = g.optimize(48, 32, 64)["winner"]
+    A, B = g.deterministic_inputs(48, 32, 64, 5)
+    C, _ = g.run_commands(g.gen_commands(winner), winner, A, B)
+    assert C == go.scalar_matmul(A, B, 48, 32, 64)
+
+
+def test_config2_int8_64_cubed_partial_sums(native, g):
+    """BASELINE config 2: 64^3 on the 4x4x4 tile grid, nonzero partial sums over the 4 K tiles."""
+    rng = np.random.default_rng(20260917 + 2)
+    a = rng.integers(-128, 128, 64 * 64, dtype=np.int8)
+    b = rng.integers(-128, 128, 64 * 64, dtype=np.int8)
+    want = go.matmul_exact(a, b, 64, 64, 64).reshape(-1)
+    part = go.matmul_exact(a.reshape(64, 64)[:, :16].reshape(-1), b.reshape(64, 64)[:16].reshape(-1), 64, 64, 16)
+    assert np.count_nonzero(part) > 0 and not np.array_equal(part.reshape(-1), want)
+    for schedule in g.SUPPORTED_SCHEDULES:
+        plan = g.make_plan(64, 64, 64, schedule)
+        C, stats = g.run_commands(g.gen_commands(plan), plan, a, b)
+        assert C.dtype == np.int32 and np.array_equal(C, want)
+        assert (stats["overwrites"], stats["accumulates"]) == (256, 768)
+
+
+@pytest.mark.parametrize("variant", [1, 2])
+def test_shapes_rasters_variants(native, variant):
+    rng = np.random.default_rng(11)
+    shapes = [(16, 16, 16), (16, 80, 32), (80, 16, 32), (48, 32, 64), (128, 256, 128), (144, 272, 400),
+              (256, 512, 384), (640, 768, 256), (1024, 1024, 1024), (2048, 16, 48), (16, 4096, 16)]
+    for (m, n, k) in shapes:
+        a = rng.integers(-128, 128, m * k, dtype=np.int8)
+        b = rng.integers(-128, 128, k * n, dtype=np.int8)
+        want = go.matmul_exact(a, b, m, n, k).reshape(-1)
+        for raster, br in ((0, 1), (1, 1), (2, 3), (2, 64), (3, 1)):
+            assert np.array_equal(gemm(native, a, b, m, n, k, variant=variant, raster=raster, batch_rows=br), want)
+
+
+def test_extreme_values_at_the_overflow_bound(native):
+    """-128 * -128 * K and -128 * 127 * K at K = 8192 (|sum| = 2^27) and at the largest legal K."""
+    for k in (8192, 131056):
+        m, n = 32, 48
+        for av, bv in ((-128, -128), (-128, 127), (127, 127)):
+            a = np.full(m * k, av, dtype=np.int8)
+            b = np.full(k * n, bv, dtype=np.int8)
+            c = gemm(native, a, b, m, n, k)
+            assert (c == av * bv * k).all()
+    alt_a, alt_b = go.raw_fill_inputs("extrema", 64 * 8192, 8192 * 64)
+    assert np.array_equal(gemm(native, alt_a, alt_b, 64, 64, 8192), go.matmul_exact(alt_a, alt_b, 64, 64, 8192).reshape(-1))
+
+
+def test_device_resident_call_and_status(native):
+    import torch
+    rng = np.random.default_rng(5)
+    m, n, k = 384, 512, 640
+    a = rng.integers(-128, 128, (m, k), dtype=np.int8)
+    b = rng.integers(-128, 128, (k, n), dtype=np.int8)
+    dA, dB = torch.from_numpy(a).cuda(), torch.from_numpy(b).cuda()
+    dC = torch.full((m, n), -2**31, dtype=torch.int32, device="cuda")
+    before = native.launch_count()
+    native.i8gemm(dA, dB, dC, m, n, k, where=native.VT_DEVICE, stream=native.torch_stream())
+    native.sync(0, native.torch_stream())
+    assert native.launch_count() == before + 1
+    assert np.array_equal(dC.cpu().numpy(), go.matmul_exact(a, b, m, n, k).astype(np.int32))
+
+
+def test_shared_b_batch(native):
+    """Batched B-reuse (BASELINE config 4 semantics, small): independent A_i against one B."""
+    rng = np.random.default_rng(9)
+    batch, m, n, k = 5, 48, 64, 96
+    a = rng.integers(-128, 128, (batch, m, k), dtype=np.int8)
+    b = rng.integers(-128, 128, (k, n), dtype=np.int8)
+    for acc_rows in (16, 32, 1024):
+        c = np.full((batch, m, n), -2**31, dtype=np.int32)
+        native.i8gemm_shared_b(a, b, c, batch, m, n, k, acc_rows=acc_rows)
+        for i in range(batch):
+            assert np.array_equal(c[i], go.matmul_exact(a[i], b, m, n, k).astype(np.int32))
+
+
+def test_tile_program_for_streams_that_are_not_a_gemm(native, g):
+    """Valid streams whose result is not the full product run tile by tile and still equal the
+    sequential interpreter: K truncated to the first tile; and a stream that never accumulates."""
+    m = n = k = 48
+    A, B = g.deterministic_inputs(m, n, k, 77)
+    plan = g.make_plan(m, n, k, "baseline")
+    cmds = g.gen_commands(plan)
+    for c in cmds:
+        if c.kind == "preload":
+            c.out_addr &= ~g.ACCUMULATE_BIT      # every K tile overwrites: C = last K tile's product
+    want, want_stats = go.interpret(cmds, plan, A, B)
+    got, stats = g.run_commands(cmds, plan, A, B)
+    assert got == want and stats == want_stats and got != go.scalar_matmul(A, B, m, n, k)
+    # same output tile moved out twice with different contents: the later mvout wins
+    cmds = g.gen_commands(plan)
+    first_mvout = next(i for i, c in enumerate(cmds) if c.kind == "mvout")
+    dup = g.Mvout(16, cmds[first_mvout].acc_addr, 16, 16)      # tile (0,0)'s accumulator also lands on tile (0,1)
+    cmds.insert(first_mvout + 1, dup)
+    want, _ = go.interpret(cmds, plan, A, B)
+    got, _ = g.run_commands(cmds, plan, A, B)
+    assert got == want
+
+
+def test_full_size_8192_cubed_properties(native):
+    """BASELINE config 3 at full size, device resident: sampled rows against the exact product,
+    the row-sum identity C*1 = A*(B*1) over every cell, poison fully overwritten, raster
+    independence, and M-row sharding equals the unsharded result."""
+    import torch
+    M = N = K = 8192
+    gen = torch.Generator(device="cuda").manual_seed(20260917 + 3)
+    A = torch.randint(-128, 128, (M, K), dtype=torch.int8, device="cuda", generator=gen)
+    B = torch.randint(-128, 128, (K, N), dtype=torch.int8, device="cuda", generator=gen)
+    C = torch.full((M, N), -2**31, dtype=torch.int32, device="cuda")
+    st = native.torch_stream()
+    native.i8gemm(A, B, C, M, N, K, where=native.VT_DEVICE, stream=st)
+    native.sync(0, st)
+    rows = torch.randint(0, M, (48,), device="cuda", generator=gen)
+    exact = (A[rows].double() @ B.double()).to(torch.int64)
+    assert torch.equal(C[rows].to(torch.int64), exact)
+    ones = B.to(torch.int64).sum(dim=1)                       # B * 1
+    assert torch.equal(C.to(torch.int64).sum(dim=1), (A.to(torch.float64) @ ones.to(torch.float64)).to(torch.int64))
+    C2 = torch.full((M, N), -2**31, dtype=torch.int32, device="cuda")
+    native.i8gemm(A, B, C2, M, N, K, raster=native.VT_RASTER_BASELINE, where=native.VT_DEVICE, stream=st)
+    native.sync(0, st)
+    assert torch.equal(C, C2)
+    from veritac_b200.sharding import row_shard
+    C3 = torch.full((M, N), -2**31, dtype=torch.int32, device="cuda")
+    for r in range(8):
+        r0, r1 = row_shard(M, 8, r)
+        native.i8gemm(A[r0:r1], B, C3[r0:r1], r1 - r0, N, K, where=native.VT_DEVICE, stream=st)
+    native.sync(0, st)
+    assert torch.equal(C, C3)
+
+
+def test_host_buffers_equal_device_buffers_large(native):
+    """The host-pointer entry point (row-block pipeline of copies and launches) at a multi-block size."""
+    import torch
+    rng = np.random.default_rng(21)
+    m, n, k = 8192 + 256, 1024, 512
+    a = rng.integers(-128, 128, (m, k), dtype=np.int8)
+    b = rng.integers(-128, 128, (k, n), dtype=np.int8)
+    c = np.full((m, n), -2**31, dtype=np.int32)
+    native.i8gemm(a, b, c, m, n, k)
+    want = (torch.from_numpy(a).cuda().double() @ torch.from_numpy(b).cuda().double()).to(torch.int32).cpu().numpy()
+    assert np.array_equal(c, want)

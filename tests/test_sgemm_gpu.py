@@ -1,0 +1,102 @@
+"""Parity of the CUDA fp32 path: relative Frobenius error <= 1e-5 against float64 (the stated
+tolerance), agreement with the generated-OpenMP-C restatement on the same seeded inputs, and the
+drop-in `benchmark_matmul` entry point."""
+import numpy as np
+import pytest
+
+import loopnest_oracle as lo
+
+pytestmark = pytest.mark.gpu
+
+TOL = 1e-5   # relative Frobenius error against a float64 product
+
+
+def relfro(c, ref):
+    return float(np.linalg.norm(c.astype(np.float64) - ref) / np.linalg.norm(ref))
+
+
+def uniform(rng, shape):
+    return (rng.random(shape, dtype=np.float32) * 2 - 1)
+
+
+@pytest.mark.parametrize("variant", [0, 1, 2])
+def test_shapes_against_float64(native, variant):
+    rng = np.random.default_rng(20260917 + 1)
+    for (m, n, k) in ((256, 256, 256), (1, 1, 1), (5, 3, 2), (77, 130, 33), (300, 200, 100), (128, 128, 16),
+                      (129, 127, 17), (512, 384, 1000), (1024, 1024, 1024), (64, 2048, 96)):
+        a, b = uniform(rng, (m, k)), uniform(rng, (k, n))
+        c = np.full((m, n), np.nan, dtype=np.float32)
+        native.sgemm(a, b, c, m, n, k, variant=variant)
+        assert relfro(c, a.astype(np.float64) @ b.astype(np.float64)) <= TOL, (m, n, k)
+
+
+def test_config1_256_cubed_vs_generated_c(native, liboracle):
+    """BASELINE config 1: uniform[-1,1) fp32 256^3, C zero-initialised; the generated OpenMP nests
+    (float64, as the reference emits them) are the float64 reference."""
+    rng = np.random.default_rng(20260917 + 1)
+    m = n = k = 256
+    a, b = uniform(rng, (m, k)), uniform(rng, (k, n))
+    a64, b64 = a.astype(np.float64), b.astype(np.float64)
+    ref_tuned, ref_naive = np.zeros((m, n)), np.zeros((m, n))
+    liboracle.oracle_dgemm_tuned(a64.ctypes.data, b64.ctypes.data, ref_tuned.ctypes.data, m, n, k)
+    liboracle.oracle_dgemm_naive(a64.ctypes.data, b64.ctypes.data, ref_naive.ctypes.data, m, n, k)
+    assert relfro(ref_tuned, ref_naive) < 1e-14
+    for variant in (0, 1, 2):
+        c = np.zeros((m, n), dtype=np.float32)
+        native.sgemm(a, b, c, m, n, k, variant=variant)
+        assert relfro(c, ref_tuned) <= TOL and relfro(c, a64 @ b64) <= TOL
+
+
+def test_skinny_kernel(native):
+    rng = np.random.default_rng(20260917 + 5)
+    for (m, n, k) in ((16, 8192, 8192), (16, 1024, 640), (7, 1024, 640), (1, 512, 4096), (16, 516, 100),
+                      (3, 128, 64)):
+        a, b = uniform(rng, (m, k)), uniform(rng, (k, n))
+        c = np.full((m, n), np.nan, dtype=np.float32)
+        native.sgemm(a, b, c, m, n, k, variant=native.VT_SGEMM_SKINNY)
+        assert relfro(c, a.astype(np.float64) @ b.astype(np.float64)) <= TOL, (m, n, k)
+        c2 = np.full((m, n), np.nan, dtype=np.float32)
+        native.sgemm(a, b, c2, m, n, k, variant=native.VT_SGEMM_SKINNY)
+        assert np.array_equal(c, c2)      # fixed summation order: bit-reproducible
+    with pytest.raises(native.NativeError):
+        native.sgemm(uniform(rng, (17, 64)), uniform(rng, (64, 64)), np.zeros((17, 64), np.float32), 17, 64, 64,
+                     variant=native.VT_SGEMM_SKINNY)
+
+
+def test_config5_large_fp32(native):
+    """BASELINE config 5: 8192^3 (device resident, checked on sampled rows in float64 on the GPU)
+    and the skinny 16 x 8192 x 8192 shape."""
+    import torch
+    M = N = K = 8192
+    gen = torch.Generator(device="cuda").manual_seed(20260917 + 5)
+    A = torch.rand((M, K), device="cuda", generator=gen) * 2 - 1
+    B = torch.rand((K, N), device="cuda", generator=gen) * 2 - 1
+    C = torch.full((M, N), float("nan"), device="cuda")
+    st = native.torch_stream()
+    native.sgemm(A, B, C, M, N, K, where=native.VT_DEVICE, stream=st)
+    native.sync(0, st)
+    rows = torch.arange(0, M, 64, device="cuda")
+    ref = A[rows].double() @ B.double()
+    assert float((C[rows].double() - ref).norm() / ref.norm()) <= TOL
+    assert not torch.isnan(C).any()
+    C16 = torch.full((16, N), float("nan"), device="cuda")
+    native.sgemm(A[:16], B, C16, 16, N, K, where=native.VT_DEVICE, stream=st)
+    native.sync(0, st)
+    ref16 = A[:16].double() @ B.double()
+    assert float((C16.double() - ref16).norm() / ref16.norm()) <= TOL
+
+
+def test_benchmark_matmul_drop_in(native, golden_cpu_gemm):
+    """The reference's entry point on its own operand pattern: same keys, same four cells."""
+    from veritac_b200.CodeGen import runner
+    for run in golden_cpu_gemm["benchmark_matmul"]:
+        M, K, N = run["M"], run["K"], run["N"]
+        stmt = lo.matmul_stmt(M, K, N)
+        if run["schedule"]:
+            stmt = lo.apply_tactics(stmt, lo.README_SCHEDULE)
+        r = runner.benchmark_matmul(stmt, M, K, N, num_runs=3)
+        assert {"c_time_ms", "numpy_time_ms", "speedup", "correct", "c_first_values", "np_first_values"} <= set(r)
+        assert r["correct"] is True
+        assert r["c_first_values"] == run["c_first_values"] and r["np_first_values"] == run["np_first_values"]
+        assert r["rel_frobenius_error"] == 0.0      # small-integer operands: fp32 is exact
+        assert r["c_time_ms"] > 0 and r["speedup"] > 0

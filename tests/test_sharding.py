@@ -1,0 +1,72 @@
+"""The multi-rank host logic on CPU: two gloo ranks shard M by rows, rank 0's B is replicated by a
+broadcast, each rank computes only its block (the exact CPU product stands in for the device call),
+and the assembled C equals the unsharded product."""
+import os
+import subprocess
+import sys
+
+import pytest
+
+from conftest import REPO
+from veritac_b200.sharding import batch_shard, row_shard
+
+
+def test_row_shard_tiles_the_range():
+    for rows in (0, 16, 48, 8192, 8192 * 8, 1040):
+        for world in (1, 2, 3, 4, 8):
+            spans = [row_shard(rows, world, r) for r in range(world)]
+            assert spans[0][0] == 0 and spans[-1][1] == rows
+            for (a0, a1), (b0, b1) in zip(spans, spans[1:]):
+                assert a1 == b0
+            sizes = [e - b for b, e in spans]
+            assert all(s % 16 == 0 for s in sizes) and max(sizes) - min(sizes) <= 16
+    assert [row_shard(8192, 8, r) for r in (0, 7)] == [(0, 1024), (7168, 8192)]
+    assert [batch_shard(256, 8, r) for r in (0, 1, 7)] == [(0, 32), (32, 64), (224, 256)]
+    with pytest.raises(ValueError):
+        row_shard(100, 2, 0)
+    with pytest.raises(ValueError):
+        row_shard(64, 2, 2)
+
+
+WORKER = r"""
+import os, sys
+sys.path.insert(0, {repo!r}); sys.path.insert(0, {repo!r} + "/oracle")
+import numpy as np, torch, torch.distributed as dist
+from veritac_b200 import sharding
+import gemmini_oracle as go
+rank, world, _ = sharding.init_process_group(backend="gloo", timeout_s=60)
+M, N, K = 80, 48, 64
+rng = np.random.default_rng(123)
+A = rng.integers(-128, 128, (M, K), dtype=np.int8)             # every rank can regenerate A ...
+B_true = rng.integers(-128, 128, (K, N), dtype=np.int8)
+B = torch.from_numpy(B_true.copy()) if rank == 0 else torch.zeros((K, N), dtype=torch.int8)
+sharding.replicate_from_rank0(B)                                 # ... but B only arrives by broadcast
+assert np.array_equal(B.numpy(), B_true)
+r0, r1 = sharding.row_shard(M, world, rank)
+C_rows = np.full((r1 - r0, N), -2**31, dtype=np.int32)
+def compute(a, b, c):
+    c[:] = go.matmul_exact(a, b, a.shape[0], N, K).astype(np.int32)
+sharding.sharded_gemm(compute, A[r0:r1], B.numpy(), C_rows)
+parts = [None] * world
+dist.all_gather_object(parts, (r0, r1, C_rows))
+C = np.concatenate([p[2] for p in sorted(parts, key=lambda p: p[0])])
+assert np.array_equal(C, go.matmul_exact(A, B_true, M, N, K).astype(np.int32))
+assert sorted((p[0], p[1]) for p in parts) == [(0, 48), (48, 80)]
+dist.barrier(); dist.destroy_process_group()
+print("rank", rank, "ok")
+"""
+
+
+def test_two_rank_gloo_row_sharding(tmp_path):
+    script = tmp_path / "worker.py"
+    script.write_text(WORKER.format(repo=str(REPO)))
+    port = 29500 + (os.getpid() % 2000)
+    procs = []
+    for rank in range(2):
+        env = dict(os.environ, RANK=str(rank), WORLD_SIZE="2", LOCAL_RANK=str(rank), MASTER_ADDR="127.0.0.1",
+                   MASTER_PORT=str(port))
+        procs.append(subprocess.Popen([sys.executable, str(script)], env=env, stdout=subprocess.PIPE,
+                                      stderr=subprocess.STDOUT, text=True))
+    outs = [p.communicate(timeout=180)[0] for p in procs]
+    for rank, (p, out) in enumerate(zip(procs, outs)):
+        assert p.returncode == 0 and "rank %d ok" % rank in out, out

@@ -1,0 +1,88 @@
+"""Sharding one GEMM over the GPUs of a box: one process per GPU, torch.distributed for plumbing.
+
+Every output row of C = A * B depends on one row of A and all of B (the reference's spec:
+VeriTac/Gemmini/Semantics.lean:76-77), so the path shards with no reduction: rank r owns a block of
+rows of A and C (or a block of the batch for the shared-B form) and B is replicated — broadcast once
+from rank 0 into each GPU's own HBM, outside the steady state.  Kernels only ever read local memory;
+there is no data-path collective and no split-K.
+"""
+from __future__ import annotations
+
+import os
+
+
+def row_shard(rows: int, world: int, rank: int, align: int = 16) -> tuple[int, int]:
+    """[begin, end) of the rows rank `rank` of `world` owns.
+
+    Blocks are contiguous, multiples of `align` (16 keeps every shard inside the Gemmini plan
+    domain), differ by at most one `align` block, and tile [0, rows) exactly.  `rows` itself must be
+    a multiple of `align`.  A rank may get an empty block when there are fewer blocks than ranks.
+    """
+    if world < 1 or not 0 <= rank < world:
+        raise ValueError("rank %d outside world of %d" % (rank, world))
+    if rows < 0 or rows % align:
+        raise ValueError("rows=%d must be a non-negative multiple of %d" % (rows, align))
+    blocks = rows // align
+    base, extra = divmod(blocks, world)
+    begin = rank * base + min(rank, extra)
+    end = begin + base + (1 if rank < extra else 0)
+    return begin * align, end * align
+
+
+def batch_shard(batch: int, world: int, rank: int) -> tuple[int, int]:
+    """[begin, end) of the batch entries (independent A_i against one shared B) a rank owns."""
+    return row_shard(batch, world, rank, align=1)
+
+
+def env_rank() -> tuple[int, int, int]:
+    """(rank, world_size, local_rank) from the torchrun environment; (0, 1, 0) outside it."""
+    return (int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1")),
+            int(os.environ.get("LOCAL_RANK", "0")))
+
+
+def init_process_group(backend: str | None = None, timeout_s: float = 120.0):
+    """Joins the job described by RANK / WORLD_SIZE / MASTER_ADDR / MASTER_PORT.
+
+    `backend` defaults to nccl when CUDA is available, else gloo.  Returns (rank, world, local_rank);
+    with WORLD_SIZE 1 no process group is created.
+    """
+    import datetime
+
+    import torch
+    import torch.distributed as dist
+
+    rank, world, local = env_rank()
+    if world == 1:
+        return rank, world, local
+    if backend is None:
+        backend = "nccl" if torch.cuda.is_available() else "gloo"
+    if backend == "nccl":
+        torch.cuda.set_device(local)
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    if not dist.is_initialized():
+        dist.init_process_group(backend=backend, rank=rank, world_size=world,
+                                timeout=datetime.timedelta(seconds=timeout_s))
+    return rank, world, local
+
+
+def replicate_from_rank0(tensor):
+    """Broadcast `tensor` (B) from rank 0 into every rank's own memory; returns it.  A single-rank
+    job returns the tensor untouched."""
+    import torch.distributed as dist
+
+    if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
+        dist.broadcast(tensor, src=0)
+    return tensor
+
+
+def sharded_gemm(compute, A_rows, B, C_rows):
+    """Runs `compute(A_rows, B, C_rows)` on this rank's block; a no-op for an empty block.
+
+    `compute` is the device call (for int8: a closure over `_native.i8gemm` with VT_DEVICE).  The
+    function exists so that the host-side sharding logic is one code path whether the call below it
+    is the CUDA kernel or, in CPU tests, a checker.
+    """
+    if A_rows.shape[0] == 0:
+        return C_rows
+    compute(A_rows, B, C_rows)
+    return C_rows

@@ -529,7 +529,7 @@ def _plain_gemm_raster(tiles, m, n, k):
     if order == sorted(order):
         return "baseline"
     if order == sorted(order, key=lambda ij: (ij[1], ij[0])):
-        return "reuse_b"
+        return "reuse_b"   # also the order of the batched lowering; the caller tells them apart
     return "batched"
 
 
@@ -543,6 +543,8 @@ def _execute(plan, A, B, tiles, raster_hint=None, batch_rows=1):
     C = np.empty(m * n, dtype=np.int32)
     try:
         raster = _plain_gemm_raster(tiles, m, n, k) if raster_hint is None else raster_hint
+        if raster == "reuse_b" and batch_rows < m // DIM:
+            raster = "batched"   # column sweeps with fewer live row tiles than the matrix has
         if raster is not None:
             code = {"baseline": nv.VT_RASTER_BASELINE, "reuse_b": nv.VT_RASTER_REUSE_B,
                     "batched": nv.VT_RASTER_BATCHED}[raster]

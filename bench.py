@@ -43,7 +43,7 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustain
 
 # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the ncu captures
 # summarised under profiles/; None until a capture exists for the workload.
-NCU_TRAFFIC_BYTES = {}
+NCU_TRAFFIC_BYTES = {"i8_8192": 572.3e6}
 
 WORKLOADS = {
     # name: (kind, M, N, K, batch)
@@ -327,7 +327,7 @@ def run_gpu_arm(args, kind, M, N, K, batch, metric, unit):
 
     if args.no_e2e:
         e2e_steps = 0
-        e2e_s = float("nan")
+        e2e_s = None
     else:
         e2e_step()
         barrier()
@@ -336,11 +336,11 @@ def run_gpu_arm(args, kind, M, N, K, batch, metric, unit):
             e2e_step()
         barrier()
         e2e_s = (time.perf_counter() - t0) / e2e_steps
-    if world > 1:
+    if world > 1 and e2e_s:
         t = torch.tensor([e2e_s], device="cuda", dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_s = float(t.item())
-    e2e_value = ops_per_step_job / e2e_s / 1e12
+    e2e_value = ops_per_step_job / e2e_s / 1e12 if e2e_s else None
     e2e_ok = bool(torch.equal(hC[:64].cuda(), C[:64])) if kind != "f32" and not args.no_e2e else None
     h2d = (rows * K + K * N) * elem_in
     d2h = rows * N * elem_out
@@ -385,7 +385,7 @@ def run_gpu_arm(args, kind, M, N, K, batch, metric, unit):
                          % ((rows * K * elem_in + K * N * elem_in + rows * N * elem_out) / 2**20)},
         "clocks": clocks,
         "e2e": {"value": e2e_value, "unit": unit, "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
-                "steps": e2e_steps, "ms_per_step": e2e_s * 1e3, "matches_device_run": e2e_ok},
+                "steps": e2e_steps, "ms_per_step": e2e_s * 1e3 if e2e_s else None, "matches_device_run": e2e_ok},
         "gpu_launches": int(launches),
         "roofline": roof,
     }

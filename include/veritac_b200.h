@@ -100,6 +100,27 @@ int vt_i8_tile_program(int dev, const int8_t* A, int64_t a_elems, const int8_t* 
 int vt_sgemm(int dev, const float* A, const float* B, float* C, int64_t M, int64_t N, int64_t K, int variant,
              int where, void* stream);
 
+/* The skinny fp32 GEMM (M <= 16, N % 4 == 0, device pointers only) for hosts that must not let this
+ * library allocate: it calls no cudaMalloc / cudaFree and no allocating library routine.  It has no
+ * counterpart in the reference; it exists for embedders whose own pool (a framework's caching
+ * allocator, a serving runtime with a fixed budget) already owns the GPU's memory, where a
+ * library-side cudaMalloc can fail or stall a request by synchronising the device.  The K-split
+ * partial tiles that vt_sgemm keeps in cudaMalloc'd workspace live here in one fixed
+ * VT_SKINNY_STATIC_SCRATCH_BYTES array inside the library image (held by every GPU that loads the
+ * library, until exit).  Shapes whose partial tiles need more are refused with VT_ERR_UNSUPPORTED and
+ * a message giving both sizes; vt_sgemm serves those.
+ *   - The first call on a device looks up the array's device address (with that device current);
+ *     make that first call before starting any stream capture.
+ *   - All calls share the one array: two calls whose kernels can overlap on the GPU (different
+ *     streams, no ordering between them) race on it.  Calls on one stream are safe.  Nothing in
+ *     the array has to be cleared between calls.
+ *   - `stream` is used as given (a cudaStream_t; NULL is the CUDA default stream).  The call only
+ *     enqueues; synchronise the stream yourself.  A, B, C are device pointers on `dev`, B and C
+ *     16-byte aligned.  Results are bit-identical to vt_sgemm's VT_SGEMM_SKINNY. */
+#define VT_SKINNY_STATIC_SCRATCH_BYTES (6u << 20)
+int vt_sgemm_skinny_static_scratch(int dev, const float* A, const float* B, float* C, int64_t M, int64_t N,
+                                   int64_t K, void* stream);
+
 /* Waits for `stream` (NULL = the library's stream) on `dev` and returns VT_ERR_DEVICE_WAIT if any
  * kernel since the last check gave up on a bounded wait, VT_ERR_CUDA on an asynchronous CUDA error. */
 int vt_sync(int dev, void* stream);

@@ -48,6 +48,8 @@ SIGNATURES = {
     "vt_i8_tile_program": (c_int, [c_int, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int64, c_int64,
                                    c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p]),
     "vt_sgemm": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_int, c_void_p]),
+    "vt_sgemm_skinny_static_scratch": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,
+                                               c_void_p]),
     "vt_sync": (c_int, [c_int, c_void_p]),
     "vt_host_alloc": (c_void_p, [c_size_t]),
     "vt_host_free": (c_int, [c_void_p]),
@@ -143,6 +145,14 @@ def i8_tile_program(A, a_elems, B, b_elems, C, c_elems, lda, ldb, ldc, c_off, te
 def sgemm(A, B, C, M: int, N: int, K: int, *, dev: int = 0, variant: int = VT_SGEMM_AUTO, where: int = VT_HOST,
           stream: int = 0) -> None:
     check(lib().vt_sgemm(dev, _ptr(A), _ptr(B), _ptr(C), M, N, K, variant, where, stream))
+
+
+SKINNY_STATIC_SCRATCH_BYTES = 6 << 20
+
+
+def sgemm_skinny_static_scratch(A, B, C, M: int, N: int, K: int, *, dev: int = 0, stream: int = 0) -> None:
+    """Skinny fp32 GEMM on device pointers that allocates nothing (see the header for the limits)."""
+    check(lib().vt_sgemm_skinny_static_scratch(dev, _ptr(A), _ptr(B), _ptr(C), M, N, K, stream))
 
 
 def sync(dev: int = 0, stream: int = 0) -> None:

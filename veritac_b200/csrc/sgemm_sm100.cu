@@ -12,6 +12,8 @@
 //       keep 16x4 accumulators per thread, and fold through shared memory.  With a K split the
 //       per-split partial tiles go to scratch memory and a second kernel sums them in split order
 //       (deterministic, no atomics).
+#include <mutex>
+
 #include "runtime.h"
 
 namespace vt {
@@ -329,4 +331,71 @@ int launch_sgemm(DeviceCtx* c, const float* A, const float* B, float* C, int64_t
   return fail(VT_ERR_UNSUPPORTED, "sgemm variant %d is not built", variant);
 }
 
+// ---------------------------------------------------------------------------------------------
+// Skinny fp32 GEMM without any allocation.
+//
+// Some hosts of this library cannot let it allocate device memory: a serving process that has
+// handed the whole of HBM to its own pool (PyTorch's caching allocator, an inference runtime with a
+// fixed budget) leaves nothing for a library-side cudaMalloc, and where memory is left, cudaMalloc
+// still synchronises the device in the middle of a request.  vt_sgemm normally takes the K-split
+// partial tiles of the skinny kernel from a grow-only cudaMalloc'd workspace; this entry point takes
+// them from the fixed array below instead, which every GPU that loads the library holds until the
+// process exits.
+// ---------------------------------------------------------------------------------------------
+namespace {
+
+constexpr size_t kStaticScratchFloats = VT_SKINNY_STATIC_SCRATCH_BYTES / sizeof(float);
+static __device__ __align__(256) float g_skinny_static_scratch[kStaticScratchFloats];
+
+struct StaticScratchSlot {
+  bool ready = false;
+  float* ptr = nullptr;   // device address of g_skinny_static_scratch on this device
+  int sm_count = 0;
+};
+constexpr int kStaticMaxDevices = 16;
+StaticScratchSlot g_static_slot[kStaticMaxDevices];
+std::mutex g_static_mu;
+
+}  // namespace
+
 }  // namespace vt
+
+extern "C" int vt_sgemm_skinny_static_scratch(int dev, const float* A, const float* B, float* C, int64_t M, int64_t N,
+                                              int64_t K, void* stream) {
+  using namespace vt;
+  clear_error_text();
+  if (!A || !B || !C) return fail(VT_ERR_INVALID, "null operand");
+  if (dev < 0 || dev >= kStaticMaxDevices) return fail(VT_ERR_INVALID, "device ordinal %d out of range", dev);
+  if (M < 1 || N < 1 || K < 1) return fail(VT_ERR_INVALID, "dimensions must be positive");
+  if (M > SK_M || N % 4 != 0) return fail(VT_ERR_UNSUPPORTED, "skinny kernel needs M <= 16 and N %% 4 == 0");
+  if (N > 0x7fffffffLL || K > 0x7fffffffLL) return fail(VT_ERR_INVALID, "dimension overflows int");
+  if ((reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(C)) & 15)
+    return fail(VT_ERR_INVALID, "B and C must be 16-byte aligned");
+  VT_CUDA(cudaSetDevice(dev));
+  StaticScratchSlot* slot = &g_static_slot[dev];
+  if (!slot->ready) {
+    // Set-up, once per device, with that device current.  In host code the array's name is only
+    // a stand-in for the symbol; the address kernels can use comes from the runtime.
+    std::lock_guard<std::mutex> lock(g_static_mu);
+    if (!slot->ready) {
+      float* p = nullptr;
+      VT_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_skinny_static_scratch));
+      int sms = 0;
+      VT_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+      if (!p || sms < 1) return fail(VT_ERR_CUDA, "static scratch set-up returned no address");
+      slot->ptr = p;
+      slot->sm_count = sms;
+      slot->ready = true;
+    }
+  }
+  int ksplit = 1;
+  const size_t need = sgemm_skinny_partials_bytes(M, N, K, slot->sm_count, &ksplit);
+  if (need > VT_SKINNY_STATIC_SCRATCH_BYTES)
+    return fail(VT_ERR_UNSUPPORTED,
+                "%lldx%lldx%lld needs %zu bytes of K-split scratch; the static array holds %zu (use vt_sgemm)",
+                (long long)M, (long long)N, (long long)K, need, size_t(VT_SKINNY_STATIC_SCRATCH_BYTES));
+  // Every partial cell the reduce pass reads is written by the first pass of this same call, so
+  // the previous call's leftovers in the array need no clearing.
+  return launch_sgemm_skinny(nullptr, A, B, C, ksplit > 1 ? slot->ptr : nullptr, M, N, K, ksplit,
+                             static_cast<cudaStream_t>(stream));
+}

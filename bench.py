@@ -50,6 +50,7 @@ WORKLOADS = {
     "i8_8192": ("i8", 8192, 8192, 8192, 1),
     "i8_64": ("i8", 64, 64, 64, 1),
     "i8_batched": ("i8b", 1024, 4096, 4096, 256),
+    "i8_batched_32": ("i8b", 1024, 4096, 4096, 32),      # one GPU's share of config 4 on 8 GPUs
     "sgemm_8192": ("f32", 8192, 8192, 8192, 1),
     "sgemm_256": ("f32", 256, 256, 256, 1),
     "sgemm_skinny": ("f32", 16, 8192, 8192, 1),
@@ -269,7 +270,7 @@ def run_gpu_arm(args, kind, M, N, K, batch, metric, unit):
         elif kind == "i8b":
             nv.i8gemm_shared_b(A, B, C, rows // M, M, N, K, dev=dev, acc_rows=16, where=nv.VT_DEVICE, stream=st)
         else:
-            nv.i8gemm(A, B, C, rows, N, K, dev=dev, where=nv.VT_DEVICE, stream=st)
+            nv.i8gemm(A, B, C, rows, N, K, dev=dev, variant=args.i8_variant, where=nv.VT_DEVICE, stream=st)
 
     def barrier():
         if world > 1:
@@ -411,6 +412,7 @@ def main() -> int:
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default="i8_8192")
     ap.add_argument("--scaling", choices=("weak", "strong"), default="weak",
                     help="weak: every GPU gets the full shape; strong: the shape's rows are split over the GPUs")
+    ap.add_argument("--i8-variant", type=int, default=0, help="VT_I8_* kernel variant (0 = the library's choice)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
     args = ap.parse_args()

@@ -53,8 +53,21 @@ enum {
   VT_RASTER_AUTO = 3      /* grouped order tuned for L2 reuse on B200                               */
 };
 
-/* int8 kernel variants (VT_I8_AUTO picks the fastest verified one). */
-enum { VT_I8_AUTO = 0, VT_I8_B_AS_STORED = 1, VT_I8_B_RELAYOUT = 2, VT_I8_CTA_PAIR = 3 };
+/* int8 kernel variants.  VT_I8_AUTO picks the fastest verified one; the others exist so that each
+ * design choice can be measured against its alternative:
+ *   B_AS_STORED            one CTA per 128x256 tile, B read as stored, C written by TMA stores
+ *   B_RELAYOUT             same, after re-laying B out as N x K on the device
+ *   CTA_PAIR               two CTAs per 256x256 tile (tcgen05 cta_group::2), C written by TMA stores
+ *   DIRECT_STORE           B_AS_STORED with plain 16-byte global stores for C
+ *   CTA_PAIR_DIRECT_STORE  CTA_PAIR with plain 16-byte global stores for C */
+enum {
+  VT_I8_AUTO = 0,
+  VT_I8_B_AS_STORED = 1,
+  VT_I8_B_RELAYOUT = 2,
+  VT_I8_CTA_PAIR = 3,
+  VT_I8_DIRECT_STORE = 4,
+  VT_I8_CTA_PAIR_DIRECT_STORE = 5
+};
 
 /* fp32 kernel variants. */
 enum { VT_SGEMM_AUTO = 0, VT_SGEMM_TILE128 = 1, VT_SGEMM_TILE64 = 2, VT_SGEMM_SKINNY = 3 };

@@ -39,7 +39,11 @@ void raster_for(int raster, int batch_rows, int64_t M, int* mode, int* group) {
   (void)M;
 }
 
-int resolve_i8_variant(int variant) { return variant == VT_I8_AUTO ? VT_I8_B_AS_STORED : variant; }
+// Two CTAs per tile need at least 256 rows to have work for both; below that one CTA per tile.
+int resolve_i8_variant(int variant, int64_t M) {
+  if (variant != VT_I8_AUTO) return variant;
+  return M > 128 ? VT_I8_CTA_PAIR : VT_I8_B_AS_STORED;
+}
 
 cudaStream_t pick_stream(DeviceCtx* c, void* stream) { return stream ? static_cast<cudaStream_t>(stream) : c->stream; }
 
@@ -103,7 +107,7 @@ int vt_i8gemm(int dev, const int8_t* A, const int8_t* B, int32_t* C, int64_t M, 
   if (!c) return VT_ERR_CUDA;
   int mode, group;
   raster_for(raster, batch_rows, M, &mode, &group);
-  variant = resolve_i8_variant(variant);
+  variant = resolve_i8_variant(variant, M);
   if (where == VT_HOST) return i8gemm_from_host(c, A, B, C, M, N, K, mode, group, variant);
   return launch_i8gemm(c, A, B, C, M, N, K, mode, group, variant, pick_stream(c, stream));
 }

@@ -36,6 +36,11 @@ constexpr int B_BOX_BYTES = 128 * BK;               // one 128-column box of the
 constexpr int NUM_THREADS = 192;
 constexpr int TMEM_COLS = 512;                      // two 256-column int32 accumulators
 
+// Epilogue staging: each epilogue warp owns two 32-row x 32-column int32 buffers (4 KiB each,
+// 128-byte rows in the 128-byte swizzle the C tensor map expects).
+constexpr int EPI_BUF_BYTES = 32 * 32 * 4;
+constexpr int EPI_STAGING_BYTES = 4 * 2 * EPI_BUF_BYTES;   // 32 KiB
+
 struct TileRaster {
   int mt, nt;  // tile counts along M and N
   int mode;    // 0 row-major, 1 column-major, 2 grouped
@@ -51,7 +56,7 @@ struct PipeState {
   int abort_word;
 };
 
-constexpr size_t SMEM_BYTES = 1024 + size_t(STAGES) * STAGE_BYTES + sizeof(PipeState);
+constexpr size_t SMEM_BYTES = 1024 + size_t(STAGES) * STAGE_BYTES + EPI_STAGING_BYTES + sizeof(PipeState);
 
 __device__ __forceinline__ void tile_coords(const TileRaster& rs, int t, int& mi, int& ni) {
   if (rs.mode == 0) {
@@ -70,15 +75,59 @@ __device__ __forceinline__ void tile_coords(const TileRaster& rs, int t, int& mi
   }
 }
 
+// Moves one warp's 32 rows x 256 columns of an accumulator from TMEM to C.
+//   kTmaStore: TMEM -> registers -> swizzled shared memory -> cp.async.bulk.tensor store, so C is
+//              written in whole 128-byte lines and rows/columns outside C are clipped by the TMA unit;
+//   otherwise: TMEM -> registers -> predicated 16-byte global stores.
+// Returns once the accumulator has been read (the stores may still be in flight).
+template <bool kTmaStore>
+__device__ __forceinline__ void epilogue_warp_tile(uint32_t t_row, const CUtensorMap* tmC, uint8_t* staging,
+                                                   int32_t* __restrict__ C, int M, int N, int row0, int n0,
+                                                   int lane) {
+  const int row = row0 + lane;
+#pragma unroll 1
+  for (int c = 0; c < BN / 32; ++c) {
+    uint32_t r[32];
+    tmem_ld_32x32b_x32(t_row + uint32_t(c * 32), r);
+    tmem_ld_wait();
+    if constexpr (kTmaStore) {
+      uint8_t* buf = staging + (c & 1) * EPI_BUF_BYTES;
+      if (lane == 0) tma_store_wait_read<1>();   // the store that last read this buffer is done with it
+      __syncwarp();
+      const uint32_t base = smem_u32(buf) + uint32_t(lane) * 128u;
+#pragma unroll
+      for (int v = 0; v < 8; ++v)
+        st_shared_v4(base + (uint32_t(v ^ (lane & 7)) << 4), r[4 * v], r[4 * v + 1], r[4 * v + 2], r[4 * v + 3]);
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        if (row0 < M && n0 + c * 32 < N) tma_store_2d(tmC, buf, n0 + c * 32, row0);
+        tma_store_commit();
+      }
+    } else {
+      if (row < M) {
+        int32_t* crow = C + size_t(row) * size_t(N) + n0;
+#pragma unroll
+        for (int v = 0; v < 8; ++v) {
+          const int col = n0 + c * 32 + v * 4;
+          if (col < N) st_global_v4(crow + c * 32 + v * 4, r[4 * v], r[4 * v + 1], r[4 * v + 2], r[4 * v + 3]);
+        }
+      }
+    }
+  }
+}
+
 // kBT == false: tmB describes B as stored (inner = N, outer = K).
 // kBT == true : tmB describes B re-laid out as N x K (inner = K, outer = N).
-template <bool kBT>
+template <bool kBT, bool kTmaStore>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 i8gemm_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                   int32_t* __restrict__ C, int M, int N, int K, TileRaster rs, int* __restrict__ status) {
+                   const __grid_constant__ CUtensorMap tmC, int32_t* __restrict__ C, int M, int N, int K,
+                   TileRaster rs, int* __restrict__ status) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  PipeState* ps = reinterpret_cast<PipeState*>(tiles + size_t(STAGES) * STAGE_BYTES);
+  uint8_t* staging = tiles + size_t(STAGES) * STAGE_BYTES;
+  PipeState* ps = reinterpret_cast<PipeState*>(staging + EPI_STAGING_BYTES);
   volatile int* abort_word = &ps->abort_word;
 
   const int warp = threadIdx.x >> 5;
@@ -100,6 +149,7 @@ i8gemm_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
     fence_proxy_async_smem();
     tma_prefetch_desc(&tmA);
     tma_prefetch_desc(&tmB);
+    if (kTmaStore) tma_prefetch_desc(&tmC);
   }
   if (warp == 1) {
     tmem_alloc<1>(&ps->tmem_base, TMEM_COLS);
@@ -220,34 +270,207 @@ i8gemm_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
       const bool ready = mbar_wait(&ps->tmem_full[acc], acc_phase, abort_word, KSTAT_WAIT_EXPIRED_EPILOGUE);
       if (!__all_sync(0xffffffffu, ready)) break;
       tc_fence_after_sync();
-      const int row = m0 + q * 32 + lane;
-      int32_t* crow = C + size_t(row) * size_t(N) + n0;
       const uint32_t t_row = tmem_base + (uint32_t(q * 32) << 16) + uint32_t(acc * BN);
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32b_x32(t_row + uint32_t(c * 32), r);
-        tmem_ld_wait();
-        if (row < M) {
-#pragma unroll
-          for (int v = 0; v < 8; ++v) {
-            const int col = n0 + c * 32 + v * 4;
-            if (col < N) st_global_v4(crow + c * 32 + v * 4, r[4 * v], r[4 * v + 1], r[4 * v + 2], r[4 * v + 3]);
-          }
-        }
-      }
+      epilogue_warp_tile<kTmaStore>(t_row, &tmC, staging + q * 2 * EPI_BUF_BYTES, C, M, N, m0 + q * 32, n0, lane);
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&ps->tmem_empty[acc]);
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1;
     }
+    if (kTmaStore && lane == 0) tma_store_wait_all<0>();   // C fully written before shared memory goes away
     __syncwarp();
   }
 
   tc_fence_before_sync();
   __syncthreads();
   if (warp == 1) tmem_dealloc<1>(tmem_base, TMEM_COLS);
+  if (threadIdx.x == 0 && ps->abort_word != 0) atomicCAS(status, 0, ps->abort_word);
+}
+
+// ---------------------------------------------------------------------------------------------
+// CTA-pair form (tcgen05 cta_group::2): two CTAs of a 2-cluster, on the two SMs of one TPC, own one
+// 256 x 256 output tile.  CTA r holds rows [128r, 128r+128) of the A tile and columns
+// [128r, 128r+128) of the B slab in its own shared memory (32 KiB per stage instead of 48, so six
+// stages fit) and its own 128 x 256 half of the accumulator in its own TMEM; the MMA instruction,
+// issued by the even CTA only, reads both halves of both operands.  Per SM and per K block this
+// moves a third less operand data through the L2 -> SM path than the single-CTA form.
+//   * both producers signal the even CTA's "full" barrier (it expects both CTAs' bytes);
+//   * tcgen05.commit multicasts the "empty" and "accumulator full" arrivals to both CTAs;
+//   * both CTAs' epilogue warps arrive on the even CTA's "accumulator empty" barrier (8 arrivals).
+// ---------------------------------------------------------------------------------------------
+constexpr int P_STAGES = 5;   // 5 x 32 KiB operands + 32 KiB epilogue staging
+constexpr int P_A_BYTES = 128 * BK;                 // this CTA's 128 rows of A
+constexpr int P_B_BYTES = 128 * BK;                 // this CTA's 128 columns of B (one TMA box)
+constexpr int P_STAGE_BYTES = P_A_BYTES + P_B_BYTES;
+
+struct PairPipeState {
+  uint64_t full[P_STAGES];
+  uint64_t empty[P_STAGES];
+  uint64_t tmem_full[2];
+  uint64_t tmem_empty[2];
+  uint32_t tmem_base;
+  int abort_word;
+};
+
+constexpr size_t P_SMEM_BYTES = 1024 + size_t(P_STAGES) * P_STAGE_BYTES + EPI_STAGING_BYTES + sizeof(PairPipeState);
+
+template <bool kTmaStore>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
+i8gemm_umma_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                        const __grid_constant__ CUtensorMap tmC, int32_t* __restrict__ C, int M, int N, int K,
+                        TileRaster rs, int* __restrict__ status) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* staging = tiles + size_t(P_STAGES) * P_STAGE_BYTES;
+  PairPipeState* ps = reinterpret_cast<PairPipeState*>(staging + EPI_STAGING_BYTES);
+  volatile int* abort_word = &ps->abort_word;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_cta_rank();          // 0 = even CTA (issues the MMAs), 1 = its peer
+  const int pair = blockIdx.x >> 1;
+  const int num_pairs = gridDim.x >> 1;
+  const int num_tiles = rs.mt * rs.nt;               // 256 x 256 tiles
+  const int kblocks = (K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < P_STAGES; ++s) {
+      mbar_init(&ps->full[s], 1);                    // the even CTA's producer arrives (with both CTAs' bytes)
+      mbar_init(&ps->empty[s], 1);                   // one multicast commit
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&ps->tmem_full[b], 1);               // one multicast commit
+      mbar_init(&ps->tmem_empty[b], 8);              // 4 epilogue warps of each CTA
+    }
+    ps->abort_word = 0;
+    fence_mbar_init();
+    fence_proxy_async_smem();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+    if (kTmaStore) tma_prefetch_desc(&tmC);
+  }
+  if (warp == 1) {
+    tmem_alloc<2>(&ps->tmem_base, TMEM_COLS);
+    tmem_relinquish<2>();
+  }
+  tc_fence_before_sync();
+  cluster_sync_all();                                // peer barriers exist before anything signals them
+  tc_fence_after_sync();
+  const uint32_t tmem_base = ps->tmem_base;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer (both CTAs) ------------------------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      uint32_t filled = 0, fill_parity = 0;
+      bool ok = true;
+      for (int t = pair; t < num_tiles && ok; t += num_pairs) {
+        int mi, ni;
+        tile_coords(rs, t, mi, ni);
+        const int m0 = mi * 256 + int(rank) * 128, n0 = ni * 256 + int(rank) * 128;
+        for (int kb = 0; kb < kblocks; ++kb) {
+          if (!mbar_wait(&ps->empty[stage], phase ^ 1, abort_word, KSTAT_WAIT_EXPIRED_PRODUCER)) {
+            ok = false;
+            break;
+          }
+          uint8_t* a_s = tiles + size_t(stage) * P_STAGE_BYTES;
+          uint8_t* b_s = a_s + P_A_BYTES;
+          if (rank == 0) mbar_arrive_expect_tx(&ps->full[stage], 2 * P_STAGE_BYTES);
+          const uint32_t full_even = mapa_shared(smem_u32(&ps->full[stage]), 0);
+          tma_load_2d_pair(a_s, &tmA, full_even, kb * BK, m0);
+          tma_load_2d_pair(b_s, &tmB, full_even, n0, kb * BK);
+          filled |= 1u << stage;
+          fill_parity = (fill_parity & ~(1u << stage)) | (phase << stage);
+          if (++stage == P_STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+      if (ok) {
+        for (int s = 0; s < P_STAGES; ++s) {
+          if (!mbar_wait(&ps->empty[stage], phase ^ 1, abort_word, KSTAT_WAIT_EXPIRED_PRODUCER)) break;
+          if (++stage == P_STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+      (void)filled;
+      (void)fill_parity;
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer (even CTA only) ------------------------------
+    if (lane == 0 && rank == 0) {
+      constexpr uint32_t idesc = umma_instr_desc(UMMA_D_S32, UMMA_AB_S8, false, true, 256, 256);
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int t = pair; t < num_tiles && ok; t += num_pairs) {
+        if (!mbar_wait<true>(&ps->tmem_empty[acc], acc_phase ^ 1, abort_word, KSTAT_WAIT_EXPIRED_MMA)) break;
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + uint32_t(acc * BN);
+        for (int kb = 0; kb < kblocks; ++kb) {
+          if (!mbar_wait<true>(&ps->full[stage], phase, abort_word, KSTAT_WAIT_EXPIRED_MMA)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          const uint32_t a_addr = smem_u32(tiles + size_t(stage) * P_STAGE_BYTES);
+          const uint32_t b_addr = a_addr + P_A_BYTES;
+#pragma unroll
+          for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+            const uint64_t a_desc = umma_smem_desc_sw128(a_addr + kk * UMMA_K, 16, 1024);
+            const uint64_t b_desc = umma_smem_desc_sw128(b_addr + kk * UMMA_K * 128, P_B_BYTES, 1024);
+            umma_i8<2>(d_tmem, a_desc, b_desc, idesc, uint32_t((kb | kk) != 0));
+          }
+          umma_commit_pair(&ps->empty[stage], 3);
+          if (++stage == P_STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (!ok) break;
+        umma_commit_pair(&ps->tmem_full[acc], 3);
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1;
+      }
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------ epilogue (both CTAs) ------------------------------
+    const int q = warp & 3;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    for (int t = pair; t < num_tiles; t += num_pairs) {
+      int mi, ni;
+      tile_coords(rs, t, mi, ni);
+      const int m0 = mi * 256 + int(rank) * 128, n0 = ni * 256;
+      const bool ready = mbar_wait<true>(&ps->tmem_full[acc], acc_phase, abort_word, KSTAT_WAIT_EXPIRED_EPILOGUE);
+      if (!__all_sync(0xffffffffu, ready)) break;
+      tc_fence_after_sync();
+      const uint32_t t_row = tmem_base + (uint32_t(q * 32) << 16) + uint32_t(acc * BN);
+      epilogue_warp_tile<kTmaStore>(t_row, &tmC, staging + q * 2 * EPI_BUF_BYTES, C, M, N, m0 + q * 32, n0, lane);
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_remote(&ps->tmem_empty[acc], 0);
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1;
+    }
+    if (kTmaStore && lane == 0) tma_store_wait_all<0>();
+    __syncwarp();
+  }
+
+  // Neither CTA may free TMEM or leave while its peer's MMAs, commits or remote arrivals can still
+  // touch it.
+  tc_fence_before_sync();
+  cluster_sync_all();
+  if (warp == 1) tmem_dealloc<2>(tmem_base, TMEM_COLS);
   if (threadIdx.x == 0 && ps->abort_word != 0) atomicCAS(status, 0, ps->abort_word);
 }
 
@@ -269,57 +492,76 @@ __global__ void __launch_bounds__(256) i8_transpose_kernel(const int8_t* __restr
   }
 }
 
+template <typename KernelT>
+int launch_with_smem(DeviceCtx* c, uint32_t attr_bit, KernelT kernel, size_t smem, int grid, cudaStream_t s,
+                     const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC, int32_t* C, int M,
+                     int N, int K, const TileRaster& rs) {
+  if (!(c->func_attr_mask & attr_bit)) {
+    VT_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+    c->func_attr_mask |= attr_bit;
+  }
+  kernel<<<grid, NUM_THREADS, smem, s>>>(tmA, tmB, tmC, C, M, N, K, rs, c->status);
+  count_launch();
+  VT_CUDA(cudaGetLastError());
+  return VT_OK;
+}
+
 }  // namespace
 
 int launch_i8gemm(DeviceCtx* c, const int8_t* A, const int8_t* B, int32_t* C, int64_t M, int64_t N, int64_t K,
                   int raster_mode, int group, int variant, cudaStream_t s) {
-  if (variant != VT_I8_B_AS_STORED && variant != VT_I8_B_RELAYOUT)
+  if (variant < VT_I8_B_AS_STORED || variant > VT_I8_CTA_PAIR_DIRECT_STORE)
     return fail(VT_ERR_UNSUPPORTED, "i8gemm variant %d is not built", variant);
   if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(C)) & 15)
     return fail(VT_ERR_INVALID, "i8gemm operands must be 16-byte aligned");
+  if (raster_mode < 0 || raster_mode > 2) return fail(VT_ERR_INVALID, "raster mode %d out of range", raster_mode);
+  const bool pair = variant == VT_I8_CTA_PAIR || variant == VT_I8_CTA_PAIR_DIRECT_STORE;
+  const int tile_m = pair ? 256 : BM;
 
   TileRaster rs;
-  rs.mt = int((M + BM - 1) / BM);
+  rs.mt = int((M + tile_m - 1) / tile_m);
   rs.nt = int((N + BN - 1) / BN);
   rs.mode = raster_mode;
-  rs.group = group < 1 ? 1 : (group > rs.mt ? rs.mt : group);
-  if (rs.mode < 0 || rs.mode > 2) return fail(VT_ERR_INVALID, "raster mode %d out of range", raster_mode);
+  const int g = pair ? (group + 1) / 2 : group;   // `group` counts 128-row tile-rows
+  rs.group = g < 1 ? 1 : (g > rs.mt ? rs.mt : g);
   const long long tiles = 1LL * rs.mt * rs.nt;
   if (tiles > 0x7fffffffLL) return fail(VT_ERR_INVALID, "tile count overflows int");
 
-  CUtensorMap tmA, tmB;
-  int rc = encode_tmap_2d(&tmA, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, A, uint64_t(K), uint64_t(M), uint64_t(K), BK, BM);
+  CUtensorMap tmA, tmB, tmC;
+  int rc = encode_tmap_2d(&tmA, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, A, uint64_t(K), uint64_t(M), uint64_t(K), BK, 128);
   if (rc) return rc;
+  rc = encode_tmap_2d(&tmC, CU_TENSOR_MAP_DATA_TYPE_INT32, 4, C, uint64_t(N), uint64_t(M), uint64_t(N) * 4, 32, 32);
+  if (rc) return rc;
+  const int iM = int(M), iN = int(N), iK = int(K);
 
-  const int grid = int(tiles < c->sm_count ? tiles : c->sm_count);
-  if (variant == VT_I8_B_AS_STORED) {
-    rc = encode_tmap_2d(&tmB, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, B, uint64_t(N), uint64_t(K), uint64_t(N), 128, BK);
-    if (rc) return rc;
-    if (!(c->func_attr_mask & 1u)) {
-      VT_CUDA(cudaFuncSetAttribute(i8gemm_umma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                   int(SMEM_BYTES)));
-      c->func_attr_mask |= 1u;
-    }
-    i8gemm_umma_kernel<false><<<grid, NUM_THREADS, SMEM_BYTES, s>>>(tmA, tmB, C, int(M), int(N), int(K), rs, c->status);
-    count_launch();
-  } else {
+  if (variant == VT_I8_B_RELAYOUT) {
     int8_t* Bt = static_cast<int8_t*>(ctx_workspace(c, 3, size_t(N) * size_t(K)));
     if (!Bt) return VT_ERR_CUDA;
     dim3 tg(unsigned((N + 63) / 64), unsigned((K + 63) / 64));
-    i8_transpose_kernel<<<tg, 256, 0, s>>>(B, Bt, int(K), int(N));
+    i8_transpose_kernel<<<tg, 256, 0, s>>>(B, Bt, iK, iN);
     count_launch();
     rc = encode_tmap_2d(&tmB, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, Bt, uint64_t(K), uint64_t(N), uint64_t(K), BK, BN);
     if (rc) return rc;
-    if (!(c->func_attr_mask & 2u)) {
-      VT_CUDA(cudaFuncSetAttribute(i8gemm_umma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                   int(SMEM_BYTES)));
-      c->func_attr_mask |= 2u;
-    }
-    i8gemm_umma_kernel<true><<<grid, NUM_THREADS, SMEM_BYTES, s>>>(tmA, tmB, C, int(M), int(N), int(K), rs, c->status);
-    count_launch();
+    const int grid = int(tiles < c->sm_count ? tiles : c->sm_count);
+    return launch_with_smem(c, 2u, i8gemm_umma_kernel<true, true>, SMEM_BYTES, grid, s, tmA, tmB, tmC, C, iM, iN, iK, rs);
   }
-  VT_CUDA(cudaGetLastError());
-  return VT_OK;
+  rc = encode_tmap_2d(&tmB, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, B, uint64_t(N), uint64_t(K), uint64_t(N), 128, BK);
+  if (rc) return rc;
+  if (!pair) {
+    const int grid = int(tiles < c->sm_count ? tiles : c->sm_count);
+    if (variant == VT_I8_B_AS_STORED)
+      return launch_with_smem(c, 1u, i8gemm_umma_kernel<false, true>, SMEM_BYTES, grid, s, tmA, tmB, tmC, C, iM, iN,
+                              iK, rs);
+    return launch_with_smem(c, 8u, i8gemm_umma_kernel<false, false>, SMEM_BYTES, grid, s, tmA, tmB, tmC, C, iM, iN,
+                            iK, rs);
+  }
+  const int max_pairs = c->sm_count / 2;
+  const int grid = 2 * int(tiles < max_pairs ? tiles : max_pairs);
+  if (variant == VT_I8_CTA_PAIR)
+    return launch_with_smem(c, 4u, i8gemm_umma_pair_kernel<true>, P_SMEM_BYTES, grid, s, tmA, tmB, tmC, C, iM, iN, iK,
+                            rs);
+  return launch_with_smem(c, 16u, i8gemm_umma_pair_kernel<false>, P_SMEM_BYTES, grid, s, tmA, tmB, tmC, C, iM, iN, iK,
+                          rs);
 }
 
 }  // namespace vt

@@ -146,6 +146,11 @@ class CpuArm:
         self.np = np
         self.kind, self.M, self.N, self.K = kind, M, N, K
         self.lib = _oracle_lib()
+        try:
+            allowed = len(os.sched_getaffinity(0))
+        except AttributeError:
+            allowed = os.cpu_count() or 1
+        self.lib.oracle_set_threads(ctypes.c_int(allowed))   # not whatever OMP_NUM_THREADS the launcher exported
         self.threads = int(self.lib.oracle_threads())
         rng = np.random.default_rng(seed)
         self.block = 16 if kind != "f32" else 32

@@ -63,6 +63,15 @@ void oracle_i8_lcg_inputs(int8_t *A, long na, int8_t *B, long nb, uint32_t seed)
   }
 }
 
+/* torchrun exports OMP_NUM_THREADS=1; the timed baseline asks for the cores it is allowed instead. */
+void oracle_set_threads(int n) {
+#ifdef _OPENMP
+  if (n > 0) omp_set_num_threads(n);
+#else
+  (void)n;
+#endif
+}
+
 int oracle_threads(void) {
 #ifdef _OPENMP
   return omp_get_max_threads();

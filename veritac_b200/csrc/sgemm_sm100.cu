@@ -8,8 +8,8 @@
 //       for step t+1 are issued into registers before the FFMAs of step t and stored (A transposed
 //       so the inner loop reads float4s along M) after them, one __syncthreads per step.
 //   sgemm_skinny_kernel       M <= 16 ("decode-like"): HBM-bound, B is streamed exactly once.  A CTA owns
-//       128 columns and a K range; its 8 warps take interleaved 8-row slices of each 64-row chunk,
-//       keep 16x4 accumulators per thread, and fold through shared memory.  With a K split the
+//       128 columns and a K range; B rows arrive through a 4-stage cp.async ring, its 4 warps take
+//       8-row slices of each 32-row stage, keep 16x4 accumulators per thread, and fold through shared memory.  With a K split the
 //       per-split partial tiles go to scratch memory and a second kernel sums them in split order
 //       (deterministic, no atomics).
 #include <mutex>
@@ -21,6 +21,18 @@ namespace {
 
 constexpr int SG_THREADS = 256;
 constexpr int SG_BK = 16;
+
+__device__ __forceinline__ void cp_async_16_zfill(float* smem_dst, const float* gmem_src, bool valid) {
+  const unsigned d = static_cast<unsigned>(__cvta_generic_to_shared(smem_dst));
+  const int bytes = valid ? 16 : 0;   // 0 source bytes => the 16 destination bytes are zero-filled
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(gmem_src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int kPending>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(kPending) : "memory");
+}
+
 
 template <int RM, int RN, bool kGuard>
 __global__ void __launch_bounds__(SG_THREADS, (RM * RN >= 4) ? 2 : 3)
@@ -162,74 +174,129 @@ sgemm_tile_kernel(const float* __restrict__ A, const float* __restrict__ B, floa
 }
 
 // ---------------------------------------------------------------------------------------------
-// Skinny: M <= 16, N % 4 == 0.  grid = (N/128 rounded up, ksplit).
+// Skinny: M <= 16, N % 4 == 0.  grid = (N/128 rounded up, ksplit), 128 threads.
+// B rows stream through a 4-stage cp.async ring (32 rows x 128 columns = 16 KiB per stage, three
+// CTAs per SM => ~150 KiB of B in flight per SM); the matching 32 x 16 slice of A goes through
+// registers one stage ahead and lands transposed ([k][m]) so the inner loop reads it as broadcast
+// float4s.  Each of the 4 warps takes 8 of a stage's 32 rows for all 128 columns (lane = 4 columns)
+// and keeps a 16 x 4 accumulator per thread; warps fold in a fixed order at the end.
 // ---------------------------------------------------------------------------------------------
 constexpr int SK_M = 16;
-constexpr int SK_COLS = 128;   // columns per CTA: 32 lanes x float4
-constexpr int SK_WARPS = 8;
-constexpr int SK_RW = 8;       // B rows each warp keeps in flight per step
-constexpr int SK_KC = SK_WARPS * SK_RW;  // K rows staged per step
+constexpr int SK_COLS = 128;
+constexpr int SK_WARPS = 4;
+constexpr int SK_THREADS = SK_WARPS * 32;
+constexpr int SK_KC = 32;                      // K rows per stage
+constexpr int SK_RW = SK_KC / SK_WARPS;        // rows of a stage each warp consumes
+constexpr int SK_STAGES = 4;
+constexpr int SK_B_STAGE = SK_KC * SK_COLS;    // floats
+constexpr int SK_A_STAGE = SK_KC * SK_M;       // floats
+constexpr size_t SK_SMEM_BYTES = size_t(SK_STAGES) * (SK_B_STAGE + SK_A_STAGE) * sizeof(float);
 
-__global__ void __launch_bounds__(SK_WARPS * 32, 2)
+__global__ void __launch_bounds__(SK_THREADS, 3)
 sgemm_skinny_kernel(const float* __restrict__ A, const float* __restrict__ B, float* __restrict__ out, int M, int N,
                     int K, int k_per_split) {
-  __shared__ __align__(16) float As[SK_KC][SK_M];          // A chunk, transposed: [k][m]
-  __shared__ __align__(16) float red[SK_M][SK_COLS];       // cross-warp fold
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n = blockIdx.x * SK_COLS + lane * 4;
-  const bool col_ok = n < N;  // N % 4 == 0: the float4 is entirely in or out
+  extern __shared__ __align__(16) float sk_smem[];
+  float* Bs = sk_smem;                                   // [stage][32][128]
+  float* As = sk_smem + SK_STAGES * SK_B_STAGE;          // [stage][32][16]
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int n0 = blockIdx.x * SK_COLS;
   const int kbeg = blockIdx.y * k_per_split;
   const int kend = min(K, kbeg + k_per_split);
+  const int nchunks = kend > kbeg ? (kend - kbeg + SK_KC - 1) / SK_KC : 0;
 
-  float acc[SK_M][4];
-#pragma unroll
-  for (int m = 0; m < SK_M; ++m)
-#pragma unroll
-    for (int j = 0; j < 4; ++j) acc[m][j] = 0.f;
+  const int a_m = tid >> 3, a_k = (tid & 7) * 4;         // this thread's 4 elements of a stage's A slice
 
-  for (int k0 = kbeg; k0 < kend; k0 += SK_KC) {
-    __syncthreads();  // previous chunk fully consumed
-    for (int i = threadIdx.x; i < SK_KC * SK_M; i += SK_WARPS * 32) {
-      const int m = i / SK_KC, kk = i - m * SK_KC;  // consecutive threads walk K: coalesced reads of A
-      const int k = k0 + kk;
-      As[kk][m] = (m < M && k < kend) ? A[size_t(m) * K + k] : 0.f;
+  auto issue_b = [&](int chunk) {                        // 8 x 16-byte copies per thread
+    float* dst = Bs + (chunk % SK_STAGES) * SK_B_STAGE;
+    const int k0 = kbeg + chunk * SK_KC;
+#pragma unroll
+    for (int i = 0; i < SK_KC * SK_COLS / 4 / SK_THREADS; ++i) {
+      const int idx = tid + SK_THREADS * i;
+      const int row = idx >> 5, c4 = (idx & 31) * 4;
+      const bool ok = (k0 + row < kend) && (n0 + c4 < N);
+      const float* src = ok ? B + size_t(k0 + row) * N + n0 + c4 : B;
+      cp_async_16_zfill(dst + row * SK_COLS + c4, src, ok);
     }
-    __syncthreads();
-    const int kw = k0 + warp * SK_RW;
-    float4 bv[SK_RW];
+  };
+  auto load_a = [&](int chunk, float (&v)[4]) {
+    const int k0 = kbeg + chunk * SK_KC + a_k;
 #pragma unroll
-    for (int r = 0; r < SK_RW; ++r) {
-      const int k = kw + r;
-      bv[r] = (col_ok && k < kend) ? __ldcs(reinterpret_cast<const float4*>(B + size_t(k) * N + n))
-                                   : make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int j = 0; j < 4; ++j) v[j] = (a_m < M && k0 + j < kend) ? __ldg(A + size_t(a_m) * K + k0 + j) : 0.f;
+  };
+  auto store_a = [&](int chunk, const float (&v)[4]) {
+    float* dst = As + (chunk % SK_STAGES) * SK_A_STAGE;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) dst[(a_k + j) * SK_M + a_m] = v[j];
+  };
+
+  float2 acc[SK_M / 2][4];   // acc[p][c] = rows (2p, 2p+1) of column c: one fma.rn.f32x2 updates both
+#pragma unroll
+  for (int m = 0; m < SK_M / 2; ++m)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[m][j] = make_float2(0.f, 0.f);
+
+  // Prologue: stages 0 .. SK_STAGES-2 (one commit per stage, empty ones included, so the
+  // wait below always counts the same number of groups).
+  for (int c = 0; c < SK_STAGES - 1; ++c) {
+    if (c < nchunks) {
+      issue_b(c);
+      float v[4];
+      load_a(c, v);
+      store_a(c, v);
     }
-#pragma unroll
-    for (int r = 0; r < SK_RW; ++r) {
-      const float* arow = &As[warp * SK_RW + r][0];
-#pragma unroll
-      for (int mq = 0; mq < SK_M / 4; ++mq) {
-        const float4 av = *reinterpret_cast<const float4*>(arow + 4 * mq);
-        const float am[4] = {av.x, av.y, av.z, av.w};
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          acc[4 * mq + e][0] = fmaf(am[e], bv[r].x, acc[4 * mq + e][0]);
-          acc[4 * mq + e][1] = fmaf(am[e], bv[r].y, acc[4 * mq + e][1]);
-          acc[4 * mq + e][2] = fmaf(am[e], bv[r].z, acc[4 * mq + e][2]);
-          acc[4 * mq + e][3] = fmaf(am[e], bv[r].w, acc[4 * mq + e][3]);
-        }
-      }
-    }
+    cp_async_commit();
   }
 
-  // Fold the 8 warps' partial tiles in warp order (fixed order => reproducible bits).
+  for (int it = 0; it < nchunks; ++it) {
+    cp_async_wait<SK_STAGES - 2>();   // chunk `it` has landed (for this thread's copies)
+    __syncthreads();                  // ... and for everyone's; everyone is also done with chunk it-1
+    const int nxt = it + SK_STAGES - 1;
+    float av[4];
+    const bool more = nxt < nchunks;
+    if (more) {
+      issue_b(nxt);
+      load_a(nxt, av);
+    }
+    cp_async_commit();
+
+    const float* bs = Bs + (it % SK_STAGES) * SK_B_STAGE + (warp * SK_RW) * SK_COLS + lane * 4;
+    const float* as = As + (it % SK_STAGES) * SK_A_STAGE + (warp * SK_RW) * SK_M;
+#pragma unroll
+    for (int r = 0; r < SK_RW; ++r) {
+      const float4 b = *reinterpret_cast<const float4*>(bs + r * SK_COLS);
+      const float2 bx = make_float2(b.x, b.x), by = make_float2(b.y, b.y), bz = make_float2(b.z, b.z),
+                   bw = make_float2(b.w, b.w);
+#pragma unroll
+      for (int mq = 0; mq < SK_M / 4; ++mq) {
+        const float4 a4 = *reinterpret_cast<const float4*>(as + r * SK_M + 4 * mq);
+        const float2 a01 = make_float2(a4.x, a4.y), a23 = make_float2(a4.z, a4.w);
+        acc[2 * mq][0] = __ffma2_rn(a01, bx, acc[2 * mq][0]);
+        acc[2 * mq][1] = __ffma2_rn(a01, by, acc[2 * mq][1]);
+        acc[2 * mq][2] = __ffma2_rn(a01, bz, acc[2 * mq][2]);
+        acc[2 * mq][3] = __ffma2_rn(a01, bw, acc[2 * mq][3]);
+        acc[2 * mq + 1][0] = __ffma2_rn(a23, bx, acc[2 * mq + 1][0]);
+        acc[2 * mq + 1][1] = __ffma2_rn(a23, by, acc[2 * mq + 1][1]);
+        acc[2 * mq + 1][2] = __ffma2_rn(a23, bz, acc[2 * mq + 1][2]);
+        acc[2 * mq + 1][3] = __ffma2_rn(a23, bw, acc[2 * mq + 1][3]);
+      }
+    }
+    if (more) store_a(nxt, av);       // read after a later __syncthreads
+  }
+  cp_async_wait<0>();
+
+  // Fold the warps' partial tiles in warp order (fixed order => reproducible bits); the ring's
+  // first stage is free by now and serves as the 16 x 128 fold buffer.
+  float* red = Bs;
   for (int w = 0; w < SK_WARPS; ++w) {
     __syncthreads();
     if (warp == w) {
 #pragma unroll
       for (int m = 0; m < SK_M; ++m) {
-        float4* p = reinterpret_cast<float4*>(&red[m][lane * 4]);
+        float4* p = reinterpret_cast<float4*>(red + m * SK_COLS + lane * 4);
         float4 v = (w == 0) ? make_float4(0.f, 0.f, 0.f, 0.f) : *p;
-        v.x += acc[m][0]; v.y += acc[m][1]; v.z += acc[m][2]; v.w += acc[m][3];
+        const float2 c0 = acc[m >> 1][0], c1 = acc[m >> 1][1], c2 = acc[m >> 1][2], c3 = acc[m >> 1][3];
+        v.x += (m & 1) ? c0.y : c0.x; v.y += (m & 1) ? c1.y : c1.x;
+        v.z += (m & 1) ? c2.y : c2.x; v.w += (m & 1) ? c3.y : c3.x;
         *p = v;
       }
     }
@@ -237,11 +304,11 @@ sgemm_skinny_kernel(const float* __restrict__ A, const float* __restrict__ B, fl
   __syncthreads();
   // out is C itself (no K split) or the partial tile of this split: [split][M][N].
   float* dst = out + size_t(blockIdx.y) * size_t(M) * size_t(N);
-  for (int i = threadIdx.x; i < SK_M * (SK_COLS / 4); i += SK_WARPS * 32) {
+  for (int i = tid; i < SK_M * (SK_COLS / 4); i += SK_THREADS) {
     const int m = i / (SK_COLS / 4), c4 = i - m * (SK_COLS / 4);
-    const int col = blockIdx.x * SK_COLS + c4 * 4;
+    const int col = n0 + c4 * 4;
     if (m < M && col < N)
-      *reinterpret_cast<float4*>(dst + size_t(m) * N + col) = *reinterpret_cast<const float4*>(&red[m][c4 * 4]);
+      *reinterpret_cast<float4*>(dst + size_t(m) * N + col) = *reinterpret_cast<const float4*>(red + m * SK_COLS + c4 * 4);
   }
 }
 
@@ -280,11 +347,11 @@ int launch_tile(const float* A, const float* B, float* C, int M, int N, int K, c
 }  // namespace
 
 size_t sgemm_skinny_partials_bytes(int64_t M, int64_t N, int64_t K, int sm_count, int* ksplit_out) {
-  // Enough CTAs for ~4 per SM, never a split shorter than 8 chunks of SK_KC rows, and splits of
-  // (nearly) equal chunk counts.
+  // Enough CTAs for ~3.5 per SM (three are resident at a time), never a split shorter than 8 chunks
+  // of SK_KC rows, and splits of (nearly) equal chunk counts.
   const int64_t col_ctas = (N + SK_COLS - 1) / SK_COLS;
   const int64_t chunks = (K + SK_KC - 1) / SK_KC;
-  int64_t want = (4LL * sm_count + col_ctas - 1) / col_ctas;
+  int64_t want = (7LL * sm_count / 2 + col_ctas - 1) / col_ctas;
   const int64_t max_split = chunks / 8 > 0 ? chunks / 8 : 1;
   if (want > max_split) want = max_split;
   if (want < 1) want = 1;
@@ -307,7 +374,9 @@ int launch_sgemm_skinny(DeviceCtx* c, const float* A, const float* B, float* C, 
   const int k_per_split = int((chunks + ksplit - 1) / ksplit) * SK_KC;
   dim3 grid(unsigned((N + SK_COLS - 1) / SK_COLS), unsigned(ksplit));
   float* out = ksplit > 1 ? partials : C;
-  sgemm_skinny_kernel<<<grid, SK_WARPS * 32, 0, s>>>(A, B, out, int(M), int(N), int(K), k_per_split);
+  // Opt in to 72 KiB of dynamic shared memory (a per-device function attribute; setting it again is harmless).
+  VT_CUDA(cudaFuncSetAttribute(sgemm_skinny_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(SK_SMEM_BYTES)));
+  sgemm_skinny_kernel<<<grid, SK_THREADS, SK_SMEM_BYTES, s>>>(A, B, out, int(M), int(N), int(K), k_per_split);
   count_launch();
   if (ksplit > 1) {
     const int64_t mn4 = M * N / 4;

@@ -1,0 +1,86 @@
+// Pieces shared by the tcgen05 GEMM kernels (int8 and 3xTF32): tile order, the TMEM -> C epilogue
+// of one warp, and the constants both pipelines agree on.  Accumulator tiles are 128 lanes x 256
+// 32-bit columns per CTA whatever the operand type.
+#pragma once
+
+#include "ptx_sm100.cuh"
+
+namespace vt {
+namespace {
+
+constexpr int BN = 256;                             // accumulator columns per tile
+constexpr int NUM_THREADS = 192;                    // 1 TMA warp, 1 MMA warp, 4 epilogue warps
+constexpr int TMEM_COLS = 512;                      // two 256-column 32-bit accumulators
+
+// Epilogue staging: each epilogue warp owns two 32-row x 32-column int32 buffers (4 KiB each,
+// 128-byte rows in the 128-byte swizzle the C tensor map expects).
+constexpr int EPI_BUF_BYTES = 32 * 32 * 4;
+constexpr int EPI_STAGING_BYTES = 4 * 2 * EPI_BUF_BYTES;   // 32 KiB
+
+struct TileRaster {
+  int mt, nt;  // tile counts along M and N
+  int mode;    // 0 row-major, 1 column-major, 2 grouped
+  int group;   // tile-rows per column sweep (mode 2)
+};
+
+__device__ __forceinline__ void tile_coords(const TileRaster& rs, int t, int& mi, int& ni) {
+  if (rs.mode == 0) {
+    mi = t / rs.nt;
+    ni = t - mi * rs.nt;
+  } else if (rs.mode == 1) {
+    ni = t / rs.mt;
+    mi = t - ni * rs.mt;
+  } else {
+    const int per = rs.group * rs.nt;
+    const int g = t / per;
+    const int w = t - g * per;
+    const int rows = min(rs.group, rs.mt - g * rs.group);
+    ni = w / rows;
+    mi = g * rs.group + (w - ni * rows);
+  }
+}
+
+// Moves one warp's 32 rows x 256 columns of an accumulator from TMEM to C.
+//   kTmaStore: TMEM -> registers -> swizzled shared memory -> cp.async.bulk.tensor store, so C is
+//              written in whole 128-byte lines and rows/columns outside C are clipped by the TMA unit;
+//   otherwise: TMEM -> registers -> predicated 16-byte global stores.
+// Returns once the accumulator has been read (the stores may still be in flight).
+template <bool kTmaStore>
+__device__ __forceinline__ void epilogue_warp_tile(uint32_t t_row, const CUtensorMap* tmC, uint8_t* staging,
+                                                   int32_t* __restrict__ C, int M, int N, int row0, int n0,
+                                                   int lane) {
+  const int row = row0 + lane;
+#pragma unroll 1
+  for (int c = 0; c < BN / 32; ++c) {
+    uint32_t r[32];
+    tmem_ld_32x32b_x32(t_row + uint32_t(c * 32), r);
+    tmem_ld_wait();
+    if constexpr (kTmaStore) {
+      uint8_t* buf = staging + (c & 1) * EPI_BUF_BYTES;
+      if (lane == 0) tma_store_wait_read<1>();   // the store that last read this buffer is done with it
+      __syncwarp();
+      const uint32_t base = smem_u32(buf) + uint32_t(lane) * 128u;
+#pragma unroll
+      for (int v = 0; v < 8; ++v)
+        st_shared_v4(base + (uint32_t(v ^ (lane & 7)) << 4), r[4 * v], r[4 * v + 1], r[4 * v + 2], r[4 * v + 3]);
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        if (row0 < M && n0 + c * 32 < N) tma_store_2d(tmC, buf, n0 + c * 32, row0);
+        tma_store_commit();
+      }
+    } else {
+      if (row < M) {
+        int32_t* crow = C + size_t(row) * size_t(N) + n0;
+#pragma unroll
+        for (int v = 0; v < 8; ++v) {
+          const int col = n0 + c * 32 + v * 4;
+          if (col < N) st_global_v4(crow + c * 32 + v * 4, r[4 * v], r[4 * v + 1], r[4 * v + 2], r[4 * v + 3]);
+        }
+      }
+    }
+  }
+}
+
+}  // namespace
+}  // namespace vt

@@ -271,7 +271,7 @@ def run_gpu_arm(args, kind, M, N, K, batch, metric, unit):
 
     def step():
         if kind == "f32":
-            nv.sgemm(A, B, C, rows, N, K, dev=dev, where=nv.VT_DEVICE, stream=st)
+            nv.sgemm(A, B, C, rows, N, K, dev=dev, variant=args.sgemm_variant, where=nv.VT_DEVICE, stream=st)
         elif kind == "i8b":
             nv.i8gemm_shared_b(A, B, C, rows // M, M, N, K, dev=dev, acc_rows=16, where=nv.VT_DEVICE, stream=st)
         else:
@@ -367,10 +367,21 @@ def run_gpu_arm(args, kind, M, N, K, batch, metric, unit):
                 "frac": achieved / peaks["hbm_gbs"], "peak_source": "%s hbm_gbs" % peaks_src}
     elif kind == "f32":
         achieved = ops_per_launch / (launch_ms * 1e-3) / 1e12
-        roof = {"bound": "fp32", "achieved": achieved, "peak": NOMINAL_FP32_TFLOPS, "unit": "TFLOP/s",
-                "frac": achieved / NOMINAL_FP32_TFLOPS,
-                "peak_source": "FFMA pipe at clocks.max.sm: 148 SMs x 128 lanes x 2 x 1.965 GHz (no fp32 SIMT figure "
-                               "in MEASURED_PEAKS.json)"}
+        tensor_path = args.sgemm_variant == nv.VT_SGEMM_TF32X3 or (
+            args.sgemm_variant == nv.VT_SGEMM_AUTO and rows >= 256 and N >= 256 and K >= 256
+            and float(rows) * N * K >= 5.0e8 and N % 4 == 0 and K % 4 == 0)
+        if tensor_path:
+            # three TF32 MMAs per fp32 product; TF32 issues at half the bf16 rate
+            peak = peaks["bf16_tflops"] / 2.0 / 3.0
+            roof = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+                    "peak_source": "%s bf16_tflops / 2 (TF32 rate) / 3 (MMAs per fp32 product); the step also holds the "
+                                   "two hi/lo split passes" % peaks_src,
+                    "vs_ffma_pipe_74.45": achieved / NOMINAL_FP32_TFLOPS}
+        else:
+            roof = {"bound": "fp32", "achieved": achieved, "peak": NOMINAL_FP32_TFLOPS, "unit": "TFLOP/s",
+                    "frac": achieved / NOMINAL_FP32_TFLOPS,
+                    "peak_source": "FFMA pipe at clocks.max.sm: 148 SMs x 128 lanes x 2 x 1.965 GHz (no fp32 SIMT "
+                                   "figure in MEASURED_PEAKS.json)"}
     else:
         achieved = ops_per_launch / (launch_ms * 1e-3) / 1e12
         peak = 2.0 * peaks["bf16_tflops"]
@@ -418,6 +429,7 @@ def main() -> int:
     ap.add_argument("--scaling", choices=("weak", "strong"), default="weak",
                     help="weak: every GPU gets the full shape; strong: the shape's rows are split over the GPUs")
     ap.add_argument("--i8-variant", type=int, default=0, help="VT_I8_* kernel variant (0 = the library's choice)")
+    ap.add_argument("--sgemm-variant", type=int, default=0, help="VT_SGEMM_* kernel variant (0 = the library's choice)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
     args = ap.parse_args()

@@ -69,8 +69,12 @@ enum {
   VT_I8_CTA_PAIR_DIRECT_STORE = 5
 };
 
-/* fp32 kernel variants. */
-enum { VT_SGEMM_AUTO = 0, VT_SGEMM_TILE128 = 1, VT_SGEMM_TILE64 = 2, VT_SGEMM_SKINNY = 3 };
+/* fp32 kernel variants.
+ *   TILE128 / TILE64  register-tiled FFMA kernel (true fp32 arithmetic), 128x128 or 64x64 CTA tiles
+ *   SKINNY            M <= 16, N % 4 == 0: streams B once (HBM-bound)
+ *   TF32X3            tensor cores, every operand split into TF32 hi + lo, three MMAs per product
+ *                     (N % 4 == 0, K % 4 == 0, 16-byte aligned operands) */
+enum { VT_SGEMM_AUTO = 0, VT_SGEMM_TILE128 = 1, VT_SGEMM_TILE64 = 2, VT_SGEMM_SKINNY = 3, VT_SGEMM_TF32X3 = 4 };
 
 /* Number of CUDA devices visible, or a negative VT_ERR_* code. */
 int vt_device_count(void);

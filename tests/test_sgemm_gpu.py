@@ -19,15 +19,40 @@ def uniform(rng, shape):
     return (rng.random(shape, dtype=np.float32) * 2 - 1)
 
 
-@pytest.mark.parametrize("variant", [0, 1, 2])
+@pytest.mark.parametrize("variant", [0, 1, 2, 4])
 def test_shapes_against_float64(native, variant):
     rng = np.random.default_rng(20260917 + 1)
     for (m, n, k) in ((256, 256, 256), (1, 1, 1), (5, 3, 2), (77, 130, 33), (300, 200, 100), (128, 128, 16),
                       (129, 127, 17), (512, 384, 1000), (1024, 1024, 1024), (64, 2048, 96)):
+        if variant == 4 and (n % 4 or k % 4):
+            with pytest.raises(native.NativeError):     # the tensor-core variant needs 16-byte row pitches
+                native.sgemm(uniform(rng, (m, k)), uniform(rng, (k, n)), np.zeros((m, n), np.float32), m, n, k,
+                             variant=variant)
+            continue
         a, b = uniform(rng, (m, k)), uniform(rng, (k, n))
         c = np.full((m, n), np.nan, dtype=np.float32)
         native.sgemm(a, b, c, m, n, k, variant=variant)
         assert relfro(c, a.astype(np.float64) @ b.astype(np.float64)) <= TOL, (m, n, k)
+
+
+def test_tf32x3_error_does_not_grow_with_k(native):
+    """The 3xTF32 variant folds at most 128 values of K into one tensor-core accumulator; its error
+    must stay far inside the tolerance for long reductions and for same-sign data (the worst case for
+    a truncating accumulator)."""
+    import torch
+    gen = torch.Generator(device="cuda").manual_seed(7)
+    st = native.torch_stream()
+    for (m, n, k) in ((512, 512, 16384), (1024, 768, 4096), (260, 516, 1028)):
+        for positive in (False, True):
+            A = torch.rand((m, k), device="cuda", generator=gen)
+            B = torch.rand((k, n), device="cuda", generator=gen)
+            if not positive:
+                A, B = A * 2 - 1, B * 2 - 1
+            C = torch.full((m, n), float("nan"), device="cuda")
+            native.sgemm(A, B, C, m, n, k, variant=native.VT_SGEMM_TF32X3, where=native.VT_DEVICE, stream=st)
+            native.sync(0, st)
+            ref = A.double() @ B.double()
+            assert float((C.double() - ref).norm() / ref.norm()) <= TOL / 4, (m, n, k, positive)
 
 
 def test_config1_256_cubed_vs_generated_c(native, liboracle):
@@ -41,7 +66,7 @@ def test_config1_256_cubed_vs_generated_c(native, liboracle):
     liboracle.oracle_dgemm_tuned(a64.ctypes.data, b64.ctypes.data, ref_tuned.ctypes.data, m, n, k)
     liboracle.oracle_dgemm_naive(a64.ctypes.data, b64.ctypes.data, ref_naive.ctypes.data, m, n, k)
     assert relfro(ref_tuned, ref_naive) < 1e-14
-    for variant in (0, 1, 2):
+    for variant in (0, 1, 2, 4):
         c = np.zeros((m, n), dtype=np.float32)
         native.sgemm(a, b, c, m, n, k, variant=variant)
         assert relfro(c, ref_tuned) <= TOL and relfro(c, a64 @ b64) <= TOL
@@ -73,12 +98,14 @@ def test_config5_large_fp32(native):
     B = torch.rand((K, N), device="cuda", generator=gen) * 2 - 1
     C = torch.full((M, N), float("nan"), device="cuda")
     st = native.torch_stream()
-    native.sgemm(A, B, C, M, N, K, where=native.VT_DEVICE, stream=st)
-    native.sync(0, st)
     rows = torch.arange(0, M, 64, device="cuda")
     ref = A[rows].double() @ B.double()
-    assert float((C[rows].double() - ref).norm() / ref.norm()) <= TOL
-    assert not torch.isnan(C).any()
+    for variant in (native.VT_SGEMM_AUTO, native.VT_SGEMM_TILE128, native.VT_SGEMM_TF32X3):
+        C.fill_(float("nan"))
+        native.sgemm(A, B, C, M, N, K, variant=variant, where=native.VT_DEVICE, stream=st)
+        native.sync(0, st)
+        assert float((C[rows].double() - ref).norm() / ref.norm()) <= TOL
+        assert not torch.isnan(C).any()
     C16 = torch.full((16, N), float("nan"), device="cuda")
     native.sgemm(A[:16], B, C16, 16, N, K, where=native.VT_DEVICE, stream=st)
     native.sync(0, st)

@@ -38,6 +38,7 @@ VT_SGEMM_AUTO = 0
 VT_SGEMM_TILE128 = 1
 VT_SGEMM_TILE64 = 2
 VT_SGEMM_SKINNY = 3
+VT_SGEMM_TF32X3 = 4
 
 # Every symbol include/veritac_b200.h declares, with its ctypes signature.
 SIGNATURES = {

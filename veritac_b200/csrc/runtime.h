@@ -66,6 +66,10 @@ int launch_sgemm(DeviceCtx* c, const float* A, const float* B, float* C, int64_t
                  int variant, cudaStream_t s);
 int launch_sgemm_skinny(DeviceCtx* c, const float* A, const float* B, float* C, float* partials, int64_t M,
                         int64_t N, int64_t K, int ksplit, cudaStream_t s);
+bool sgemm_tf32x3_supported(const float* A, const float* B, const float* C, int64_t M, int64_t N, int64_t K);
+size_t sgemm_tf32x3_workspace_bytes(int64_t M, int64_t N, int64_t K);
+int launch_sgemm_tf32x3(DeviceCtx* c, const float* A, const float* B, float* C, float* split, int64_t M, int64_t N,
+                        int64_t K, cudaStream_t s);
 size_t sgemm_skinny_partials_bytes(int64_t M, int64_t N, int64_t K, int sm_count, int* ksplit_out);
 int launch_i8_tile_program(DeviceCtx* c, const int8_t* A, const int8_t* B, int32_t* C, int64_t lda, int64_t ldb,
                            int64_t ldc, int64_t n_tiles, const int64_t* d_c_off, const int64_t* d_term_begin,

@@ -134,7 +134,7 @@ int vt_sgemm(int dev, const float* A, const float* B, float* C, int64_t M, int64
  *   - `stream` is used as given (a cudaStream_t; NULL is the CUDA default stream).  The call only
  *     enqueues; synchronise the stream yourself.  A, B, C are device pointers on `dev`, B and C
  *     16-byte aligned.  Results are bit-identical to vt_sgemm's VT_SGEMM_SKINNY. */
-#define VT_SKINNY_STATIC_SCRATCH_BYTES (6u << 20)
+#define VT_SKINNY_STATIC_SCRATCH_BYTES (8u << 20)
 int vt_sgemm_skinny_static_scratch(int dev, const float* A, const float* B, float* C, int64_t M, int64_t N,
                                    int64_t K, void* stream);
 

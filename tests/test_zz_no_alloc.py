@@ -46,8 +46,8 @@ def test_static_scratch_refuses_what_does_not_fit(native):
     import torch
 
     dummy = torch.zeros(64, device="cuda")
-    with pytest.raises(native.NativeError) as info:      # two K splits of 16 x 75648 partials > 6 MiB
-        native.sgemm_skinny_static_scratch(dummy, dummy, dummy, 16, 75648, 8192, stream=native.torch_stream())
+    with pytest.raises(native.NativeError) as info:      # seven K splits of 16 x 64000 partials = 27 MiB > 8 MiB
+        native.sgemm_skinny_static_scratch(dummy, dummy, dummy, 16, 64000, 8192, stream=native.torch_stream())
     assert info.value.code == native.VT_ERR_UNSUPPORTED
     assert "static array holds %d" % native.SKINNY_STATIC_SCRATCH_BYTES in info.value.message
     with pytest.raises(native.NativeError):              # not a skinny shape

@@ -150,7 +150,7 @@ def sgemm(A, B, C, M: int, N: int, K: int, *, dev: int = 0, variant: int = VT_SG
     check(lib().vt_sgemm(dev, _ptr(A), _ptr(B), _ptr(C), M, N, K, variant, where, stream))
 
 
-SKINNY_STATIC_SCRATCH_BYTES = 6 << 20
+SKINNY_STATIC_SCRATCH_BYTES = 8 << 20
 
 
 def sgemm_skinny_static_scratch(A, B, C, M: int, N: int, K: int, *, dev: int = 0, stream: int = 0) -> None:

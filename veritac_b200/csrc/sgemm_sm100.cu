@@ -347,19 +347,32 @@ int launch_tile(const float* A, const float* B, float* C, int M, int N, int K, c
 }  // namespace
 
 size_t sgemm_skinny_partials_bytes(int64_t M, int64_t N, int64_t K, int sm_count, int* ksplit_out) {
-  // Enough CTAs for ~3.5 per SM (three are resident at a time), never a split shorter than 8 chunks
-  // of SK_KC rows, and splits of (nearly) equal chunk counts.
+  // Three CTAs are resident per SM.  The K split is the one that minimises a simple cost model:
+  // whole "waves" of resident CTAs (a last wave that is mostly empty costs as much as a full one)
+  // times the extra traffic of writing and re-reading ksplit partial tiles.  A split is never
+  // shorter than 8 stages of SK_KC rows, and splits have (nearly) equal stage counts.
   const int64_t col_ctas = (N + SK_COLS - 1) / SK_COLS;
   const int64_t chunks = (K + SK_KC - 1) / SK_KC;
-  int64_t want = (7LL * sm_count / 2 + col_ctas - 1) / col_ctas;
-  const int64_t max_split = chunks / 8 > 0 ? chunks / 8 : 1;
-  if (want > max_split) want = max_split;
-  if (want < 1) want = 1;
-  if (want > 64) want = 64;
-  const int64_t per = (chunks + want - 1) / want;
-  want = (chunks + per - 1) / per;
-  if (ksplit_out) *ksplit_out = int(want);
-  return want > 1 ? size_t(want) * size_t(M) * size_t(N) * sizeof(float) : 0;
+  const int64_t max_split = chunks / 8 > 0 ? (chunks / 8 < 64 ? chunks / 8 : 64) : 1;
+  const double slots = 3.0 * sm_count;
+  int64_t best = 1;
+  double best_cost = 1e300;
+  for (int64_t cand = 1; cand <= max_split; ++cand) {
+    const int64_t per = (chunks + cand - 1) / cand;
+    const int64_t ks = (chunks + per - 1) / per;          // the split count this stage count really gives
+    const double waves = double(col_ctas * ks) / slots;
+    const double rounds = waves <= 1.0 ? 1.0 : double(int64_t(waves + 0.999999));
+    // fewer CTAs than slots: the idle SMs' share of bandwidth is not lost, but parallelism is
+    const double fill = waves < 1.0 ? waves : waves / rounds;
+    const double extra = ks > 1 ? 1.0 + double(ks) * 2.0 * double(M) / double(K) : 1.0;
+    const double cost = extra / (0.15 + 0.85 * fill);
+    if (cost < best_cost - 1e-12) {
+      best_cost = cost;
+      best = ks;
+    }
+  }
+  if (ksplit_out) *ksplit_out = int(best);
+  return best > 1 ? size_t(best) * size_t(M) * size_t(N) * sizeof(float) : 0;
 }
 
 int launch_sgemm_skinny(DeviceCtx* c, const float* A, const float* B, float* C, float* partials, int64_t M,

@@ -225,3 +225,22 @@ def test_host_buffers_equal_device_buffers_large(native):
     native.i8gemm(a, b, c, m, n, k)
     want = (torch.from_numpy(a).cuda().double() @ torch.from_numpy(b).cuda().double()).to(torch.int32).cpu().numpy()
     assert np.array_equal(c, want)
+
+
+def test_measure_controls_matches_reference_scoring(native, g, lowering):
+    """The reference's tests/test_gemmini_evaluation.py:16-31 on the measured counterpart: a known
+    batched stream is recognised as an existing control, gains nothing over the best one, and every
+    control computes the same bits."""
+    from veritac_b200.specializations.gemmini_gemm.evaluation import measure_controls
+    plan = g.make_plan(32, 16, 16, "baseline")
+    plan["accumulator_rows"] = 32
+    a, b = go.deterministic_inputs(32, 16, 16, 3)
+    result = measure_controls(plan, lowering.gen_batched_reuse_b(plan, 2), a, b, repeats=3)
+    assert result["input_reduction_vs_baseline"] > 0
+    assert result["input_reduction_vs_best_existing"] == 0
+    assert result["beats_best_existing_objective"] is False
+    assert "existing_batched_b_2" in result["exact_matches"]
+    assert result["bit_exact"] is True and result["hardware_latency"]["candidate"] > 0
+    assert [c["name"] for c in result["controls"]] == ["baseline", "existing_batched_b_1", "existing_batched_b_2"]
+    with pytest.raises(ValueError, match="candidate failed"):
+        measure_controls(g.make_plan(16, 16, 16, "baseline"), [g.Fence()], a[:256], b[:256])

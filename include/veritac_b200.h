@@ -74,7 +74,14 @@ enum {
  *   SKINNY            M <= 16, N % 4 == 0: streams B once (HBM-bound)
  *   TF32X3            tensor cores, every operand split into TF32 hi + lo, three MMAs per product
  *                     (N % 4 == 0, K % 4 == 0, 16-byte aligned operands) */
-enum { VT_SGEMM_AUTO = 0, VT_SGEMM_TILE128 = 1, VT_SGEMM_TILE64 = 2, VT_SGEMM_SKINNY = 3, VT_SGEMM_TF32X3 = 4 };
+enum {
+  VT_SGEMM_AUTO = 0,
+  VT_SGEMM_TILE128 = 1,
+  VT_SGEMM_TILE64 = 2,
+  VT_SGEMM_SKINNY = 3,
+  VT_SGEMM_TF32X3 = 4,
+  VT_SGEMM_SKINNY_TF32X3 = 5 /* SKINNY with the products on mma.sync TF32 (3xTF32 split in registers) */
+};
 
 /* Number of CUDA devices visible, or a negative VT_ERR_* code. */
 int vt_device_count(void);

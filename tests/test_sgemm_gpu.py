@@ -72,20 +72,21 @@ def test_config1_256_cubed_vs_generated_c(native, liboracle):
         assert relfro(c, ref_tuned) <= TOL and relfro(c, a64 @ b64) <= TOL
 
 
-def test_skinny_kernel(native):
+@pytest.mark.parametrize("variant", [3, 5])
+def test_skinny_kernel(native, variant):
     rng = np.random.default_rng(20260917 + 5)
     for (m, n, k) in ((16, 8192, 8192), (16, 1024, 640), (7, 1024, 640), (1, 512, 4096), (16, 516, 100),
                       (3, 128, 64)):
         a, b = uniform(rng, (m, k)), uniform(rng, (k, n))
         c = np.full((m, n), np.nan, dtype=np.float32)
-        native.sgemm(a, b, c, m, n, k, variant=native.VT_SGEMM_SKINNY)
+        native.sgemm(a, b, c, m, n, k, variant=variant)
         assert relfro(c, a.astype(np.float64) @ b.astype(np.float64)) <= TOL, (m, n, k)
         c2 = np.full((m, n), np.nan, dtype=np.float32)
-        native.sgemm(a, b, c2, m, n, k, variant=native.VT_SGEMM_SKINNY)
+        native.sgemm(a, b, c2, m, n, k, variant=variant)
         assert np.array_equal(c, c2)      # fixed summation order: bit-reproducible
     with pytest.raises(native.NativeError):
         native.sgemm(uniform(rng, (17, 64)), uniform(rng, (64, 64)), np.zeros((17, 64), np.float32), 17, 64, 64,
-                     variant=native.VT_SGEMM_SKINNY)
+                     variant=variant)
 
 
 def test_config5_large_fp32(native):

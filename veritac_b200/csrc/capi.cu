@@ -201,7 +201,7 @@ int vt_sgemm(int dev, const float* A, const float* B, float* C, int64_t M, int64
   if (where != VT_HOST && where != VT_DEVICE) return fail(VT_ERR_INVALID, "where must be VT_HOST or VT_DEVICE");
   if (M < 1 || N < 1 || K < 1) return fail(VT_ERR_INVALID, "dimensions must be positive");
   if (M > 0x7fffffffLL || N > 0x7fffffffLL || K > 0x7fffffffLL) return fail(VT_ERR_INVALID, "dimension overflows int");
-  if (variant < VT_SGEMM_AUTO || variant > VT_SGEMM_TF32X3) return fail(VT_ERR_INVALID, "unknown sgemm variant %d", variant);
+  if (variant < VT_SGEMM_AUTO || variant > VT_SGEMM_SKINNY_TF32X3) return fail(VT_ERR_INVALID, "unknown sgemm variant %d", variant);
   DeviceCtx* c = ctx_for(dev);
   if (!c) return VT_ERR_CUDA;
   cudaStream_t s = where == VT_HOST ? c->stream : pick_stream(c, stream);
@@ -227,7 +227,7 @@ int vt_sgemm(int dev, const float* A, const float* B, float* C, int64_t M, int64
       sgemm_tf32x3_supported(dA, dB, dC, M, N, K))
     variant = VT_SGEMM_TF32X3;
   int rc;
-  if (variant == VT_SGEMM_SKINNY) {
+  if (variant == VT_SGEMM_SKINNY || variant == VT_SGEMM_SKINNY_TF32X3) {
     if (!skinny_ok) return fail(VT_ERR_UNSUPPORTED, "skinny kernel needs M <= 16, N %% 4 == 0 and 16-byte aligned B, C");
     int ksplit = 1;
     const size_t pbytes = sgemm_skinny_partials_bytes(M, N, K, c->sm_count, &ksplit);
@@ -236,7 +236,7 @@ int vt_sgemm(int dev, const float* A, const float* B, float* C, int64_t M, int64
       partials = static_cast<float*>(ctx_workspace(c, 3, pbytes));
       if (!partials) return VT_ERR_CUDA;
     }
-    rc = launch_sgemm_skinny(c, dA, dB, dC, partials, M, N, K, ksplit, s);
+    rc = launch_sgemm_skinny(c, dA, dB, dC, partials, M, N, K, ksplit, s, variant == VT_SGEMM_SKINNY_TF32X3);
   } else if (variant == VT_SGEMM_TF32X3) {
     if (!sgemm_tf32x3_supported(dA, dB, dC, M, N, K))
       return fail(VT_ERR_UNSUPPORTED, "3xTF32 kernel needs N %% 4 == 0, K %% 4 == 0 and 16-byte aligned operands");

@@ -65,7 +65,7 @@ int launch_i8gemm(DeviceCtx* c, const int8_t* A, const int8_t* B, int32_t* C, in
 int launch_sgemm(DeviceCtx* c, const float* A, const float* B, float* C, int64_t M, int64_t N, int64_t K,
                  int variant, cudaStream_t s);
 int launch_sgemm_skinny(DeviceCtx* c, const float* A, const float* B, float* C, float* partials, int64_t M,
-                        int64_t N, int64_t K, int ksplit, cudaStream_t s);
+                        int64_t N, int64_t K, int ksplit, cudaStream_t s, bool tensor_cores);
 bool sgemm_tf32x3_supported(const float* A, const float* B, const float* C, int64_t M, int64_t N, int64_t K);
 size_t sgemm_tf32x3_workspace_bytes(int64_t M, int64_t N, int64_t K);
 int launch_sgemm_tf32x3(DeviceCtx* c, const float* A, const float* B, float* C, float* split, int64_t M, int64_t N,

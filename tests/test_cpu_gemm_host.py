@@ -156,3 +156,13 @@ def test_old_import_paths_are_the_same_modules():
     from CodeGen import runner as top
     from specializations.cpu_gemm import runner as top2
     assert top is r2 and top2 is r2
+
+
+def test_demo_scheduled_nest_is_what_the_tactics_produce():
+    """The demo's directly-built README nest equals the nest the tactic restatement derives."""
+    from veritac_b200.examples import gemm_demo
+    for (M, K, N) in ((256, 256, 256), (64, 96, 128)):
+        assert gemm_demo.naive_matmul_stmt(M, K, N) == lo.matmul_stmt(M, K, N)
+        assert gemm_demo.readme_scheduled_stmt(M, K, N) == lo.apply_tactics(lo.matmul_stmt(M, K, N), lo.README_SCHEDULE)
+    with pytest.raises(ValueError):
+        gemm_demo.readme_scheduled_stmt(48, 32, 32)

@@ -211,3 +211,34 @@ def test_c_loop_nests_agree_with_float64(liboracle, golden_cpu_gemm):
         fn32 = liboracle.oracle_sgemm_tuned if run["schedule"] else liboracle.oracle_sgemm_naive
         fn32(a32.ctypes.data, b32.ctypes.data, c32.ctypes.data, M, N, K)
         assert np.array_equal(c32.astype(np.float64), c)  # small integers: fp32 is exact too
+
+
+def test_c_restatement_equals_reference_generated_c(liboracle):
+    """oracle/_ref holds C printed by the reference's own, unmodified emitter (built by
+    oracle/build_ref.py where the reference tree exists).  The restated nests must reproduce its
+    result bit for bit on uniform random doubles: same loop order, same arithmetic."""
+    from conftest import REPO
+    ref_dir = REPO / "oracle" / "_ref"
+    libs = sorted(ref_dir.glob("matmul_256_*.so"))
+    if not libs:
+        pytest.skip("oracle/_ref not built (no reference tree on this machine)")
+    rng = np.random.default_rng(8)
+    M = N = K = 256
+    a = rng.random((M, K)) * 2 - 1
+    b = rng.random((K, N)) * 2 - 1
+    for lib in libs:
+        fn = ctypes.CDLL(str(lib)).matmul
+        fn.argtypes = [ctypes.c_void_p] * 3
+        # the reference's layout: row stride 1000 doubles
+        A = np.zeros(M * lo.STRIDE)
+        B = np.zeros(K * lo.STRIDE)
+        C = np.zeros(M * lo.STRIDE)
+        A.reshape(M, lo.STRIDE)[:, :K] = a
+        B.reshape(K, lo.STRIDE)[:, :N] = b
+        fn(A.ctypes.data, B.ctypes.data, C.ctypes.data)
+        got = C.reshape(M, lo.STRIDE)[:, :N]
+        want = np.zeros((M, N))
+        mine = liboracle.oracle_dgemm_tuned if "readme" in lib.name else liboracle.oracle_dgemm_naive
+        mine(np.ascontiguousarray(a).ctypes.data, np.ascontiguousarray(b).ctypes.data, want.ctypes.data, M, N, K)
+        assert np.array_equal(got, want), lib.name
+        assert np.allclose(got, a @ b, rtol=0, atol=1e-11)

@@ -128,3 +128,15 @@ def test_benchmark_matmul_drop_in(native, golden_cpu_gemm):
         assert r["c_first_values"] == run["c_first_values"] and r["np_first_values"] == run["np_first_values"]
         assert r["rel_frobenius_error"] == 0.0      # small-integer operands: fp32 is exact
         assert r["c_time_ms"] > 0 and r["speedup"] > 0
+
+
+def test_demos_run_end_to_end(native, capsys):
+    """The reference demo callers (examples/gemm_demo.py, examples/gemmini_gemm_demo.py) on this back end."""
+    from veritac_b200.examples import gemm_demo, gemmini_gemm_demo
+    assert gemm_demo.main(["--dim", "256", "--runs", "2"]) == 0
+    assert "correct: True" in capsys.readouterr().out
+    report = gemmini_gemm_demo.run_demo(64, 64, 64)
+    assert report["verified"] and report["winner"]["schedule"] == "reuse_b"
+    for cand in report["candidates"]:
+        assert cand["numeric_passed"] and len(cand["validation"]) == 6
+    assert report["illustrative_repair"]["accepted"] is False and report["illustrative_repair"]["repair_accepted"]

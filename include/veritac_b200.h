@@ -59,14 +59,17 @@ enum {
  *   B_RELAYOUT             same, after re-laying B out as N x K on the device
  *   CTA_PAIR               two CTAs per 256x256 tile (tcgen05 cta_group::2), C written by TMA stores
  *   DIRECT_STORE           B_AS_STORED with plain 16-byte global stores for C
- *   CTA_PAIR_DIRECT_STORE  CTA_PAIR with plain 16-byte global stores for C */
+ *   CTA_PAIR_DIRECT_STORE  CTA_PAIR with plain 16-byte global stores for C
+ *   CTA_PAIR_TWO_EPI_BUFFERS  CTA_PAIR with 5 operand stages and two store buffers per epilogue warp
+ *                          (CTA_PAIR itself runs 6 stages and one buffer) */
 enum {
   VT_I8_AUTO = 0,
   VT_I8_B_AS_STORED = 1,
   VT_I8_B_RELAYOUT = 2,
   VT_I8_CTA_PAIR = 3,
   VT_I8_DIRECT_STORE = 4,
-  VT_I8_CTA_PAIR_DIRECT_STORE = 5
+  VT_I8_CTA_PAIR_DIRECT_STORE = 5,
+  VT_I8_CTA_PAIR_TWO_EPI_BUFFERS = 6
 };
 
 /* fp32 kernel variants.

@@ -106,7 +106,7 @@ def test_config2_int8_64_cubed_partial_sums(native, g):
         assert (stats["overwrites"], stats["accumulates"]) == (256, 768)
 
 
-@pytest.mark.parametrize("variant", [0, 1, 2, 3, 4, 5])
+@pytest.mark.parametrize("variant", [0, 1, 2, 3, 4, 5, 6])
 def test_shapes_rasters_variants(native, variant):
     rng = np.random.default_rng(11)
     shapes = [(16, 16, 16), (16, 80, 32), (80, 16, 32), (48, 32, 64), (128, 256, 128), (144, 272, 400),

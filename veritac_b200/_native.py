@@ -33,6 +33,7 @@ VT_I8_B_RELAYOUT = 2
 VT_I8_CTA_PAIR = 3
 VT_I8_DIRECT_STORE = 4
 VT_I8_CTA_PAIR_DIRECT_STORE = 5
+VT_I8_CTA_PAIR_TWO_EPI_BUFFERS = 6
 
 VT_SGEMM_AUTO = 0
 VT_SGEMM_TILE128 = 1

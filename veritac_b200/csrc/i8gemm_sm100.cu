@@ -227,11 +227,11 @@ i8gemm_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
 //   * tcgen05.commit multicasts the "empty" and "accumulator full" arrivals to both CTAs;
 //   * both CTAs' epilogue warps arrive on the even CTA's "accumulator empty" barrier (8 arrivals).
 // ---------------------------------------------------------------------------------------------
-constexpr int P_STAGES = 5;   // 5 x 32 KiB operands + 32 KiB epilogue staging
 constexpr int P_A_BYTES = 128 * BK;                 // this CTA's 128 rows of A
 constexpr int P_B_BYTES = 128 * BK;                 // this CTA's 128 columns of B (one TMA box)
 constexpr int P_STAGE_BYTES = P_A_BYTES + P_B_BYTES;
 
+template <int P_STAGES>
 struct PairPipeState {
   uint64_t full[P_STAGES];
   uint64_t empty[P_STAGES];
@@ -241,9 +241,12 @@ struct PairPipeState {
   int abort_word;
 };
 
-constexpr size_t P_SMEM_BYTES = 1024 + size_t(P_STAGES) * P_STAGE_BYTES + EPI_STAGING_BYTES + sizeof(PairPipeState);
+constexpr size_t pair_smem_bytes(int stages, int bufs) {
+  return 1024 + size_t(stages) * P_STAGE_BYTES + size_t(4 * bufs) * EPI_BUF_BYTES + 256;
+}
 
-template <bool kTmaStore>
+// P_STAGES operand stages and kBufs epilogue buffers per warp: (6, 1) and (5, 2) both fit in 227 KiB.
+template <bool kTmaStore, int P_STAGES, int kBufs>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
 i8gemm_umma_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                         const __grid_constant__ CUtensorMap tmC, int32_t* __restrict__ C, int M, int N, int K,
@@ -251,7 +254,7 @@ i8gemm_umma_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
   extern __shared__ uint8_t smem_raw[];
   uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* staging = tiles + size_t(P_STAGES) * P_STAGE_BYTES;
-  PairPipeState* ps = reinterpret_cast<PairPipeState*>(staging + EPI_STAGING_BYTES);
+  PairPipeState<P_STAGES>* ps = reinterpret_cast<PairPipeState<P_STAGES>*>(staging + 4 * kBufs * EPI_BUF_BYTES);
   volatile int* abort_word = &ps->abort_word;
 
   const int warp = threadIdx.x >> 5;
@@ -383,7 +386,7 @@ i8gemm_umma_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
       if (!__all_sync(0xffffffffu, ready)) break;
       tc_fence_after_sync();
       const uint32_t t_row = tmem_base + (uint32_t(q * 32) << 16) + uint32_t(acc * BN);
-      epilogue_warp_tile<kTmaStore>(t_row, &tmC, staging + q * 2 * EPI_BUF_BYTES, C, M, N, m0 + q * 32, n0, lane);
+      epilogue_warp_tile<kTmaStore, kBufs>(t_row, &tmC, staging + q * kBufs * EPI_BUF_BYTES, C, M, N, m0 + q * 32, n0, lane);
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive_remote(&ps->tmem_empty[acc], 0);
@@ -438,12 +441,13 @@ int launch_with_smem(DeviceCtx* c, uint32_t attr_bit, KernelT kernel, size_t sme
 
 int launch_i8gemm(DeviceCtx* c, const int8_t* A, const int8_t* B, int32_t* C, int64_t M, int64_t N, int64_t K,
                   int raster_mode, int group, int variant, cudaStream_t s) {
-  if (variant < VT_I8_B_AS_STORED || variant > VT_I8_CTA_PAIR_DIRECT_STORE)
+  if (variant < VT_I8_B_AS_STORED || variant > VT_I8_CTA_PAIR_TWO_EPI_BUFFERS)
     return fail(VT_ERR_UNSUPPORTED, "i8gemm variant %d is not built", variant);
   if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(C)) & 15)
     return fail(VT_ERR_INVALID, "i8gemm operands must be 16-byte aligned");
   if (raster_mode < 0 || raster_mode > 2) return fail(VT_ERR_INVALID, "raster mode %d out of range", raster_mode);
-  const bool pair = variant == VT_I8_CTA_PAIR || variant == VT_I8_CTA_PAIR_DIRECT_STORE;
+  const bool pair = variant == VT_I8_CTA_PAIR || variant == VT_I8_CTA_PAIR_DIRECT_STORE ||
+                    variant == VT_I8_CTA_PAIR_TWO_EPI_BUFFERS;
   const int tile_m = pair ? 256 : BM;
 
   TileRaster rs;
@@ -486,10 +490,13 @@ int launch_i8gemm(DeviceCtx* c, const int8_t* A, const int8_t* B, int32_t* C, in
   const int max_pairs = c->sm_count / 2;
   const int grid = 2 * int(tiles < max_pairs ? tiles : max_pairs);
   if (variant == VT_I8_CTA_PAIR)
-    return launch_with_smem(c, 4u, i8gemm_umma_pair_kernel<true>, P_SMEM_BYTES, grid, s, tmA, tmB, tmC, C, iM, iN, iK,
-                            rs);
-  return launch_with_smem(c, 16u, i8gemm_umma_pair_kernel<false>, P_SMEM_BYTES, grid, s, tmA, tmB, tmC, C, iM, iN, iK,
-                          rs);
+    return launch_with_smem(c, 4u, i8gemm_umma_pair_kernel<true, 6, 1>, pair_smem_bytes(6, 1), grid, s, tmA, tmB, tmC,
+                            C, iM, iN, iK, rs);
+  if (variant == VT_I8_CTA_PAIR_TWO_EPI_BUFFERS)
+    return launch_with_smem(c, 64u, i8gemm_umma_pair_kernel<true, 5, 2>, pair_smem_bytes(5, 2), grid, s, tmA, tmB, tmC,
+                            C, iM, iN, iK, rs);
+  return launch_with_smem(c, 16u, i8gemm_umma_pair_kernel<false, 6, 1>, pair_smem_bytes(6, 1), grid, s, tmA, tmB, tmC,
+                          C, iM, iN, iK, rs);
 }
 
 }  // namespace vt

@@ -45,7 +45,7 @@ __device__ __forceinline__ void tile_coords(const TileRaster& rs, int t, int& mi
 //              written in whole 128-byte lines and rows/columns outside C are clipped by the TMA unit;
 //   otherwise: TMEM -> registers -> predicated 16-byte global stores.
 // Returns once the accumulator has been read (the stores may still be in flight).
-template <bool kTmaStore>
+template <bool kTmaStore, int kBufs = 2>
 __device__ __forceinline__ void epilogue_warp_tile(uint32_t t_row, const CUtensorMap* tmC, uint8_t* staging,
                                                    int32_t* __restrict__ C, int M, int N, int row0, int n0,
                                                    int lane) {
@@ -56,8 +56,8 @@ __device__ __forceinline__ void epilogue_warp_tile(uint32_t t_row, const CUtenso
     tmem_ld_32x32b_x32(t_row + uint32_t(c * 32), r);
     tmem_ld_wait();
     if constexpr (kTmaStore) {
-      uint8_t* buf = staging + (c & 1) * EPI_BUF_BYTES;
-      if (lane == 0) tma_store_wait_read<1>();   // the store that last read this buffer is done with it
+      uint8_t* buf = staging + (c & (kBufs - 1)) * EPI_BUF_BYTES;
+      if (lane == 0) tma_store_wait_read<kBufs - 1>();   // the store that last read this buffer is done with it
       __syncwarp();
       const uint32_t base = smem_u32(buf) + uint32_t(lane) * 128u;
 #pragma unroll

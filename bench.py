@@ -68,22 +68,49 @@ def load_peaks():
 
 
 class ClockSampler:
-    """nvidia-smi clocks and throttle reasons of one GPU, sampled while the timed region runs."""
+    """SM clock, power and clock-event reasons of one GPU, read through NVML by a polling thread; only samples taken between mark_begin() and mark_end() (the timed region)
+    count.  Falls back to an `nvidia-smi -lms` child when NVML cannot be loaded."""
 
     FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
               "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
               "clocks_event_reasons.sw_power_cap")
+    REASON_BITS = (("hw_slowdown", 0x8), ("hw_thermal_slowdown", 0x40), ("sw_thermal_slowdown", 0x20),
+                   ("sw_power_cap", 0x4))
 
-    def __init__(self, index: int):
+    def __init__(self, index: int, uuid: str | None = None):
         self.index = index
-        self.rows: list[list[str]] = []
+        self.uuid = uuid
+        self.samples: list[tuple] = []       # (host time, sm MHz, reason mask, watts)
+        self.rows: list[list[str]] = []      # nvidia-smi fallback
         self.proc = None
         self.thread = None
+        self.nvml = None
+        self.handle = None
+        self.max_mhz = None
+        self.running = False
+        self.t_begin = self.t_end = None
 
     def start(self):
         try:
+            import pynvml
+            pynvml.nvmlInit()
+            try:
+                self.handle = pynvml.nvmlDeviceGetHandleByUUID(("GPU-" + self.uuid).encode()) if self.uuid else None
+            except Exception:
+                self.handle = None
+            if self.handle is None:
+                self.handle = pynvml.nvmlDeviceGetHandleByIndex(self.index)
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM))
+            self.nvml = pynvml
+            self.running = True
+            self.thread = threading.Thread(target=self._poll, daemon=True)
+            self.thread.start()
+            return
+        except Exception:
+            self.nvml = None
+        try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.FIELDS,
-                                          "--format=csv,noheader,nounits", "-lms", "50"], stdout=subprocess.PIPE,
+                                          "--format=csv,noheader,nounits", "-lms", "20"], stdout=subprocess.PIPE,
                                          stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.proc = None
@@ -91,13 +118,44 @@ class ClockSampler:
         self.thread = threading.Thread(target=self._pump, daemon=True)
         self.thread.start()
 
+    def _poll(self):
+        nv, h = self.nvml, self.handle
+        while self.running:
+            try:
+                mhz = nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM)
+                mask = nv.nvmlDeviceGetCurrentClocksEventReasons(h)
+                watts = nv.nvmlDeviceGetPowerUsage(h) / 1000.0
+            except Exception:
+                break
+            self.samples.append((time.perf_counter(), float(mhz), int(mask), watts))
+            time.sleep(0.0005)   # leave the interpreter to the launching thread
+
     def _pump(self):
         for line in self.proc.stdout:
-            self.rows.append([x.strip() for x in line.split(",")])
+            self.rows.append([time.perf_counter()] + [x.strip() for x in line.split(",")])
+
+    def mark_begin(self):
+        self.t_begin = time.perf_counter()
+
+    def mark_end(self):
+        self.t_end = time.perf_counter()
+
+    def _inside(self, t):
+        return self.t_begin is None or self.t_end is None or self.t_begin <= t <= self.t_end
 
     def stop(self) -> dict:
+        if self.nvml is not None:
+            self.running = False
+            self.thread.join(timeout=2)
+            inside = [x for x in self.samples if self._inside(x[0])]
+            reasons = sorted({name for x in inside for name, bit in self.REASON_BITS if x[2] & bit})
+            sm = [x[1] for x in inside]
+            return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": self.max_mhz, "reasons": reasons,
+                    "samples": len(sm), "sm_mhz_min": min(sm) if sm else None,
+                    "power_w_max": max(x[3] for x in inside) if inside else None,
+                    "source": "NVML polled during the timed region"}
         if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["NVML and nvidia-smi unavailable"]}
         self.proc.terminate()
         try:
             self.proc.wait(timeout=5)
@@ -105,7 +163,9 @@ class ClockSampler:
             self.proc.kill()
         sm, mx, reasons = [], [], set()
         names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
-        for r in self.rows:
+        rows = [r for r in self.rows if self._inside(r[0])] or self.rows
+        for r in rows:
+            r = r[1:]
             if len(r) < 7:
                 continue
             try:
@@ -117,7 +177,7 @@ class ClockSampler:
                 if flag.lower().startswith("active"):
                     reasons.add(name)
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": sorted(reasons), "samples": len(sm)}
+                "reasons": sorted(reasons), "samples": len(sm), "source": "nvidia-smi -lms 20"}
 
 
 # ---------------------------------------------------------------------------------------------
@@ -286,18 +346,24 @@ def run_gpu_arm(args, kind, M, N, K, batch, metric, unit):
         step()
     nv.sync(dev, st)
     barrier()
-    sampler = ClockSampler(local)
+    try:
+        gpu_uuid = str(torch.cuda.get_device_properties(dev).uuid)
+    except Exception:
+        gpu_uuid = None
+    sampler = ClockSampler(local, gpu_uuid)
     if rank == 0:
         sampler.start()
-        time.sleep(0.15)
+        time.sleep(0.05)
     launches0 = nv.launch_count()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
+    sampler.mark_begin()
     e0.record()
     for _ in range(steps):
         step()
     e1.record()
     barrier()
+    sampler.mark_end()
     elapsed_ms = e0.elapsed_time(e1)
     launches = nv.launch_count() - launches0
     nv.sync(dev, st)

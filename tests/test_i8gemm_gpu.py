@@ -119,6 +119,18 @@ def test_shapes_rasters_variants(native, variant):
             assert np.array_equal(gemm(native, a, b, m, n, k, variant=variant, raster=raster, batch_rows=br), want)
 
 
+@pytest.mark.parametrize("variant", [0, 1, 4, 6])
+def test_host_buffers_large_enough_for_the_corner_pipeline(native, variant):
+    """From 2048 x 2048 outputs on, host-buffer calls bring B in by column blocks and return C by
+    regions (pitched copies, kernels on sub-matrices); variant 4 takes no pitch and keeps row blocks."""
+    rng = np.random.default_rng(12)
+    for (m, n, k) in ((2048, 2048, 32), (2320, 2576, 64), (4112, 2064, 48), (2064, 6160, 16)):
+        a = rng.integers(-128, 128, m * k, dtype=np.int8)
+        b = rng.integers(-128, 128, k * n, dtype=np.int8)
+        want = go.matmul_exact(a, b, m, n, k).reshape(-1)
+        assert np.array_equal(gemm(native, a, b, m, n, k, variant=variant), want)
+
+
 def test_extreme_values_at_the_overflow_bound(native):
     """-128 * -128 * K and -128 * 127 * K at K = 8192 (|sum| = 2^27) and at the largest legal K."""
     for k in (8192, 131056):

@@ -440,7 +440,13 @@ int launch_with_smem(DeviceCtx* c, uint32_t attr_bit, KernelT kernel, size_t sme
 }  // namespace
 
 int launch_i8gemm(DeviceCtx* c, const int8_t* A, const int8_t* B, int32_t* C, int64_t M, int64_t N, int64_t K,
-                  int raster_mode, int group, int variant, cudaStream_t s) {
+                  int raster_mode, int group, int variant, cudaStream_t s, int64_t ldb, int64_t ldc) {
+  if (ldb == 0) ldb = N;
+  if (ldc == 0) ldc = N;
+  if (ldb < N || ldc < N || (ldb & 15) || (ldc & 3)) return fail(VT_ERR_INVALID, "bad row pitch for B or C");
+  if ((ldb != N || ldc != N) && variant != VT_I8_B_AS_STORED && variant != VT_I8_CTA_PAIR &&
+      variant != VT_I8_CTA_PAIR_TWO_EPI_BUFFERS)
+    return fail(VT_ERR_UNSUPPORTED, "i8gemm variant %d takes no row pitch", variant);
   if (variant < VT_I8_B_AS_STORED || variant > VT_I8_CTA_PAIR_TWO_EPI_BUFFERS)
     return fail(VT_ERR_UNSUPPORTED, "i8gemm variant %d is not built", variant);
   if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(C)) & 15)
@@ -462,7 +468,7 @@ int launch_i8gemm(DeviceCtx* c, const int8_t* A, const int8_t* B, int32_t* C, in
   CUtensorMap tmA, tmB, tmC;
   int rc = encode_tmap_2d(&tmA, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, A, uint64_t(K), uint64_t(M), uint64_t(K), BK, 128);
   if (rc) return rc;
-  rc = encode_tmap_2d(&tmC, CU_TENSOR_MAP_DATA_TYPE_INT32, 4, C, uint64_t(N), uint64_t(M), uint64_t(N) * 4, 32, 32);
+  rc = encode_tmap_2d(&tmC, CU_TENSOR_MAP_DATA_TYPE_INT32, 4, C, uint64_t(N), uint64_t(M), uint64_t(ldc) * 4, 32, 32);
   if (rc) return rc;
   const int iM = int(M), iN = int(N), iK = int(K);
 
@@ -477,7 +483,7 @@ int launch_i8gemm(DeviceCtx* c, const int8_t* A, const int8_t* B, int32_t* C, in
     const int grid = int(tiles < c->sm_count ? tiles : c->sm_count);
     return launch_with_smem(c, 2u, i8gemm_umma_kernel<true, true>, SMEM_BYTES, grid, s, tmA, tmB, tmC, C, iM, iN, iK, rs);
   }
-  rc = encode_tmap_2d(&tmB, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, B, uint64_t(N), uint64_t(K), uint64_t(N), 128, BK);
+  rc = encode_tmap_2d(&tmB, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, B, uint64_t(N), uint64_t(K), uint64_t(ldb), 128, BK);
   if (rc) return rc;
   if (!pair) {
     const int grid = int(tiles < c->sm_count ? tiles : c->sm_count);

@@ -60,8 +60,10 @@ int encode_tmap_2d(CUtensorMap* out, CUtensorMapDataType dtype, int elem_bytes, 
 // raster_mode: 0 row-major tiles, 1 column-major tiles, 2 grouped (group = tile-rows per sweep).
 // variant: VT_I8_B_AS_STORED (B consumed as K x N row-major, an MN-major operand),
 // VT_I8_B_RELAYOUT (B re-laid out to N x K first, a K-major operand), VT_I8_CTA_PAIR.
+// ldb / ldc: row pitch of B and C in elements when they are sub-blocks of wider matrices (0 = N);
+// only the variants that write C through TMA stores and read B as stored take a pitch.
 int launch_i8gemm(DeviceCtx* c, const int8_t* A, const int8_t* B, int32_t* C, int64_t M, int64_t N, int64_t K,
-                  int raster_mode, int group, int variant, cudaStream_t s);
+                  int raster_mode, int group, int variant, cudaStream_t s, int64_t ldb = 0, int64_t ldc = 0);
 int launch_sgemm(DeviceCtx* c, const float* A, const float* B, float* C, int64_t M, int64_t N, int64_t K,
                  int variant, cudaStream_t s);
 int launch_sgemm_skinny(DeviceCtx* c, const float* A, const float* B, float* C, float* partials, int64_t M,

@@ -74,16 +74,20 @@ enum {
 
 /* fp32 kernel variants.
  *   TILE128 / TILE64  register-tiled FFMA kernel (true fp32 arithmetic), 128x128 or 64x64 CTA tiles
- *   SKINNY            M <= 16, N % 4 == 0: streams B once (HBM-bound)
+ *   SKINNY            M <= 16, N % 4 == 0: streams B once (HBM-bound), true fp32 FFMA arithmetic
  *   TF32X3            tensor cores, every operand split into TF32 hi + lo, three MMAs per product
- *                     (N % 4 == 0, K % 4 == 0, 16-byte aligned operands) */
+ *                     (N % 4 == 0, K % 4 == 0, 16-byte aligned operands)
+ *   SKINNY_TF32X3     M <= 16 on the tensor cores (3xTF32): one TMA-fed launch, tcgen05 with B used as it
+ *                     lies in memory; when K % 4 != 0 or A is not 16-byte aligned, SKINNY_MMA_SYNC runs
+ *   SKINNY_MMA_SYNC   the same stream of B with the products on mma.sync TF32 (any K, any alignment of A) */
 enum {
   VT_SGEMM_AUTO = 0,
   VT_SGEMM_TILE128 = 1,
   VT_SGEMM_TILE64 = 2,
   VT_SGEMM_SKINNY = 3,
   VT_SGEMM_TF32X3 = 4,
-  VT_SGEMM_SKINNY_TF32X3 = 5 /* SKINNY with the products on mma.sync TF32 (3xTF32 split in registers) */
+  VT_SGEMM_SKINNY_TF32X3 = 5,
+  VT_SGEMM_SKINNY_MMA_SYNC = 6
 };
 
 /* Number of CUDA devices visible, or a negative VT_ERR_* code. */

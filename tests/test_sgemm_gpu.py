@@ -72,11 +72,15 @@ def test_config1_256_cubed_vs_generated_c(native, liboracle):
         assert relfro(c, ref_tuned) <= TOL and relfro(c, a64 @ b64) <= TOL
 
 
-@pytest.mark.parametrize("variant", [3, 5])
+@pytest.mark.parametrize("variant", [3, 5, 6])
 def test_skinny_kernel(native, variant):
+    """Variant 5 runs tcgen05 where K % 4 == 0 and the mma.sync form elsewhere; the shapes cover one CTA
+    per slab, whole K ranges per CTA, left-over CTAs that run through several slabs, more slabs than
+    CTAs, ragged N and K, and the K-split tickets returning to zero between calls."""
     rng = np.random.default_rng(20260917 + 5)
     for (m, n, k) in ((16, 8192, 8192), (16, 1024, 640), (7, 1024, 640), (1, 512, 4096), (16, 516, 100),
-                      (3, 128, 64)):
+                      (3, 128, 64), (16, 132, 31), (5, 4, 7), (9, 260, 8), (16, 16384, 4096), (12, 60000, 512),
+                      (16, 4096, 16384), (2, 2048, 2050)):
         a, b = uniform(rng, (m, k)), uniform(rng, (k, n))
         c = np.full((m, n), np.nan, dtype=np.float32)
         native.sgemm(a, b, c, m, n, k, variant=variant)

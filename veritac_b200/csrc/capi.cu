@@ -280,7 +280,7 @@ int vt_sgemm(int dev, const float* A, const float* B, float* C, int64_t M, int64
   if (where != VT_HOST && where != VT_DEVICE) return fail(VT_ERR_INVALID, "where must be VT_HOST or VT_DEVICE");
   if (M < 1 || N < 1 || K < 1) return fail(VT_ERR_INVALID, "dimensions must be positive");
   if (M > 0x7fffffffLL || N > 0x7fffffffLL || K > 0x7fffffffLL) return fail(VT_ERR_INVALID, "dimension overflows int");
-  if (variant < VT_SGEMM_AUTO || variant > VT_SGEMM_SKINNY_TF32X3) return fail(VT_ERR_INVALID, "unknown sgemm variant %d", variant);
+  if (variant < VT_SGEMM_AUTO || variant > VT_SGEMM_SKINNY_MMA_SYNC) return fail(VT_ERR_INVALID, "unknown sgemm variant %d", variant);
   DeviceCtx* c = ctx_for(dev);
   if (!c) return VT_ERR_CUDA;
   cudaStream_t s = where == VT_HOST ? c->stream : pick_stream(c, stream);
@@ -299,14 +299,27 @@ int vt_sgemm(int dev, const float* A, const float* B, float* C, int64_t M, int64
   }
   const bool skinny_ok = M <= 16 && N % 4 == 0 &&
                          ((reinterpret_cast<uintptr_t>(dB) | reinterpret_cast<uintptr_t>(dC)) & 15) == 0;
-  if (variant == VT_SGEMM_AUTO && skinny_ok && N >= 512 && K >= 512) variant = VT_SGEMM_SKINNY;
+  if (variant == VT_SGEMM_AUTO && skinny_ok && N >= 512 && K >= 512) variant = VT_SGEMM_SKINNY_TF32X3;
   // Large products go to the tensor cores (3xTF32, measured ~1e-6 relative Frobenius error at any K);
   // below ~1 GFLOP the two split passes cost more than they save and the FFMA kernel runs.
   if (variant == VT_SGEMM_AUTO && M >= 256 && N >= 256 && K >= 256 && double(M) * double(N) * double(K) >= 5.0e8 &&
       sgemm_tf32x3_supported(dA, dB, dC, M, N, K))
     variant = VT_SGEMM_TF32X3;
   int rc;
-  if (variant == VT_SGEMM_SKINNY || variant == VT_SGEMM_SKINNY_TF32X3) {
+  if (variant == VT_SGEMM_SKINNY_TF32X3 || variant == VT_SGEMM_SKINNY_MMA_SYNC) {
+    if (!skinny_ok) return fail(VT_ERR_UNSUPPORTED, "skinny kernel needs M <= 16, N %% 4 == 0 and 16-byte aligned B, C");
+    const bool umma = variant == VT_SGEMM_SKINNY_TF32X3 && sgemm_skinny_umma_supported(dA, dB, dC, M, N, K);
+    int ctas, slabs, max_parts;
+    if (umma) sgemm_skinny_umma_plan(N, K, c->sm_count, &ctas, &slabs, &max_parts);
+    else sgemm_skinny_tma_plan(N, K, c->sm_count, &ctas, &slabs, &max_parts);
+    float* partials = nullptr;
+    if (max_parts > 1) {
+      partials = static_cast<float*>(ctx_workspace(c, 3, size_t(max_parts) * size_t(M) * size_t(N) * 4));
+      if (!partials) return VT_ERR_CUDA;
+    }
+    rc = umma ? launch_sgemm_skinny_umma(c, dA, dB, dC, partials, c->tickets, M, N, K, s)
+              : launch_sgemm_skinny_tma(c, dA, dB, dC, partials, c->tickets, M, N, K, s);
+  } else if (variant == VT_SGEMM_SKINNY) {
     if (!skinny_ok) return fail(VT_ERR_UNSUPPORTED, "skinny kernel needs M <= 16, N %% 4 == 0 and 16-byte aligned B, C");
     int ksplit = 1;
     const size_t pbytes = sgemm_skinny_partials_bytes(M, N, K, c->sm_count, &ksplit);
@@ -315,7 +328,7 @@ int vt_sgemm(int dev, const float* A, const float* B, float* C, int64_t M, int64
       partials = static_cast<float*>(ctx_workspace(c, 3, pbytes));
       if (!partials) return VT_ERR_CUDA;
     }
-    rc = launch_sgemm_skinny(c, dA, dB, dC, partials, M, N, K, ksplit, s, variant == VT_SGEMM_SKINNY_TF32X3);
+    rc = launch_sgemm_skinny(c, dA, dB, dC, partials, M, N, K, ksplit, s);
   } else if (variant == VT_SGEMM_TF32X3) {
     if (!sgemm_tf32x3_supported(dA, dB, dC, M, N, K))
       return fail(VT_ERR_UNSUPPORTED, "3xTF32 kernel needs N %% 4 == 0, K %% 4 == 0 and 16-byte aligned operands");

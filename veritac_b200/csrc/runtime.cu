@@ -83,6 +83,8 @@ DeviceCtx* ctx_for(int dev) {
   CTX_TRY(cudaMalloc(&c->status, sizeof(int)));
   CTX_TRY(cudaMemset(c->status, 0, sizeof(int)));
   CTX_TRY(cudaMallocHost(&c->status_host, sizeof(int)));
+  CTX_TRY(cudaMalloc(&c->tickets, kTicketCount * sizeof(int)));
+  CTX_TRY(cudaMemset(c->tickets, 0, kTicketCount * sizeof(int)));
   for (auto& ev : c->ev) CTX_TRY(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
 #undef CTX_TRY
   if (!g_encode) {
@@ -122,6 +124,7 @@ int ctx_check_status(DeviceCtx* c, cudaStream_t s) {
   const int st = *c->status_host;
   if (st != KSTAT_OK) {
     VT_CUDA(cudaMemsetAsync(c->status, 0, sizeof(int), s));
+    VT_CUDA(cudaMemsetAsync(c->tickets, 0, kTicketCount * sizeof(int), s));   // an aborted kernel may have left counts behind
     VT_CUDA(cudaStreamSynchronize(s));
     return fail(VT_ERR_DEVICE_WAIT, "a kernel gave up on a bounded device-side wait (status %d)", st);
   }
@@ -139,6 +142,7 @@ void ctx_destroy_all() {
       if (c->ws[i]) cudaFree(c->ws[i]);
     if (c->status) cudaFree(c->status);
     if (c->status_host) cudaFreeHost(c->status_host);
+    if (c->tickets) cudaFree(c->tickets);
     for (auto& ev : c->ev)
       if (ev) cudaEventDestroy(ev);
     if (c->stream) cudaStreamDestroy(c->stream);
@@ -149,7 +153,8 @@ void ctx_destroy_all() {
 }
 
 int encode_tmap_2d(CUtensorMap* out, CUtensorMapDataType dtype, int elem_bytes, const void* base, uint64_t inner,
-                   uint64_t outer, uint64_t row_pitch_bytes, uint32_t box_inner, uint32_t box_outer) {
+                   uint64_t outer, uint64_t row_pitch_bytes, uint32_t box_inner, uint32_t box_outer,
+                   CUtensorMapSwizzle swizzle) {
   if (!g_encode) return fail(VT_ERR_CUDA, "tensor-map encoder not initialised");
   if (reinterpret_cast<uintptr_t>(base) & 15) return fail(VT_ERR_INVALID, "TMA base address must be 16-byte aligned");
   if (row_pitch_bytes & 15) return fail(VT_ERR_INVALID, "TMA row pitch must be a multiple of 16 bytes");
@@ -160,7 +165,7 @@ int encode_tmap_2d(CUtensorMap* out, CUtensorMapDataType dtype, int elem_bytes, 
   const cuuint32_t box[2] = {box_inner, box_outer};
   const cuuint32_t estr[2] = {1, 1};
   const CUresult r = g_encode(out, dtype, 2, const_cast<void*>(base), dims, strides, box, estr,
-                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                              CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle,
                               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS)
     return fail(VT_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d (inner %llu outer %llu box %ux%u)", int(r),

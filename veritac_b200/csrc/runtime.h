@@ -12,6 +12,8 @@
 
 namespace vt {
 
+constexpr int kTicketCount = 4096;
+
 struct DeviceCtx {
   int dev = -1;
   bool ready = false;
@@ -22,6 +24,7 @@ struct DeviceCtx {
   cudaStream_t copy_out = nullptr;     // device->host staging
   int* status = nullptr;               // device word kernels write a KSTAT_* code into
   int* status_host = nullptr;          // pinned mirror
+  int* tickets = nullptr;              // kTicketCount zeroed counters (per-slab arrival counts of the skinny kernel)
   // grow-only device workspace for host-pointer calls and operand re-layouts
   void* ws[4] = {nullptr, nullptr, nullptr, nullptr};
   size_t ws_bytes[4] = {0, 0, 0, 0};
@@ -48,7 +51,8 @@ void count_launch(int n = 1);
 // cuTensorMapEncodeTiled for a row-major 2-D byte/word matrix: `inner` contiguous elements per
 // row, `outer` rows, 128-byte swizzle, zero fill outside the matrix.
 int encode_tmap_2d(CUtensorMap* out, CUtensorMapDataType dtype, int elem_bytes, const void* base, uint64_t inner,
-                   uint64_t outer, uint64_t row_pitch_bytes, uint32_t box_inner, uint32_t box_outer);
+                   uint64_t outer, uint64_t row_pitch_bytes, uint32_t box_inner, uint32_t box_outer,
+                   CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B);
 
 #define VT_CUDA(expr)                                   \
   do {                                                  \
@@ -67,11 +71,19 @@ int launch_i8gemm(DeviceCtx* c, const int8_t* A, const int8_t* B, int32_t* C, in
 int launch_sgemm(DeviceCtx* c, const float* A, const float* B, float* C, int64_t M, int64_t N, int64_t K,
                  int variant, cudaStream_t s);
 int launch_sgemm_skinny(DeviceCtx* c, const float* A, const float* B, float* C, float* partials, int64_t M,
-                        int64_t N, int64_t K, int ksplit, cudaStream_t s, bool tensor_cores);
+                        int64_t N, int64_t K, int ksplit, cudaStream_t s);
 bool sgemm_tf32x3_supported(const float* A, const float* B, const float* C, int64_t M, int64_t N, int64_t K);
 size_t sgemm_tf32x3_workspace_bytes(int64_t M, int64_t N, int64_t K);
 int launch_sgemm_tf32x3(DeviceCtx* c, const float* A, const float* B, float* C, float* split, int64_t M, int64_t N,
                         int64_t K, cudaStream_t s);
+void sgemm_skinny_tma_plan(int64_t N, int64_t K, int sm_count, int* ctas, int* slabs, int* max_parts);
+bool sgemm_skinny_tma_supported(const float* B, const float* C, int64_t M, int64_t N, int64_t K);
+int launch_sgemm_skinny_tma(DeviceCtx* c, const float* A, const float* B, float* C, float* partials, int* tickets,
+                            int64_t M, int64_t N, int64_t K, cudaStream_t s);
+void sgemm_skinny_umma_plan(int64_t N, int64_t K, int sm_count, int* ctas, int* slabs, int* max_parts);
+bool sgemm_skinny_umma_supported(const float* A, const float* B, const float* C, int64_t M, int64_t N, int64_t K);
+int launch_sgemm_skinny_umma(DeviceCtx* c, const float* A, const float* B, float* C, float* partials, int* tickets,
+                             int64_t M, int64_t N, int64_t K, cudaStream_t s);
 size_t sgemm_skinny_partials_bytes(int64_t M, int64_t N, int64_t K, int sm_count, int* ksplit_out);
 int launch_i8_tile_program(DeviceCtx* c, const int8_t* A, const int8_t* B, int32_t* C, int64_t lda, int64_t ldb,
                            int64_t ldc, int64_t n_tiles, const int64_t* d_c_off, const int64_t* d_term_begin,

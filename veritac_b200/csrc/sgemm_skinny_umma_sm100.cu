@@ -1,0 +1,394 @@
+// Skinny fp32 GEMM (M <= 16) on the 5th-generation tensor cores: one HBM-bound stream of B.
+//
+// The product is computed transposed, C^T (n x m) = B^T (n x k) * A^T (k x m), so that the streamed
+// matrix is the tensor core's 128-row operand:
+//   A operand  a 32-row chunk of a 128-column slab of B exactly as it lies in memory (n contiguous:
+//              an MN-major TF32 operand).  For 32-bit MN-major operands tcgen05 wants the
+//              "128-byte swizzle with 32-byte atoms" layout: TMA boxes of 32 floats x 32 rows
+//              written with that swizzle, descriptors with leading offset = one box (4 KiB) and
+//              stride offset = four rows (512 B); a K step of 8 rows moves 1 KiB.
+//   B operand  the matching 16 x 32 block of A (k contiguous: K-major, plain 128-byte swizzle);
+//              rows past M are zero-filled by TMA.
+//   D          128 lanes (n) x 32 columns of fp32 in tensor memory.
+// fp32 accuracy comes from the 3xTF32 split, done without a pass over global memory.  The tensor
+// core reads only the top 19 bits of each 32-bit operand, so the data as loaded *is* the hi part
+// (cut, not rounded).  The lo parts, lo = x - hi (exact; its own cut-off point pre-rounded), are
+// computed by warps of the CTA:
+//   B lo  goes straight into tensor memory (tcgen05.st, 32 columns per chunk) and is used from
+//         there as the A operand of its MMA, so B crosses shared memory once;
+//   A lo  is written under A in shared memory, which makes [A; A lo] one 32-row operand.
+// Two MMAs per K step of 8:  B (smem) x [A; A lo] -> columns 0-15 (hi*hi) and 16-31 (hi*lo);
+//                            B lo (tmem) x A      -> added into columns 0-15 (lo*hi).
+// Accumulators are folded into fp32 registers every KU_WINDOW chunks (the tensor core's own
+// accumulation truncates), adding the two column groups.
+//
+// One CTA per SM.  Warp 0 is the TMA producer (a ring of KU_STAGES x 18 KiB in flight).  MMAs this
+// small cost their issuing thread, and the warps that feed them, more time than the loads take, so
+// the chunks of the ring are dealt to KU_PIPES independent pipes (chunk at ring position p goes to
+// pipe p mod KU_PIPES).  A pipe is one MMA-issuing warp plus four splitting warps (one per TMEM
+// lane quarter) with its own accumulators and B lo buffers; at the end of a piece of work the pipes'
+// sums are added in pipe order through shared memory.  Work split and K-split reduction: see
+// skinny_sched.cuh.  Every wait is bounded.
+#include "ptx_sm100.cuh"
+#include "runtime.h"
+#include "skinny_sched.cuh"
+
+namespace vt {
+namespace {
+
+constexpr int KU_STAGES = 10;
+constexpr int KU_CTAS_PER_SM = 1;
+constexpr int KU_WINDOW = 4;                       // chunks a pipe accumulates in tensor memory between folds
+constexpr int KU_PIPES = 2;
+constexpr int KU_PIECE_OVERHEAD = 10;              // chunks' worth of time between two pieces of work (measured)
+constexpr int KU_THREADS = 32 * (1 + KU_PIPES + 4 * KU_PIPES);
+constexpr int KU_B_BYTES = SKINNY_KC * SKINNY_COLS * 4;   // 16 KiB: four boxes of 32 floats x 32 rows
+constexpr int KU_BOX_BYTES = 32 * 32 * 4;
+constexpr int KU_A_BYTES = 16 * SKINNY_KC * 4;            // 2 KiB
+constexpr int KU_STAGE_BYTES = KU_B_BYTES + 2 * KU_A_BYTES;   // B, A, A lo
+constexpr int KU_PIPE_COLS = 128;                  // per pipe: accumulators at +0 and +32, B lo at +64 and +96
+constexpr int KU_TMEM_COLS = KU_PIPES * KU_PIPE_COLS;
+constexpr int KU_EXCH_BYTES = (KU_PIPES - 1) * 16 * SKINNY_COLS * 4;
+constexpr size_t KU_SMEM_BYTES = 1024 + size_t(KU_STAGES) * KU_STAGE_BYTES + KU_EXCH_BYTES + 512;
+static_assert(KU_TMEM_COLS == 256 || KU_TMEM_COLS == 512 || KU_TMEM_COLS == 128, "TMEM allocations are powers of two");
+
+struct UmmaSkinnyPipe {
+  uint64_t raw_full[KU_STAGES];    // TMA bytes have landed
+  uint64_t split_done[KU_STAGES];  // the chunk's pipe has written the lo parts
+  uint64_t empty[KU_STAGES];       // the MMAs that read the stage have retired
+  uint64_t lo_free[KU_PIPES][2];   // the MMAs that read a B lo buffer in tensor memory have retired
+  uint64_t acc_full[KU_PIPES][2];
+  uint64_t acc_empty[KU_PIPES][2];
+  uint32_t tmem_base;
+  int abort_word;
+  int last_flag;
+};
+
+// lo part of x as the tensor core should see it: x minus its top 19 bits, then half of the cut-off
+// unit added to the bit pattern so that the core's own cut rounds to nearest.
+__device__ __forceinline__ uint32_t lo_part(uint32_t bits) {
+  const float hi = __uint_as_float(bits & 0xffffe000u);
+  return __float_as_uint(__uint_as_float(bits) - hi) + 0x1000u;
+}
+
+__global__ void __launch_bounds__(KU_THREADS, KU_CTAS_PER_SM)
+sgemm_skinny_umma_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmA,
+                         float* __restrict__ C, float* __restrict__ partials, int* __restrict__ tickets, int M, int N,
+                         SkinnySched sc, int* __restrict__ status) {
+  extern __shared__ uint8_t ku_smem_raw[];
+  uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(ku_smem_raw) + 1023) & ~uintptr_t(1023));
+  float* exch = reinterpret_cast<float*>(tiles + size_t(KU_STAGES) * KU_STAGE_BYTES);
+  UmmaSkinnyPipe* ps = reinterpret_cast<UmmaSkinnyPipe*>(tiles + size_t(KU_STAGES) * KU_STAGE_BYTES + KU_EXCH_BYTES);
+  volatile int* abort_word = &ps->abort_word;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int cta = int(blockIdx.x);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < KU_STAGES; ++s) {
+      mbar_init(&ps->raw_full[s], 1);
+      mbar_init(&ps->split_done[s], 4);
+      mbar_init(&ps->empty[s], 1);
+    }
+    for (int p = 0; p < KU_PIPES; ++p)
+      for (int b = 0; b < 2; ++b) {
+        mbar_init(&ps->lo_free[p][b], 1);
+        mbar_init(&ps->acc_full[p][b], 1);
+        mbar_init(&ps->acc_empty[p][b], 4);
+      }
+    ps->abort_word = 0;
+    ps->last_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc<1>(&ps->tmem_base, KU_TMEM_COLS);
+    tmem_relinquish<1>();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = ps->tmem_base;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0) {
+      tma_prefetch_desc(&tmB);
+      tma_prefetch_desc(&tmA);
+      uint32_t filled = 0, fill_parity = 0;
+      uint32_t stage = 0, phase = 0;
+      bool ok = true;
+      SkinnySegment seg;
+      for (int idx = 0; ok && sched_segment(sc, cta, idx, seg); ++idx) {
+        const int n0 = seg.slab * SKINNY_COLS;
+        for (int ch = seg.chunk_beg; ch < seg.chunk_end; ++ch) {
+          if (!mbar_wait(&ps->empty[stage], phase ^ 1, abort_word, KSTAT_WAIT_EXPIRED_PRODUCER)) {
+            ok = false;
+            break;
+          }
+          uint64_t* full = &ps->raw_full[stage];
+          uint8_t* dst = tiles + size_t(stage) * KU_STAGE_BYTES;
+          mbar_arrive_expect_tx(full, KU_B_BYTES + KU_A_BYTES);
+#pragma unroll
+          for (int b = 0; b < 4; ++b) tma_load_2d(dst + b * KU_BOX_BYTES, &tmB, full, n0 + 32 * b, ch * SKINNY_KC);
+          tma_load_2d(dst + KU_B_BYTES, &tmA, full, ch * SKINNY_KC, 0);
+          filled |= 1u << stage;
+          fill_parity = (fill_parity & ~(1u << stage)) | (phase << stage);
+          if (++stage == KU_STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+      if (ok) {
+        // Tail: every stage released => every MMA that reads shared memory has retired and every
+        // commit arrival has landed before the CTA gives its shared memory back.
+        for (int s = 0; s < KU_STAGES; ++s) {
+          if (!mbar_wait(&ps->empty[stage], phase ^ 1, abort_word, KSTAT_WAIT_EXPIRED_PRODUCER)) break;
+          if (++stage == KU_STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+      if (*abort_word != 0) {
+        // Aborting: wait (bounded) for the copies already issued before shared memory goes back.
+        for (int s = 0; s < KU_STAGES; ++s)
+          if (filled & (1u << s)) mbar_wait_drain(&ps->raw_full[s], (fill_parity >> s) & 1u);
+      }
+    }
+    __syncwarp();
+  } else if (warp <= KU_PIPES) {
+    // ------------------------------ MMA issuer of pipe (warp - 1) ------------------------------
+    if (lane == 0) {
+      const int pipe = warp - 1;
+      constexpr uint32_t idesc_pair = umma_instr_desc(UMMA_D_F32, UMMA_AB_TF32, true, false, 128, 32);
+      constexpr uint32_t idesc_lo = umma_instr_desc(UMMA_D_F32, UMMA_AB_TF32, false, false, 128, 16);
+      // Descriptors are kept as a constant high word and a low word that only ever has a constant
+      // added to it, and the ring position is counted, not divided.
+      constexpr uint32_t kMn32Hi = (512u >> 4) | (1u << 14) | (1u << 29);    // stride offset, version, swizzle mode 1
+      constexpr uint32_t kSw128Hi = (1024u >> 4) | (1u << 14) | (2u << 29);  // stride offset, version, swizzle mode 2
+      const uint32_t tiles_lo = (smem_u32(tiles) & 0x3FFFFu) >> 4;
+      auto make_desc = [](uint32_t lo, uint32_t hi) {
+        uint64_t d;
+        asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(lo), "r"(hi));
+        return d;
+      };
+      const uint32_t pipe_tmem = tmem_base + uint32_t(pipe * KU_PIPE_COLS);
+      uint32_t stage = 0, phase = 0, turn = 0;   // ring position of the next chunk; turn = position mod KU_PIPES
+      uint32_t mine = 0;                         // chunks this pipe has taken: B lo buffer = mine & 1
+      int win = 0;
+      bool ok = true;
+      SkinnySegment seg;
+      for (int idx = 0; ok && sched_segment(sc, cta, idx, seg); ++idx) {
+        const int nchunks = seg.chunk_end - seg.chunk_beg;
+        int in_window = 0;
+        for (int i = 0; i < nchunks; ++i) {
+          if (int(turn) == pipe) {
+            const int buf = win & 1;
+            const uint32_t lo_buf = mine & 1u;
+            const bool opens = in_window == 0;
+            if (opens &&
+                !mbar_wait(&ps->acc_empty[pipe][buf], (uint32_t(win >> 1) & 1u) ^ 1u, abort_word, KSTAT_WAIT_EXPIRED_MMA)) {
+              ok = false;
+              break;
+            }
+            if (!mbar_wait(&ps->split_done[stage], phase, abort_word, KSTAT_WAIT_EXPIRED_MMA)) {
+              ok = false;
+              break;
+            }
+            tc_fence_after_sync();
+            const uint32_t b_lo32 = (tiles_lo + stage * (KU_STAGE_BYTES >> 4)) | ((4096u >> 4) << 16);            // B as loaded
+            const uint32_t a_lo32 = (tiles_lo + stage * (KU_STAGE_BYTES >> 4) + (KU_B_BYTES >> 4)) | (1u << 16);  // [A; A lo]
+            const uint32_t d_tmem = pipe_tmem + uint32_t(buf * 32);
+            const uint32_t lo_tmem = pipe_tmem + 64u + lo_buf * 32u;
+#pragma unroll
+            for (int ks = 0; ks < SKINNY_KC / 8; ++ks) {
+              const uint64_t a_desc = make_desc(a_lo32 + ks * (32u >> 4), kSw128Hi);
+              const uint64_t b_desc = make_desc(b_lo32 + ks * (1024u >> 4), kMn32Hi);
+              umma_tf32<1>(d_tmem, b_desc, a_desc, idesc_pair, (ks == 0 && opens) ? 0u : 1u);
+              umma_tf32_a_tmem(d_tmem, lo_tmem + uint32_t(ks * 8), a_desc, idesc_lo, 1u);
+            }
+            umma_commit(&ps->empty[stage]);
+            umma_commit(&ps->lo_free[pipe][lo_buf]);
+            // The window closes when it is full or with this pipe's last chunk of the piece.
+            if (++in_window == KU_WINDOW || i + KU_PIPES >= nchunks) {
+              umma_commit(&ps->acc_full[pipe][buf]);
+              ++win;
+              in_window = 0;
+            }
+            ++mine;
+          }
+          if (++turn == KU_PIPES) turn = 0;
+          if (++stage == KU_STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+    }
+    __syncwarp();
+  } else {
+    // ------------- splitting warps of a pipe: lo parts, accumulator drain, result -------------
+    const int pipe = (warp - 1 - KU_PIPES) >> 2;
+    const int quarter = warp & 3;                                 // the TMEM lanes (and the TMA box) of this warp
+    const int t = ((warp - 1 - KU_PIPES) & 3) * 32 + lane;        // 0..127 within the pipe
+    const uint32_t lane_base = tmem_base + (uint32_t(quarter * 32) << 16) + uint32_t(pipe * KU_PIPE_COLS);
+    uint32_t stage = 0, phase = 0, turn = 0, mine = 0;
+    int win = 0;
+    bool ok = true;
+    SkinnySegment seg;
+    for (int idx = 0; sched_segment(sc, cta, idx, seg); ++idx) {
+      const int nchunks = seg.chunk_end - seg.chunk_beg;
+      float master[16];
+#pragma unroll
+      for (int m = 0; m < 16; ++m) master[m] = 0.f;
+      // Adds this pipe's oldest undrained accumulator (both column groups) into master.
+      auto drain = [&]() -> bool {
+        const int buf = win & 1;
+        if (!mbar_wait(&ps->acc_full[pipe][buf], uint32_t(win >> 1) & 1u, abort_word, KSTAT_WAIT_EXPIRED_EPILOGUE)) return false;
+        tc_fence_after_sync();
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(lane_base + uint32_t(buf * 32), r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int m = 0; m < 16; ++m) master[m] += __uint_as_float(r[m]) + __uint_as_float(r[16 + m]);
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&ps->acc_empty[pipe][buf]);
+        ++win;
+        return true;
+      };
+      int taken = 0, drained = 0;
+      bool due = false;
+      for (int i = 0; i < nchunks && ok; ++i) {
+        if (int(turn) == pipe) {
+          ok = mbar_wait(&ps->raw_full[stage], phase, abort_word, KSTAT_WAIT_EXPIRED_EPILOGUE);
+          if (!ok) break;
+          const uint8_t* stage_ptr = tiles + size_t(stage) * KU_STAGE_BYTES;
+          // This thread's column of the slab, all 32 rows of the chunk.  Box `quarter`: rows of
+          // 128 bytes, 32-byte units XOR-swizzled with (row % 4).
+          const float* box = reinterpret_cast<const float*>(stage_ptr + quarter * KU_BOX_BYTES);
+          uint32_t lo_a[16], lo_b[16];
+#pragma unroll
+          for (int k = 0; k < 16; ++k)
+            lo_a[k] = lo_part(__float_as_uint(box[k * 32 + (((lane >> 3) ^ (k & 3)) << 3) + (lane & 7)]));
+#pragma unroll
+          for (int k = 16; k < 32; ++k)
+            lo_b[k - 16] = lo_part(__float_as_uint(box[k * 32 + (((lane >> 3) ^ (k & 3)) << 3) + (lane & 7)]));
+          {
+            const uint32_t a_addr = smem_u32(stage_ptr + KU_B_BYTES) + uint32_t(t) * 16u;
+            uint32_t x0, x1, x2, x3;
+            asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(x0), "=r"(x1), "=r"(x2), "=r"(x3) : "r"(a_addr));
+            st_shared_v4(a_addr + KU_A_BYTES, lo_part(x0), lo_part(x1), lo_part(x2), lo_part(x3));
+          }
+          // The MMAs that read this B lo buffer two of this pipe's chunks ago must have retired.
+          const uint32_t lo_buf = mine & 1u;
+          ok = mbar_wait(&ps->lo_free[pipe][lo_buf], (uint32_t(mine >> 1) & 1u) ^ 1u, abort_word, KSTAT_WAIT_EXPIRED_EPILOGUE);
+          if (!ok) break;
+          tc_fence_after_sync();
+          tmem_st_32x32b_x16(lane_base + 64u + lo_buf * 32u, lo_a);
+          tmem_st_32x32b_x16(lane_base + 64u + lo_buf * 32u + 16u, lo_b);
+          tmem_st_wait();
+          fence_proxy_async_smem();
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&ps->split_done[stage]);
+          // A window that closed with this pipe's previous chunk has had this whole split to finish.
+          if (due) {
+            ok = drain();
+            ++drained;
+            due = false;
+          }
+          if (++taken % KU_WINDOW == 0) due = true;
+          ++mine;
+        }
+        if (++turn == KU_PIPES) turn = 0;
+        if (++stage == KU_STAGES) {
+          stage = 0;
+          phase ^= 1u;
+        }
+      }
+      const int windows = (taken + KU_WINDOW - 1) / KU_WINDOW;
+      while (ok && drained < windows) {
+        ok = drain();
+        ++drained;
+      }
+
+      // Pipes above 0 hand their sums to pipe 0, which adds them in pipe order.  Whether the CTA is
+      // giving up is read between the two barriers, where no thread can still be in a wait, so all
+      // splitting threads take the same way out.
+      if (pipe > 0) {
+#pragma unroll
+        for (int m = 0; m < 16; ++m) exch[((pipe - 1) * 16 + m) * SKINNY_COLS + t] = master[m];
+      }
+      asm volatile("bar.sync 2, %0;" ::"n"(128 * KU_PIPES) : "memory");
+      const bool giving_up = *abort_word != 0;
+      if (pipe == 0) {
+#pragma unroll
+        for (int q = 1; q < KU_PIPES; ++q)
+#pragma unroll
+          for (int m = 0; m < 16; ++m) master[m] += exch[((q - 1) * 16 + m) * SKINNY_COLS + t];
+      }
+      asm volatile("bar.sync 2, %0;" ::"n"(128 * KU_PIPES) : "memory");   // exch may be rewritten
+      if (giving_up) break;
+      if (pipe == 0) {
+        // The tile of this piece goes to C (the slab has one piece) or to its slot among the slab's partial tiles.
+        float* dst = seg.parts == 1 ? C : partials + size_t(seg.part) * size_t(M) * size_t(N);
+        const int col = seg.slab * SKINNY_COLS + quarter * 32 + lane;
+        if (col < N) {
+#pragma unroll
+          for (int m = 0; m < 16; ++m)
+            if (m < M) dst[size_t(m) * N + col] = master[m];
+        }
+        if (seg.parts > 1) skinny_finish_piece<128>(seg, t, 1, &ps->last_flag, tickets, partials, C, M, N);
+      }
+    }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc<1>(tmem_base, KU_TMEM_COLS);
+  if (threadIdx.x == 0 && ps->abort_word != 0) atomicCAS(status, 0, ps->abort_word);
+}
+
+}  // namespace
+
+void sgemm_skinny_umma_plan(int64_t N, int64_t K, int sm_count, int* ctas, int* slabs, int* max_parts) {
+  const SkinnySched sc = make_skinny_sched(N, K, sm_count, KU_CTAS_PER_SM, KU_PIECE_OVERHEAD, ctas);
+  *slabs = sc.slabs;
+  *max_parts = skinny_max_parts(sc);
+}
+
+bool sgemm_skinny_umma_supported(const float* A, const float* B, const float* C, int64_t M, int64_t N, int64_t K) {
+  return M >= 1 && M <= 16 && N % 4 == 0 && N >= 4 && K % 4 == 0 && K >= 4 && N < (1LL << 31) && K < (1LL << 31) &&
+         ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(C)) & 15) == 0;
+}
+
+int launch_sgemm_skinny_umma(DeviceCtx* c, const float* A, const float* B, float* C, float* partials, int* tickets,
+                             int64_t M, int64_t N, int64_t K, cudaStream_t s) {
+  if (!sgemm_skinny_umma_supported(A, B, C, M, N, K))
+    return fail(VT_ERR_UNSUPPORTED,
+                "skinny tensor-core kernel needs M <= 16, N %% 4 == 0, K %% 4 == 0 and 16-byte aligned operands");
+  int ctas;
+  const SkinnySched sc = make_skinny_sched(N, K, c->sm_count, KU_CTAS_PER_SM, KU_PIECE_OVERHEAD, &ctas);
+  if (skinny_max_parts(sc) > 1 && (!partials || !tickets)) return fail(VT_ERR_INVALID, "skinny K split needs scratch memory");
+  if (sc.slabs > kTicketCount)
+    return fail(VT_ERR_UNSUPPORTED, "N = %lld has more slabs than the library keeps tickets for", (long long)N);
+  CUtensorMap tmB, tmA;
+  int rc = encode_tmap_2d(&tmB, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, B, uint64_t(N), uint64_t(K), uint64_t(N) * 4, 32, 32,
+                          CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B);
+  if (rc) return rc;
+  rc = encode_tmap_2d(&tmA, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, A, uint64_t(K), uint64_t(M), uint64_t(K) * 4, 32, 16);
+  if (rc) return rc;
+  constexpr uint32_t attr_bit = 1u << 21;
+  if (!(c->func_attr_mask & attr_bit)) {
+    VT_CUDA(cudaFuncSetAttribute(sgemm_skinny_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 int(KU_SMEM_BYTES)));
+    c->func_attr_mask |= attr_bit;
+  }
+  sgemm_skinny_umma_kernel<<<ctas, KU_THREADS, KU_SMEM_BYTES, s>>>(tmB, tmA, C, partials, tickets, int(M), int(N), sc,
+                                                                    c->status);
+  count_launch();
+  VT_CUDA(cudaGetLastError());
+  return VT_OK;
+}
+
+}  // namespace vt

@@ -325,157 +325,6 @@ sgemm_skinny_reduce_kernel(const float* __restrict__ partials, float* __restrict
   reinterpret_cast<float4*>(C)[i] = s;
 }
 
-// ---------------------------------------------------------------------------------------------
-// Skinny on the tensor cores: the same CTA shape, cp.async ring and K split as sgemm_skinny_kernel,
-// but the 16 x 8 x 8 products go to mma.sync (m16n8k8, TF32) with the 3xTF32 split done in
-// registers: M = 16 is exactly the MMA's M, so nothing is padded.  tcgen05 is not used here
-// because its TF32 path needs K-major operands and B arrives N-major; mma.sync takes B fragments
-// element by element from shared memory, so no transposition is needed.  Each warp owns 32 of
-// the CTA's 128 columns for all 32 rows of a stage (no cross-warp fold).  Accumulators are folded
-// into fp32 registers after every stage so the truncating tensor-core accumulation never runs
-// longer than 32 values of K.
-// ---------------------------------------------------------------------------------------------
-constexpr int ST_STAGES = 3;                        // 3 x 23 KiB: three CTAs stay resident per SM
-constexpr int ST_BPITCH = SK_COLS + 8;             // floats; makes the B fragment loads bank-conflict free
-constexpr int ST_APITCH = 24;                      // floats per k row of the A slice (16 used)
-constexpr int ST_B_STAGE = SK_KC * ST_BPITCH;
-constexpr int ST_A_STAGE = SK_KC * ST_APITCH;      // one of hi / lo
-constexpr size_t ST_SMEM_BYTES = size_t(ST_STAGES) * (ST_B_STAGE + 2 * ST_A_STAGE) * sizeof(float);
-
-__device__ __forceinline__ uint32_t to_tf32(float x) {
-  uint32_t t;
-  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(t) : "f"(x));
-  return t;
-}
-__device__ __forceinline__ void mma_tf32_16x8x8(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-  asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
-
-__global__ void __launch_bounds__(SK_THREADS, 3)
-sgemm_skinny_tc_kernel(const float* __restrict__ A, const float* __restrict__ B, float* __restrict__ out, int M, int N,
-                       int K, int k_per_split) {
-  extern __shared__ __align__(16) float sk_smem[];
-  float* Bs = sk_smem;                                        // [stage][32][136]
-  float* Ah = sk_smem + ST_STAGES * ST_B_STAGE;               // [stage][32][24]  TF32-rounded A
-  float* Al = Ah + ST_STAGES * ST_A_STAGE;                    // [stage][32][24]  A - hi
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int g = lane >> 2, t = lane & 3;
-  const int n0 = blockIdx.x * SK_COLS;
-  const int kbeg = blockIdx.y * k_per_split;
-  const int kend = min(K, kbeg + k_per_split);
-  const int nchunks = kend > kbeg ? (kend - kbeg + SK_KC - 1) / SK_KC : 0;
-  const int a_m = tid >> 3, a_k = (tid & 7) * 4;
-
-  auto issue_b = [&](int chunk) {
-    float* dst = Bs + (chunk % ST_STAGES) * ST_B_STAGE;
-    const int k0 = kbeg + chunk * SK_KC;
-#pragma unroll
-    for (int i = 0; i < SK_KC * SK_COLS / 4 / SK_THREADS; ++i) {
-      const int idx = tid + SK_THREADS * i;
-      const int row = idx >> 5, c4 = (idx & 31) * 4;
-      const bool ok = (k0 + row < kend) && (n0 + c4 < N);
-      const float* src = ok ? B + size_t(k0 + row) * N + n0 + c4 : B;
-      cp_async_16_zfill(dst + row * ST_BPITCH + c4, src, ok);
-    }
-  };
-  auto load_a = [&](int chunk, float (&v)[4]) {
-    const int k0 = kbeg + chunk * SK_KC + a_k;
-#pragma unroll
-    for (int j = 0; j < 4; ++j) v[j] = (a_m < M && k0 + j < kend) ? __ldg(A + size_t(a_m) * K + k0 + j) : 0.f;
-  };
-  auto store_a = [&](int chunk, const float (&v)[4]) {
-    float* dh = Ah + (chunk % ST_STAGES) * ST_A_STAGE;
-    float* dl = Al + (chunk % ST_STAGES) * ST_A_STAGE;
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const float h = __uint_as_float(to_tf32(v[j]));
-      dh[(a_k + j) * ST_APITCH + a_m] = h;
-      dl[(a_k + j) * ST_APITCH + a_m] = v[j] - h;
-    }
-  };
-
-  float master[4][4];   // [n-tile][c0..c3]: rows g / g+8, columns 2t / 2t+1 of the warp's 32 columns
-#pragma unroll
-  for (int j = 0; j < 4; ++j)
-#pragma unroll
-    for (int e = 0; e < 4; ++e) master[j][e] = 0.f;
-
-  for (int c = 0; c < ST_STAGES - 1; ++c) {
-    if (c < nchunks) {
-      issue_b(c);
-      float v[4];
-      load_a(c, v);
-      store_a(c, v);
-    }
-    cp_async_commit();
-  }
-
-  for (int it = 0; it < nchunks; ++it) {
-    cp_async_wait<ST_STAGES - 2>();
-    __syncthreads();
-    const int nxt = it + ST_STAGES - 1;
-    float av[4];
-    const bool more = nxt < nchunks;
-    if (more) {
-      issue_b(nxt);
-      load_a(nxt, av);
-    }
-    cp_async_commit();
-
-    const float* bs = Bs + (it % ST_STAGES) * ST_B_STAGE + warp * 32 + g;
-    const float* ah = Ah + (it % ST_STAGES) * ST_A_STAGE;
-    const float* al = Al + (it % ST_STAGES) * ST_A_STAGE;
-    float acc[4][4];
-#pragma unroll
-    for (int j = 0; j < 4; ++j)
-#pragma unroll
-      for (int e = 0; e < 4; ++e) acc[j][e] = 0.f;
-#pragma unroll
-    for (int ks = 0; ks < SK_KC / 8; ++ks) {
-      const int kr = ks * 8 + t;
-      uint32_t fh[4], fl[4];   // A fragments: (g,t) (g+8,t) (g,t+4) (g+8,t+4)
-      fh[0] = __float_as_uint(ah[kr * ST_APITCH + g]);
-      fh[1] = __float_as_uint(ah[kr * ST_APITCH + g + 8]);
-      fh[2] = __float_as_uint(ah[(kr + 4) * ST_APITCH + g]);
-      fh[3] = __float_as_uint(ah[(kr + 4) * ST_APITCH + g + 8]);
-      fl[0] = __float_as_uint(al[kr * ST_APITCH + g]);
-      fl[1] = __float_as_uint(al[kr * ST_APITCH + g + 8]);
-      fl[2] = __float_as_uint(al[(kr + 4) * ST_APITCH + g]);
-      fl[3] = __float_as_uint(al[(kr + 4) * ST_APITCH + g + 8]);
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const float b0 = bs[kr * ST_BPITCH + j * 8];          // B[k = t][n = g] of this n-tile
-        const float b1 = bs[(kr + 4) * ST_BPITCH + j * 8];    // B[k = t+4][n = g]
-        const uint32_t b0h = to_tf32(b0), b1h = to_tf32(b1);
-        const uint32_t b0l = __float_as_uint(b0 - __uint_as_float(b0h));
-        const uint32_t b1l = __float_as_uint(b1 - __uint_as_float(b1h));
-        mma_tf32_16x8x8(acc[j], fl, b0h, b1h);   // small terms first
-        mma_tf32_16x8x8(acc[j], fh, b0l, b1l);
-        mma_tf32_16x8x8(acc[j], fh, b0h, b1h);
-      }
-    }
-#pragma unroll
-    for (int j = 0; j < 4; ++j)
-#pragma unroll
-      for (int e = 0; e < 4; ++e) master[j][e] += acc[j][e];
-    if (more) store_a(nxt, av);
-  }
-  cp_async_wait<0>();
-
-  // out is C itself (no K split) or the partial tile of this split: [split][M][N].
-  float* dst = out + size_t(blockIdx.y) * size_t(M) * size_t(N);
-#pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    const int col = n0 + warp * 32 + j * 8 + 2 * t;   // N % 4 == 0 and col even: the pair is in or out together
-    if (col < N) {
-      if (g < M) *reinterpret_cast<float2*>(dst + size_t(g) * N + col) = make_float2(master[j][0], master[j][1]);
-      if (g + 8 < M) *reinterpret_cast<float2*>(dst + size_t(g + 8) * N + col) = make_float2(master[j][2], master[j][3]);
-    }
-  }
-}
-
 template <int RM, int RN>
 int launch_tile(const float* A, const float* B, float* C, int M, int N, int K, cudaStream_t s) {
   constexpr int BM = 64 * RM, BN = 64 * RN;
@@ -527,7 +376,7 @@ size_t sgemm_skinny_partials_bytes(int64_t M, int64_t N, int64_t K, int sm_count
 }
 
 int launch_sgemm_skinny(DeviceCtx* c, const float* A, const float* B, float* C, float* partials, int64_t M,
-                        int64_t N, int64_t K, int ksplit, cudaStream_t s, bool tensor_cores) {
+                        int64_t N, int64_t K, int ksplit, cudaStream_t s) {
   (void)c;
   if (M > SK_M || N % 4 != 0) return fail(VT_ERR_UNSUPPORTED, "skinny kernel needs M <= 16 and N %% 4 == 0");
   if ((reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(C) | reinterpret_cast<uintptr_t>(partials)) & 15)
@@ -539,14 +388,8 @@ int launch_sgemm_skinny(DeviceCtx* c, const float* A, const float* B, float* C, 
   dim3 grid(unsigned((N + SK_COLS - 1) / SK_COLS), unsigned(ksplit));
   float* out = ksplit > 1 ? partials : C;
   // Opt in to 72 KiB of dynamic shared memory (a per-device function attribute; setting it again is harmless).
-  if (tensor_cores) {
-    VT_CUDA(cudaFuncSetAttribute(sgemm_skinny_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 int(ST_SMEM_BYTES)));
-    sgemm_skinny_tc_kernel<<<grid, SK_THREADS, ST_SMEM_BYTES, s>>>(A, B, out, int(M), int(N), int(K), k_per_split);
-  } else {
-    VT_CUDA(cudaFuncSetAttribute(sgemm_skinny_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(SK_SMEM_BYTES)));
-    sgemm_skinny_kernel<<<grid, SK_THREADS, SK_SMEM_BYTES, s>>>(A, B, out, int(M), int(N), int(K), k_per_split);
-  }
+  VT_CUDA(cudaFuncSetAttribute(sgemm_skinny_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(SK_SMEM_BYTES)));
+  sgemm_skinny_kernel<<<grid, SK_THREADS, SK_SMEM_BYTES, s>>>(A, B, out, int(M), int(N), int(K), k_per_split);
   count_launch();
   if (ksplit > 1) {
     const int64_t mn4 = M * N / 4;
@@ -636,5 +479,5 @@ extern "C" int vt_sgemm_skinny_static_scratch(int dev, const float* A, const flo
   // Every partial cell the reduce pass reads is written by the first pass of this same call, so
   // the previous call's leftovers in the array need no clearing.
   return launch_sgemm_skinny(nullptr, A, B, C, ksplit > 1 ? slot->ptr : nullptr, M, N, K, ksplit,
-                             static_cast<cudaStream_t>(stream), false);
+                             static_cast<cudaStream_t>(stream));
 }

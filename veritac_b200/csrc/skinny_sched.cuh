@@ -19,7 +19,7 @@ constexpr int SKINNY_KC = 32;      // rows of B per chunk
 struct SkinnySched {
   int slabs;      // S
   int chunks;     // chunks per slab (C)
-  int regular;    // regular CTAs per slab (p)
+  int regular;    // regular CTAs per slab (p); 0 when there are more slabs than CTAs
   int extras;     // CTAs left over (R = G - S * p)
   int bottom;     // chunks per slab left to the extras (L); the regular CTAs share [0, C - L)
 };
@@ -89,12 +89,16 @@ inline SkinnySched make_skinny_sched(int64_t N, int64_t K, int sm_count, int cta
   if (G > most) G = most;
   sc.slabs = int(S);
   sc.chunks = int(Cn);
-  if (S >= G) {
-    // Wide enough to fill the GPU with one CTA per slab (several waves when S is large).
-    G = S;
+  if (S == G) {
     sc.regular = 1;
     sc.extras = 0;
     sc.bottom = 0;
+  } else if (S > G) {
+    // More slabs than CTAs: no regular CTAs at all; every CTA takes an equal run of chunks in
+    // slab-major order (a slab and a part of the next, or several slabs), so there is no second wave.
+    sc.regular = 0;
+    sc.extras = int(G);
+    sc.bottom = int(Cn);
   } else {
     sc.regular = int(G / S);
     sc.extras = int(G - S * sc.regular);

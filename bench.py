@@ -200,6 +200,8 @@ class CpuArm:
     """Times rows [0, R) of the workload's product on the host cores; R is sized from a probe so one
     sample takes about `seconds`.  Rows are independent, so ops/s of the sample is ops/s of the job."""
 
+    kind_label = "port"
+
     def __init__(self, kind, M, N, K, seed):
         import numpy as np
 
@@ -253,11 +255,69 @@ class CpuArm:
         return "%s; rows [0,%d) of the %dx%dx%d product (all of B)" % (what, rows, self.M, self.N, self.K)
 
 
+class GeneratedCArm:
+    """The reference's own generated OpenMP C for a whole M = N = K product: `matmul()` printed by its
+    unmodified emitter for the README schedule and compiled ahead of time into oracle/_ref/ (doubles, row
+    stride 1000, as the reference lays its buffers out).  One unit of work is the whole product, timed the
+    way the reference's runner times it (clear C, call matmul)."""
+
+    kind_label = "reference"
+
+    def __init__(self, path, dim):
+        import numpy as np
+
+        self.np, self.dim = np, dim
+        self.lib = ctypes.CDLL(str(path))
+        self.lib.matmul.argtypes = [ctypes.c_void_p] * 3
+        try:
+            allowed = len(os.sched_getaffinity(0))
+        except AttributeError:
+            allowed = os.cpu_count() or 1
+        try:                                           # same OpenMP runtime as the loaded object
+            gomp = ctypes.CDLL("libgomp.so.1")
+            gomp.omp_set_num_threads(ctypes.c_int(allowed))
+            gomp.omp_get_max_threads.restype = ctypes.c_int
+            self.threads = int(gomp.omp_get_max_threads())
+        except OSError:
+            self.threads = int(os.environ.get("OMP_NUM_THREADS", allowed))
+        rng = np.random.default_rng(20260917)
+        self.A = np.zeros((dim, 1000)); self.B = np.zeros((dim, 1000)); self.C = np.zeros((dim, 1000))
+        self.A[:, :dim] = rng.random((dim, dim)) * 2 - 1
+        self.B[:, :dim] = rng.random((dim, dim)) * 2 - 1
+
+    def run_rows(self, reps: int) -> float:
+        t0 = time.perf_counter()
+        for _ in range(reps):
+            self.C[:] = 0
+            self.lib.matmul(self.A.ctypes.data, self.B.ctypes.data, self.C.ctypes.data)
+        return time.perf_counter() - t0
+
+    def size_sample(self, seconds: float) -> int:
+        self.run_rows(2)
+        t = self.run_rows(5) / 5
+        return max(5, int(min(seconds, 10.0) / max(t, 1e-6)))
+
+    def ops(self, reps: int) -> float:
+        return 2.0 * self.dim ** 3 * reps
+
+    def describe(self, reps: int) -> str:
+        return ("matmul() as printed by the reference's emitter for the README schedule (double, row stride 1000, "
+                "OpenMP), %d whole %d^3 products" % (reps, self.dim))
+
+
+def make_cpu_arm(args, kind, M, N, K):
+    """The reference's generated C where it was built for this exact shape, else the C restatement."""
+    ref = REPO / "oracle" / "_ref" / ("matmul_%d_readme.so" % M)
+    if kind == "f32" and M == N == K and ref.is_file():
+        return GeneratedCArm(ref, M)
+    return CpuArm(kind, M, N, K, seed=20260917)
+
+
 def run_reference_arm(args, kind, M, N, K, metric, unit):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return 0
-    arm = CpuArm(kind, M, N, K, seed=20260917)
+    arm = make_cpu_arm(args, kind, M, N, K)
     steps, warm = max(1, args.steps), max(0, args.warmup)
     rows = arm.size_sample(min(8.0, 120.0 / (steps + warm)))
     for _ in range(warm):
@@ -272,7 +332,7 @@ def run_reference_arm(args, kind, M, N, K, metric, unit):
         "vs_baseline": None, "dtype": "f32" if kind == "f32" else "s8->s32", "data": "synthetic",
         "config": {"workload": args.workload, "M": M, "N": N, "K": K,
                    "note": "CPU arm: each step is a bounded row sample of the workload on the host cores"},
-        "cpu_baseline": {"value": value, "unit": unit, "cores": arm.threads, "kind": "port",
+        "cpu_baseline": {"value": value, "unit": unit, "cores": arm.threads, "kind": arm.kind_label,
                          "sample": arm.describe(rows)},
         "e2e": {"value": value, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -473,11 +533,11 @@ def run_gpu_arm(args, kind, M, N, K, batch, metric, unit):
         "roofline": roof,
     }
     if world == 1 and not args.no_cpu_baseline:
-        arm = CpuArm(kind if kind != "i8b" else "i8", M * batch if kind == "i8b" else M, N, K, seed=20260917)
+        arm = make_cpu_arm(args, kind if kind != "i8b" else "i8", M * batch if kind == "i8b" else M, N, K)
         rows_cpu = arm.size_sample(12.0)
         t = arm.run_rows(rows_cpu)
         line["cpu_baseline"] = {"value": arm.ops(rows_cpu) / t / 1e12, "unit": unit, "cores": arm.threads,
-                                "kind": "port", "sample": arm.describe(rows_cpu), "seconds": t}
+                                "kind": arm.kind_label, "sample": arm.describe(rows_cpu), "seconds": t}
     print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()

@@ -74,6 +74,8 @@ enum {
 
 /* fp32 kernel variants.
  *   TILE128 / TILE64  register-tiled FFMA kernel (true fp32 arithmetic), 128x128 or 64x64 CTA tiles
+ *   TILE32            32x32 CTA tiles, K brought in 256 at a time and split four ways inside the CTA (true fp32):
+ *                     for products too small to fill the GPU with 64x64 tiles (N % 4 == 0, K % 4 == 0, aligned)
  *   SKINNY            M <= 16, N % 4 == 0: streams B once (HBM-bound), true fp32 FFMA arithmetic
  *   TF32X3            tensor cores, every operand split into TF32 hi + lo, three MMAs per product
  *                     (N % 4 == 0, K % 4 == 0, 16-byte aligned operands)
@@ -87,7 +89,8 @@ enum {
   VT_SGEMM_SKINNY = 3,
   VT_SGEMM_TF32X3 = 4,
   VT_SGEMM_SKINNY_TF32X3 = 5,
-  VT_SGEMM_SKINNY_MMA_SYNC = 6
+  VT_SGEMM_SKINNY_MMA_SYNC = 6,
+  VT_SGEMM_TILE32 = 7
 };
 
 /* Number of CUDA devices visible, or a negative VT_ERR_* code. */

@@ -19,12 +19,13 @@ def uniform(rng, shape):
     return (rng.random(shape, dtype=np.float32) * 2 - 1)
 
 
-@pytest.mark.parametrize("variant", [0, 1, 2, 4])
+@pytest.mark.parametrize("variant", [0, 1, 2, 4, 7])
 def test_shapes_against_float64(native, variant):
     rng = np.random.default_rng(20260917 + 1)
     for (m, n, k) in ((256, 256, 256), (1, 1, 1), (5, 3, 2), (77, 130, 33), (300, 200, 100), (128, 128, 16),
-                      (129, 127, 17), (512, 384, 1000), (1024, 1024, 1024), (64, 2048, 96)):
-        if variant == 4 and (n % 4 or k % 4):
+                      (129, 127, 17), (512, 384, 1000), (1024, 1024, 1024), (64, 2048, 96), (40, 36, 260), (512, 512, 512),
+                      (33, 4, 4)):
+        if variant in (4, 7) and (n % 4 or k % 4):
             with pytest.raises(native.NativeError):     # the tensor-core variant needs 16-byte row pitches
                 native.sgemm(uniform(rng, (m, k)), uniform(rng, (k, n)), np.zeros((m, n), np.float32), m, n, k,
                              variant=variant)
@@ -66,7 +67,7 @@ def test_config1_256_cubed_vs_generated_c(native, liboracle):
     liboracle.oracle_dgemm_tuned(a64.ctypes.data, b64.ctypes.data, ref_tuned.ctypes.data, m, n, k)
     liboracle.oracle_dgemm_naive(a64.ctypes.data, b64.ctypes.data, ref_naive.ctypes.data, m, n, k)
     assert relfro(ref_tuned, ref_naive) < 1e-14
-    for variant in (0, 1, 2, 4):
+    for variant in (0, 1, 2, 4, 7):
         c = np.zeros((m, n), dtype=np.float32)
         native.sgemm(a, b, c, m, n, k, variant=variant)
         assert relfro(c, ref_tuned) <= TOL and relfro(c, a64 @ b64) <= TOL

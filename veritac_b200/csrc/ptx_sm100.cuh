@@ -212,6 +212,21 @@ __device__ __forceinline__ uint64_t umma_smem_desc_sw128(uint32_t saddr, uint32_
   return d;
 }
 
+// MN-major 32-bit operand (the matrix dimension contiguous in memory, e.g. B[K][N] used as the N x K
+// operand): tcgen05 accepts it only in swizzle mode 1, "128 B with 32 B atoms" (TMA
+// CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B), as boxes of 32 elements x rows of K.  Leading offset = the
+// distance between boxes (32 more elements of the matrix dimension), stride offset = four rows of
+// K (512 B); a K step of 8 rows moves the start address by 1 KiB.
+__device__ __forceinline__ uint64_t umma_smem_desc_mn32(uint32_t saddr, uint32_t box_bytes) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((saddr & 0x3FFFFu) >> 4);
+  d |= static_cast<uint64_t>((box_bytes >> 4) & 0x3FFFu) << 16;
+  d |= static_cast<uint64_t>(512u >> 4) << 32;
+  d |= static_cast<uint64_t>(1) << 46;
+  d |= static_cast<uint64_t>(1) << 61;
+  return d;
+}
+
 // Instruction descriptor (32 bit), dense, no negate/saturate:
 //   [4,6) D format (1 = F32, 2 = S32)   [7,10) A format   [10,13) B format
 //   bit 15 A is MN-major   bit 16 B is MN-major   [17,23) N >> 3   [24,29) M >> 4

@@ -1,22 +1,22 @@
 // fp32 GEMM on the tensor cores by the 3xTF32 split: C = A*B with every fp32 operand written as
-// hi + lo, hi = the operand rounded to TF32 (10-bit mantissa), lo = operand - hi (exact in fp32), and
-//     A*B ~= Ahi*Bhi + Alo*Bhi + Ahi*Blo        (the dropped lo*lo term is ~2^-22 relative),
+// hi + lo, hi = the operand cut to TF32 (its top 19 bits), lo = operand - hi (exact in fp32), and
+//     A*B ~= Ahi*Bhi + Alo*Bhi + Ahi*Blo        (the dropped lo*lo term is ~2^-21 relative),
 // all three products accumulated in fp32 in one TMEM accumulator by tcgen05.mma.kind::tf32.
 // It replaces the same generated `matmul()` loop nest as the FFMA kernel
 // (reference specializations/cpu_gemm/emit_c.py:83-155, runner.py:155-190) and is used only where it
 // meets the 1e-5 relative-Frobenius contract; the tests hold it to that against float64.
 //
-// Two passes:
-//   split_tf32_kernel / split_transpose_tf32_kernel   one streaming pass per operand: A -> (Ahi, Alo)
-//                        as stored; B -> (Bhi, Blo) written transposed (N x K), because kind::tf32
-//                        with an MN-major B operand (B as stored) returned all zeros when measured
-//                        on B200, while K-major operands are exact.  HBM-bound, ~0.1-0.2 ms per
-//                        256 MiB operand, against several ms of GEMM.
+// Two kernels:
+//   lo_parts_kernel      one streaming pass that writes A lo and B lo.  There are no hi arrays: the
+//                        tensor core reads only the top 19 bits of a 32-bit TF32 operand, so A and B
+//                        themselves are the hi operands.  HBM-bound (reads and writes 4 bytes per
+//                        element of A and B), against several ms of GEMM.
 //   sgemm_tf32x3_pair_kernel   the CTA-pair pipeline of the int8 kernel (cta_group::2, 256x256 tile per
-//                        pair, TMA-staged 128-byte-swizzled operands, double-buffered TMEM
-//                        accumulator, TMA-store epilogue) with BK = 32 floats, four K-major operand
-//                        tiles per stage (Ahi, Alo, Bhi^T, Blo^T; 64 KiB per CTA, 3 stages) and three
-//                        MMAs per K step of 8.
+//                        pair, TMA-staged swizzled operands, double-buffered TMEM accumulator,
+//                        TMA-store epilogue) with BK = 32 floats, four operand tiles per stage (A,
+//                        A lo: K-major, 128-byte swizzle; B, B lo: as stored, N contiguous, which for
+//                        32-bit operands needs the "128 B swizzle with 32 B atoms" layout; 64 KiB per
+//                        CTA, 3 stages) and three MMAs per K step of 8.
 #include "ptx_sm100.cuh"
 #include "runtime.h"
 #include "umma_tile.cuh"
@@ -30,7 +30,8 @@ constexpr int T_STAGES = 3;
 constexpr int T_CHUNK_KB = 4;                   // K blocks (of 32) folded into one TMEM accumulator
 constexpr int T_THREADS = 384;                 // warpgroup 0: TMA warp, MMA warp, 2 idle; warpgroups 1-2: 8 epilogue warps
 constexpr int T_A_BYTES = 128 * T_BK * 4;      // 128 rows x 128 B = 16 KiB (hi or lo)
-constexpr int T_B_BYTES = 128 * T_BK * 4;      // this CTA's 128 columns of B as 128 rows of B^T (hi or lo)
+constexpr int T_B_BYTES = 128 * T_BK * 4;      // this CTA's 128 columns of B for 32 rows of K (B or B lo)
+constexpr int T_B_BOX_BYTES = 32 * T_BK * 4;   // one TMA box: 32 columns x 32 rows
 constexpr int T_STAGE_BYTES = 2 * T_A_BYTES + 2 * T_B_BYTES;   // 64 KiB
 
 struct TfPipeState {
@@ -44,47 +45,22 @@ struct TfPipeState {
 
 constexpr size_t T_SMEM_BYTES = 1024 + size_t(T_STAGES) * T_STAGE_BYTES + EPI_STAGING_BYTES + sizeof(TfPipeState);
 
-__global__ void __launch_bounds__(256) split_tf32_kernel(const float4* __restrict__ x, float4* __restrict__ hi,
-                                                         float4* __restrict__ lo, int64_t n4) {
-  const int64_t stride = int64_t(gridDim.x) * blockDim.x;
-  for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n4; i += stride) {
-    const float4 v = __ldcs(x + i);
-    float4 h, l;
-    uint32_t t;
-    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(t) : "f"(v.x)); h.x = __uint_as_float(t); l.x = v.x - h.x;
-    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(t) : "f"(v.y)); h.y = __uint_as_float(t); l.y = v.y - h.y;
-    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(t) : "f"(v.z)); h.z = __uint_as_float(t); l.z = v.z - h.z;
-    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(t) : "f"(v.w)); h.w = __uint_as_float(t); l.w = v.w - h.w;
-    hi[i] = h;
-    lo[i] = l;
-  }
+// lo parts of A and of B in one streaming pass: lo = x - (x cut to its top 19 bits), exact, with half
+// of its own cut-off unit added to the bit pattern so that the tensor core's cut rounds it to nearest.
+// The hi parts need no pass: the tensor core reads the top 19 bits of the operands as they are.
+__device__ __forceinline__ float tf32_lo_part(float x) {
+  const float hi = __uint_as_float(__float_as_uint(x) & 0xffffe000u);
+  return __uint_as_float(__float_as_uint(x - hi) + 0x1000u);
 }
-
-// B[K][N] -> Bhi^T[N][K], Blo^T[N][K] through a 32x32 shared-memory tile (both sides coalesced).
-__global__ void __launch_bounds__(256) split_transpose_tf32_kernel(const float* __restrict__ B, float* __restrict__ hiT,
-                                                                   float* __restrict__ loT, int K, int N) {
-  __shared__ float th[32][33];
-  __shared__ float tl[32][33];
-  const int n0 = blockIdx.x * 32, k0 = blockIdx.y * 32;
-  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;   // 32 x 8
-#pragma unroll
-  for (int r = ty; r < 32; r += 8) {
-    const int k = k0 + r, n = n0 + tx;
-    const float v = (k < K && n < N) ? __ldcs(B + size_t(k) * N + n) : 0.f;
-    uint32_t t;
-    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(t) : "f"(v));
-    const float h = __uint_as_float(t);
-    th[r][tx] = h;
-    tl[r][tx] = v - h;
-  }
-  __syncthreads();
-#pragma unroll
-  for (int r = ty; r < 32; r += 8) {
-    const int n = n0 + r, k = k0 + tx;
-    if (n < N && k < K) {
-      hiT[size_t(n) * K + k] = th[tx][r];
-      loT[size_t(n) * K + k] = tl[tx][r];
-    }
+__global__ void __launch_bounds__(256) lo_parts_kernel(const float4* __restrict__ a, float4* __restrict__ a_lo, int64_t na4,
+                                                      const float4* __restrict__ b, float4* __restrict__ b_lo, int64_t nb4) {
+  const int64_t stride = int64_t(gridDim.x) * blockDim.x;
+  for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < na4 + nb4; i += stride) {
+    const bool in_a = i < na4;
+    const float4 v = __ldcs(in_a ? a + i : b + (i - na4));
+    const float4 l = make_float4(tf32_lo_part(v.x), tf32_lo_part(v.y), tf32_lo_part(v.z), tf32_lo_part(v.w));
+    if (in_a) a_lo[i] = l;
+    else b_lo[i - na4] = l;
   }
 }
 
@@ -162,8 +138,11 @@ sgemm_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_
           const int k0 = kb * T_BK;
           tma_load_2d_pair(a_hi, &tmAh, full_even, k0, m0);
           tma_load_2d_pair(a_lo, &tmAl, full_even, k0, m0);
-          tma_load_2d_pair(b_hi, &tmBh, full_even, k0, n0);
-          tma_load_2d_pair(b_lo, &tmBl, full_even, k0, n0);
+#pragma unroll
+          for (int b = 0; b < 4; ++b) {   // this CTA's 128 columns of B as stored: four boxes of 32 columns x 32 rows
+            tma_load_2d_pair(b_hi + b * T_B_BOX_BYTES, &tmBh, full_even, n0 + 32 * b, k0);
+            tma_load_2d_pair(b_lo + b * T_B_BOX_BYTES, &tmBl, full_even, n0 + 32 * b, k0);
+          }
           if (++stage == T_STAGES) {
             stage = 0;
             phase ^= 1;
@@ -189,7 +168,7 @@ sgemm_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_
     // the epilogue warps add finished chunks into fp32 registers with round-to-nearest while the
     // next chunk runs in the other accumulator.
     if (lane == 0 && rank == 0) {
-      constexpr uint32_t idesc = umma_instr_desc(UMMA_D_F32, UMMA_AB_TF32, false, false, 256, 256);
+      constexpr uint32_t idesc = umma_instr_desc(UMMA_D_F32, UMMA_AB_TF32, false, true, 256, 256);
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
@@ -216,11 +195,12 @@ sgemm_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_
             const uint32_t b_lo = b_hi + T_B_BYTES;
 #pragma unroll
             for (int kk = 0; kk < T_BK / T_UMMA_K; ++kk) {
-              // All four tiles are K-major: 8 floats = 32 bytes per K step inside the swizzle row.
+              // A tiles are K-major: 8 floats = 32 bytes per K step inside the swizzle row.  B tiles
+              // are B as stored (N contiguous): a K step of 8 rows moves 1 KiB.
               const uint64_t ah = umma_smem_desc_sw128(a_hi + kk * 32, 16, 1024);
               const uint64_t al = umma_smem_desc_sw128(a_lo + kk * 32, 16, 1024);
-              const uint64_t bh = umma_smem_desc_sw128(b_hi + kk * 32, 16, 1024);
-              const uint64_t bl = umma_smem_desc_sw128(b_lo + kk * 32, 16, 1024);
+              const uint64_t bh = umma_smem_desc_mn32(b_hi + kk * 1024, T_B_BOX_BYTES);
+              const uint64_t bl = umma_smem_desc_mn32(b_lo + kk * 1024, T_B_BOX_BYTES);
               // small terms first, the dominant product last
               umma_tf32<2>(d_tmem, al, bh, idesc, uint32_t((kb != kb0) || kk != 0));
               umma_tf32<2>(d_tmem, ah, bl, idesc, 1u);
@@ -323,25 +303,21 @@ bool sgemm_tf32x3_supported(const float* A, const float* B, const float* C, int6
 }
 
 size_t sgemm_tf32x3_workspace_bytes(int64_t M, int64_t N, int64_t K) {
-  return 2 * (size_t(M) * K + size_t(K) * N) * sizeof(float);
+  return (size_t(M) * K + size_t(K) * N) * sizeof(float);
 }
 
-// `split` holds Ahi | Alo | Bhi | Blo back to back (sgemm_tf32x3_workspace_bytes).
+// `split` holds A lo | B lo back to back (sgemm_tf32x3_workspace_bytes).
 int launch_sgemm_tf32x3(DeviceCtx* c, const float* A, const float* B, float* C, float* split, int64_t M, int64_t N,
                         int64_t K, cudaStream_t s) {
   if (!sgemm_tf32x3_supported(A, B, C, M, N, K))
     return fail(VT_ERR_UNSUPPORTED, "3xTF32 kernel needs N %% 4 == 0, K %% 4 == 0 and 16-byte aligned operands");
   const size_t na = size_t(M) * K, nb = size_t(K) * N;
-  float* Ah = split;
-  float* Al = Ah + na;
-  float* Bh = Al + na;
-  float* Bl = Bh + nb;
+  float* Al = split;
+  float* Bl = Al + na;
   const int blocks = c->sm_count * 8;
-  split_tf32_kernel<<<blocks, 256, 0, s>>>(reinterpret_cast<const float4*>(A), reinterpret_cast<float4*>(Ah),
-                                           reinterpret_cast<float4*>(Al), int64_t(na / 4));
-  dim3 tgrid(unsigned((N + 31) / 32), unsigned((K + 31) / 32));
-  split_transpose_tf32_kernel<<<tgrid, 256, 0, s>>>(B, Bh, Bl, int(K), int(N));
-  count_launch(2);
+  lo_parts_kernel<<<blocks, 256, 0, s>>>(reinterpret_cast<const float4*>(A), reinterpret_cast<float4*>(Al), int64_t(na / 4),
+                                         reinterpret_cast<const float4*>(B), reinterpret_cast<float4*>(Bl), int64_t(nb / 4));
+  count_launch();
 
   TileRaster rs;
   rs.mt = int((M + 255) / 256);
@@ -353,10 +329,11 @@ int launch_sgemm_tf32x3(DeviceCtx* c, const float* A, const float* B, float* C, 
   CUtensorMap tmAh, tmAl, tmBh, tmBl, tmC;
   int rc = 0;
   const CUtensorMapDataType f32 = CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
-  if ((rc = encode_tmap_2d(&tmAh, f32, 4, Ah, uint64_t(K), uint64_t(M), uint64_t(K) * 4, T_BK, 128))) return rc;
+  const CUtensorMapSwizzle mn32 = CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B;
+  if ((rc = encode_tmap_2d(&tmAh, f32, 4, A, uint64_t(K), uint64_t(M), uint64_t(K) * 4, T_BK, 128))) return rc;
   if ((rc = encode_tmap_2d(&tmAl, f32, 4, Al, uint64_t(K), uint64_t(M), uint64_t(K) * 4, T_BK, 128))) return rc;
-  if ((rc = encode_tmap_2d(&tmBh, f32, 4, Bh, uint64_t(K), uint64_t(N), uint64_t(K) * 4, T_BK, 128))) return rc;
-  if ((rc = encode_tmap_2d(&tmBl, f32, 4, Bl, uint64_t(K), uint64_t(N), uint64_t(K) * 4, T_BK, 128))) return rc;
+  if ((rc = encode_tmap_2d(&tmBh, f32, 4, B, uint64_t(N), uint64_t(K), uint64_t(N) * 4, 32, T_BK, mn32))) return rc;
+  if ((rc = encode_tmap_2d(&tmBl, f32, 4, Bl, uint64_t(N), uint64_t(K), uint64_t(N) * 4, 32, T_BK, mn32))) return rc;
   if ((rc = encode_tmap_2d(&tmC, f32, 4, C, uint64_t(N), uint64_t(M), uint64_t(N) * 4, 32, 32))) return rc;
   if (!(c->func_attr_mask & 32u)) {
     VT_CUDA(cudaFuncSetAttribute(sgemm_tf32x3_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,

@@ -43,7 +43,7 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustain
 
 # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the ncu captures
 # summarised under profiles/; None until a capture exists for the workload.
-NCU_TRAFFIC_BYTES = {"sgemm_skinny": 273.9e6, "i8_8192": 611.1e6, "i8_batched_32": 654.4e6, "i8_batched": 8 * 654.4e6}
+NCU_TRAFFIC_BYTES = {"sgemm_skinny": 273.9e6, "i8_8192": 608.8e6, "i8_batched_32": 654.4e6, "i8_batched": 8 * 654.4e6}
 
 WORKLOADS = {
     # name: (kind, M, N, K, batch)
@@ -501,7 +501,7 @@ def run_gpu_arm(args, kind, M, N, K, batch, metric, unit):
             peak = peaks["bf16_tflops"] / 2.0 / 3.0
             roof = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
                     "peak_source": "%s bf16_tflops / 2 (TF32 rate) / 3 (MMAs per fp32 product); the step also holds the "
-                                   "two hi/lo split passes" % peaks_src,
+                                   "pass that writes the lo parts" % peaks_src,
                     "vs_ffma_pipe_74.45": achieved / NOMINAL_FP32_TFLOPS}
         else:
             roof = {"bound": "fp32", "achieved": achieved, "peak": NOMINAL_FP32_TFLOPS, "unit": "TFLOP/s",

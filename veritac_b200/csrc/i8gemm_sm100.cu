@@ -254,6 +254,9 @@ i8gemm_umma_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
   extern __shared__ uint8_t smem_raw[];
   uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* staging = tiles + size_t(P_STAGES) * P_STAGE_BYTES;
+  // C is written once and never read here: its lines should be the first to leave L2, so that A and B
+  // (128 MiB at 8192^3, about the size of L2) stay (measured +0.5 %).
+  const uint64_t store_policy = l2_policy_evict_first();
   PairPipeState<P_STAGES>* ps = reinterpret_cast<PairPipeState<P_STAGES>*>(staging + 4 * kBufs * EPI_BUF_BYTES);
   volatile int* abort_word = &ps->abort_word;
 
@@ -386,7 +389,8 @@ i8gemm_umma_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
       if (!__all_sync(0xffffffffu, ready)) break;
       tc_fence_after_sync();
       const uint32_t t_row = tmem_base + (uint32_t(q * 32) << 16) + uint32_t(acc * BN);
-      epilogue_warp_tile<kTmaStore, kBufs>(t_row, &tmC, staging + q * kBufs * EPI_BUF_BYTES, C, M, N, m0 + q * 32, n0, lane);
+      epilogue_warp_tile<kTmaStore, kBufs>(t_row, &tmC, staging + q * kBufs * EPI_BUF_BYTES, C, M, N, m0 + q * 32, n0, lane,
+                                           store_policy);
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive_remote(&ps->tmem_empty[acc], 0);

@@ -145,6 +145,20 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap* tmap, const void
                "r"(smem_u32(smem_src)), "r"(x), "r"(y)
                : "memory");
 }
+// L2 eviction-priority policy for bulk stores: data that is written once and never read again by
+// the kernel should leave L2 first.
+__device__ __forceinline__ uint64_t l2_policy_evict_first() {
+  uint64_t p;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+  return p;
+}
+__device__ __forceinline__ void tma_store_2d_hint(const CUtensorMap* tmap, const void* smem_src, int32_t x, int32_t y,
+                                                  uint64_t policy) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group.L2::cache_hint [%0, {%2, %3}], [%1], %4;" ::"l"(
+                   reinterpret_cast<uint64_t>(tmap)),
+               "r"(smem_u32(smem_src)), "r"(x), "r"(y), "l"(policy)
+               : "memory");
+}
 __device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 // Waits until at most kPending of this thread's committed store groups still read shared memory.
 template <int kPending>

@@ -48,7 +48,7 @@ __device__ __forceinline__ void tile_coords(const TileRaster& rs, int t, int& mi
 template <bool kTmaStore, int kBufs = 2>
 __device__ __forceinline__ void epilogue_warp_tile(uint32_t t_row, const CUtensorMap* tmC, uint8_t* staging,
                                                    int32_t* __restrict__ C, int M, int N, int row0, int n0,
-                                                   int lane) {
+                                                   int lane, uint64_t store_policy = 0) {
   const int row = row0 + lane;
 #pragma unroll 1
   for (int c = 0; c < BN / 32; ++c) {
@@ -66,7 +66,10 @@ __device__ __forceinline__ void epilogue_warp_tile(uint32_t t_row, const CUtenso
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) {
-        if (row0 < M && n0 + c * 32 < N) tma_store_2d(tmC, buf, n0 + c * 32, row0);
+        if (row0 < M && n0 + c * 32 < N) {
+          if (store_policy) tma_store_2d_hint(tmC, buf, n0 + c * 32, row0, store_policy);
+          else tma_store_2d(tmC, buf, n0 + c * 32, row0);
+        }
         tma_store_commit();
       }
     } else {

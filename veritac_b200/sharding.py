@@ -60,8 +60,9 @@ def init_process_group(backend: str | None = None, timeout_s: float = 120.0):
         torch.cuda.set_device(local)
     os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
     if not dist.is_initialized():
+        extra = {"device_id": torch.device("cuda", local)} if backend == "nccl" else {}
         dist.init_process_group(backend=backend, rank=rank, world_size=world,
-                                timeout=datetime.timedelta(seconds=timeout_s))
+                                timeout=datetime.timedelta(seconds=timeout_s), **extra)
     return rank, world, local
 
 

@@ -37,6 +37,11 @@ def golden_gemmini():
 
 
 @pytest.fixture(scope="session")
+def golden_learned_streams():
+    return json.loads((GOLDEN / "learned_streams.json").read_text())
+
+
+@pytest.fixture(scope="session")
 def golden_cpu_gemm():
     return json.loads((GOLDEN / "cpu_gemm.json").read_text())
 

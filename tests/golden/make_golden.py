@@ -1,4 +1,4 @@
-"""Regenerates tests/golden/gemmini.json and tests/golden/cpu_gemm.json from the reference tree.
+"""Regenerates tests/golden/gemmini.json, cpu_gemm.json and learned_streams.json from the reference tree.
 
 Needs the reference checkout (default /root/reference, or REFERENCE_ROOT) — it is imported and its
 recorded evidence files are read — so it runs only where that tree exists; the fixtures it writes are
@@ -219,6 +219,50 @@ def gemmini_fixture() -> dict:
     return out
 
 
+def learned_streams_fixture() -> dict:
+    """Command streams printed by the reference's learned-strategy generators (specializations/gemmini_gemm/
+    learned_strategies.py:19-193: batched A reuse, resident A, resident A with row batches, serpentine B
+    cache) with what the reference's interpreter makes of them.  The streams are data for the executor
+    tests; the generators themselves are not part of this package."""
+    from specializations.gemmini_gemm import learned_strategies as ls
+
+    cases = []
+
+    def add(name, plan, cmds):
+        m, n, k = plan["m"], plan["n"], plan["k"]
+        entry = {"generator": name, "plan": plan, "commands": g.serialize_commands(cmds),
+                 "command_sha256": lowering.command_hash(cmds), "counts": g.modeled_counts(cmds), "runs": []}
+        for mode, seed in (("lcg", 3), ("minmax", 0), ("min", 0)):
+            A, B = g.deterministic_inputs(m, n, k, seed, mode)
+            try:
+                C, stats = g.run_commands(cmds, plan, A, B)
+                assert C == g.scalar_matmul(A, B, m, n, k)
+                entry["runs"].append({"mode": mode, "seed": seed, "stats": stats, "output_sha256": sha(C)})
+            except g.GemminiError as exc:
+                entry["runs"].append({"mode": mode, "seed": seed, "error": str(exc)})
+        cases.append(entry)
+
+    def plan_for(m, n, k, acc, spad):
+        plan = g.make_plan(m, n, k, g.SCHEDULE_BASELINE)
+        plan["accumulator_rows"], plan["scratchpad_rows"] = acc, spad
+        return plan
+
+    for (m, n, k, acc, batch) in ((32, 48, 48, 48, 3), (48, 80, 32, 32, 2), (16, 80, 32, 80, 5), (32, 32, 64, 16, 2)):
+        plan = plan_for(m, n, k, acc, 32)
+        add("gen_batched_reuse_a(batch_columns=%d)" % batch, plan, ls.gen_batched_reuse_a(plan, batch))
+    for (m, n, k) in ((32, 48, 48), (16, 80, 32), (48, 32, 64)):
+        plan = plan_for(m, n, k, 16, k + 16)
+        add("gen_resident_a", plan, ls.gen_resident_a(plan))
+    for (m, n, k, acc, batch) in ((48, 32, 32, 32, 2), (80, 16, 32, 48, 3), (64, 48, 48, 64, 4)):
+        plan = plan_for(m, n, k, acc, k + 16)
+        add("gen_resident_a_batched_rows(batch_rows=%d)" % batch, plan, ls.gen_resident_a_batched_rows(plan, batch))
+    for (m, n, k) in ((48, 32, 32), (32, 48, 48), (64, 64, 64), (16, 32, 48)):
+        plan = plan_for(m, n, k, 16, k + 16)
+        add("gen_serpentine_b_cache", plan, ls.gen_serpentine_b_cache(plan))
+    # select_learned_strategy needs the reference's native program checker, which cannot be built here.
+    return {"source": "CuteCake/VeriTac reference tree; see make_golden.py", "cases": cases}
+
+
 def cpu_gemm_fixture() -> dict:
     out = {"source": "CuteCake/VeriTac reference tree; see make_golden.py"}
 
@@ -277,4 +321,5 @@ def cpu_gemm_fixture() -> dict:
 if __name__ == "__main__":
     (HERE / "gemmini.json").write_text(json.dumps(gemmini_fixture(), indent=1, sort_keys=True) + "\n")
     (HERE / "cpu_gemm.json").write_text(json.dumps(cpu_gemm_fixture(), indent=1, sort_keys=True) + "\n")
+    (HERE / "learned_streams.json").write_text(json.dumps(learned_streams_fixture(), sort_keys=True) + "\n")
     print("wrote", HERE / "gemmini.json", HERE / "cpu_gemm.json")

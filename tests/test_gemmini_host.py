@@ -214,6 +214,32 @@ def test_recorded_programs_replay_to_plain_gemm(golden_gemmini):
             assert replay.stats == run["cases"][0]["stats"]
 
 
+def test_learned_strategy_streams_replay_like_the_reference(golden_learned_streams):
+    """Streams printed by the reference's learned-strategy generators (batched A reuse, resident A, row
+    batches over a resident A, serpentine B cache: scratchpad rows change roles between A and B tiles) go
+    through the symbolic replay with the reference's counts and stats, or its refusal."""
+    for case in golden_learned_streams["cases"]:
+        plan = case["plan"]
+        cmds = commands_from_dicts(case["commands"])
+        assert lowering.command_hash(cmds) == case["command_sha256"], case["generator"]
+        assert g.modeled_counts(cmds) == case["counts"]
+        replay = g._Replay(plan)
+        if "error" in case["runs"][0]:
+            with pytest.raises(g.GemminiError) as info:
+                for c in cmds:
+                    replay.step(c)
+                replay.finish()
+            assert str(info.value) == case["runs"][0]["error"]
+            continue
+        for c in cmds:
+            replay.step(c)
+        replay.finish()
+        assert replay.stats == case["runs"][0]["stats"], case["generator"]
+        # every output tile gets each K tile of its row of A and column of B exactly once
+        it, jt, kt = plan["m"] // 16, plan["n"] // 16, plan["k"] // 16
+        assert len(replay.tiles) == it * jt
+
+
 def test_batched_generator_argument_checks():
     plan = g.make_plan(32, 32, 32, "baseline")
     for bad in (0, -1, 1.0, True, None):

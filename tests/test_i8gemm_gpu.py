@@ -56,6 +56,23 @@ def test_recorded_output_hashes(native, g, golden_gemmini):
             assert sha(C) == case["output_sha256"] and stats == case["stats"]
 
 
+def test_learned_strategy_streams_on_the_gpu(native, g, golden_learned_streams):
+    """14 streams from the reference's learned-strategy generators, executed here: same output hashes and
+    stats as the reference's interpreter recorded, same refusal for the oversized batch."""
+    for case in golden_learned_streams["cases"]:
+        p = case["plan"]
+        cmds = commands_from_dicts(case["commands"])
+        for run in case["runs"]:
+            A, B = g.deterministic_inputs(p["m"], p["n"], p["k"], run["seed"], run["mode"])
+            if "error" in run:
+                with pytest.raises(g.GemminiError) as info:
+                    g.run_commands(cmds, p, A, B)
+                assert str(info.value) == run["error"]
+                continue
+            C, stats = g.run_commands(cmds, p, A, B)
+            assert sha(C) == run["output_sha256"] and stats == run["stats"], case["generator"]
+
+
 def test_generator_streams_match_reference_interpreter(native, g, lowering, golden_gemmini):
     for e in golden_gemmini["generators"]:
         if "runs" not in e:

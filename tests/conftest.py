@@ -37,6 +37,11 @@ def golden_gemmini():
 
 
 @pytest.fixture(scope="session")
+def golden_schedule_ir():
+    return json.loads((GOLDEN / "schedule_ir.json").read_text())
+
+
+@pytest.fixture(scope="session")
 def golden_learned_streams():
     return json.loads((GOLDEN / "learned_streams.json").read_text())
 

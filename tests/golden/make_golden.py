@@ -1,4 +1,5 @@
-"""Regenerates tests/golden/gemmini.json, cpu_gemm.json and learned_streams.json from the reference tree.
+"""Regenerates tests/golden/gemmini.json, cpu_gemm.json, learned_streams.json and schedule_ir.json from the
+reference tree.
 
 Needs the reference checkout (default /root/reference, or REFERENCE_ROOT) — it is imported and its
 recorded evidence files are read — so it runs only where that tree exists; the fixtures it writes are
@@ -263,6 +264,79 @@ def learned_streams_fixture() -> dict:
     return {"source": "CuteCake/VeriTac reference tree; see make_golden.py", "cases": cases}
 
 
+def schedule_ir_fixture() -> dict:
+    """What the reference's compact-schedule adapter (specializations/gemmini_gemm/schedule_ir.py) makes of
+    a list of expressions and programs: values, expansions, refusal texts."""
+    from specializations.gemmini_gemm import schedule_ir as ir
+
+    env = {"i": 1, "M": 32, "N": 16, "K": 32}
+    texts = ["1", "i", "i*16", "i * 16 * N", "0xA0000000 if i == 0 else 0xE0000000", "K // 16", "i > 0",
+             "10 if i == 0 else 20", "M.bit_length()", "2 ** 10", "M[0]", "1 / 2", "True + 1", "1 // 0", "1 << 9",
+             "0 if True else int('1')", "0 if True else missing", "", " 1", "1 ", "1 # c", "1\n+2", "(1\n+2)", "--1",
+             "not True", "1 < 2 < 3", "0 if True else 1 < 2 < 3", "1 == True", "True == True", "1 if 1 else 2",
+             "18446744073709551615", "18446744073709551616", "18446744073709551615 + 1", "1.0", "'a'", "(1,)", "None",
+             "-5 // 2", "-5 % 3", "M % 0", "1 if i > 0 else 2 if i < 0 else 3", "1 if 1 == 1 else 1 // 0", "-True",
+             "True < 2", "x := 1", "(x := 1)", "M" * 300, "-" * 20 + "1", "1" + " + 1" * 20, "017", "1_000", "0b101"]
+    expressions = []
+    for text in texts:
+        try:
+            v = ir.expression(text, env)
+            expressions.append({"text": text, "value": v, "is_bool": type(v) is bool})
+        except ir.ScheduleError as exc:
+            expressions.append({"text": text, "error": str(exc)})
+
+    def loop(var, stop, body, start=0, step=1):
+        return {"for": var, "start": start, "stop": stop, "step": step, "body": body}
+
+    plan = g.make_plan(32, 32, 64, g.SCHEDULE_BASELINE)
+    flat = g.serialize_commands(g.gen_commands(plan))
+    # the baseline stream of the plan written as i, j, k loops over one tile's four commands + its mvout
+    inner = [dict(c) for c in flat[4:8]]
+    inner[0]["offset"] = {"expr": "(i * 16) * K + kk * 16"}
+    inner[1]["offset"] = {"expr": "(kk * 16) * N + j * 16"}
+    inner[2]["out_addr"] = {"expr": "0xA0000000 if kk == 0 else 0xE0000000"}
+    mvout = dict(flat[4 + 4 * (plan["k"] // 16)])
+    mvout["buf_offset"] = {"expr": "(i * 16) * N + j * 16"}
+    compact = flat[:4] + [loop("i", {"expr": "M // 16"}, [loop("j", {"expr": "N // 16"}, [
+        loop("kk", {"expr": "K // 16"}, inner), mvout])])] + flat[-1:]
+    programs = [
+        {"name": "baseline_32x32x64_as_loops", "program": compact, "constants": {"M": 32, "N": 32, "K": 64}, "limits": {},
+         "plan": plan},
+        {"name": "scoped_variable", "program": [loop("i", {"expr": "M // 16"}, [{"kind": "mvin", "offset": {"expr": "i * 16"},
+                                                                                   "buf": "A"}]),
+                                                 {"kind": "x", "offset": {"expr": "i"}}], "constants": {"M": 32}, "limits": {}},
+        {"name": "negative_step", "program": [loop("i", -2, [{"kind": "x", "i": {"expr": "i"}}], 5, -2)], "constants": {},
+         "limits": {}},
+        {"name": "empty_body_budget", "program": [loop("i", 1000000000, [])], "constants": {},
+         "limits": {"max_commands": 3, "max_iterations": 10}},
+        {"name": "command_budget", "program": [loop("i", 5, [{"kind": "fence"}])], "constants": {},
+         "limits": {"max_commands": 3, "max_iterations": 10}},
+        {"name": "shadowing", "program": [loop("i", 2, [])], "constants": {"i": 1}, "limits": {}},
+        {"name": "boolean_bound", "program": [loop("i", True, [])], "constants": {}, "limits": {}},
+        {"name": "zero_step", "program": [loop("i", 4, [], 0, 0)], "constants": {}, "limits": {}},
+        {"name": "extra_loop_field", "program": [dict(loop("i", 2, []), note=1)], "constants": {}, "limits": {}},
+        {"name": "field_object", "program": [{"kind": "x", "v": {"expr": "1", "more": 2}}], "constants": {}, "limits": {}},
+        {"name": "float_and_string_fields", "program": [{"kind": "config_ld", "scale": 1.0, "buf": "A", "flag": True}],
+         "constants": {}, "limits": {}},
+        {"name": "no_kind", "program": [{"offset": 1}], "constants": {}, "limits": {}},
+        {"name": "bad_constant", "program": [], "constants": {"M": 1.5}, "limits": {}},
+        {"name": "nesting", "program": [loop("a", 1, [loop("b", 1, [loop("c", 1, [{"kind": "x"}])])])], "constants": {},
+         "limits": {"max_depth": 2}},
+    ]
+    for p in programs:
+        try:
+            expanded = ir.expand_program(p["program"], p["constants"], **p["limits"])
+            p["expanded_sha256"] = sha_bytes(json.dumps(expanded, sort_keys=True).encode())   # key order is not data
+            p["expanded_len"] = len(expanded)
+            if len(expanded) <= 8:
+                p["expanded"] = expanded
+        except ir.ScheduleError as exc:
+            p["error"] = str(exc)
+    assert programs[0]["expanded_sha256"] == sha_bytes(json.dumps(flat, sort_keys=True).encode())
+    return {"source": "CuteCake/VeriTac reference tree; see make_golden.py", "bindings": env, "expressions": expressions,
+            "programs": programs}
+
+
 def cpu_gemm_fixture() -> dict:
     out = {"source": "CuteCake/VeriTac reference tree; see make_golden.py"}
 
@@ -322,4 +396,5 @@ if __name__ == "__main__":
     (HERE / "gemmini.json").write_text(json.dumps(gemmini_fixture(), indent=1, sort_keys=True) + "\n")
     (HERE / "cpu_gemm.json").write_text(json.dumps(cpu_gemm_fixture(), indent=1, sort_keys=True) + "\n")
     (HERE / "learned_streams.json").write_text(json.dumps(learned_streams_fixture(), sort_keys=True) + "\n")
+    (HERE / "schedule_ir.json").write_text(json.dumps(schedule_ir_fixture(), indent=1, sort_keys=True) + "\n")
     print("wrote", HERE / "gemmini.json", HERE / "cpu_gemm.json")

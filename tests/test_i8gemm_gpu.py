@@ -56,6 +56,25 @@ def test_recorded_output_hashes(native, g, golden_gemmini):
             assert sha(C) == case["output_sha256"] and stats == case["stats"]
 
 
+def test_compact_schedule_expands_and_runs(native, g, golden_schedule_ir):
+    """A loop-form schedule goes through the adapter, the strict command objects and the GPU; the
+    search controller's interpretation step reports it as matching the reference product."""
+    from veritac_b200.specializations.gemmini_gemm import evaluation, schedule_ir
+
+    p = golden_schedule_ir["programs"][0]
+    plan = p["plan"]
+    cmds = commands_from_dicts(schedule_ir.expand_program(p["program"], p["constants"]))
+    A, B = g.deterministic_inputs(plan["m"], plan["n"], plan["k"], 11)
+    C, stats = g.run_commands(cmds, plan, A, B)
+    assert C == go.scalar_matmul(A, B, plan["m"], plan["n"], plan["k"])
+    assert evaluation.interpret_commands(plan, cmds) == {"ran": True, "matches_reference": True}
+    broken = cmds[:-2] + cmds[-1:]          # the last tile is never moved out
+    got = evaluation.interpret_commands(plan, broken)
+    assert got["ran"] is True and got["matches_reference"] is False and "error" in got
+    assert evaluation.interpret_commands(plan, cmds, interpret_macs_limit=1000) == {
+        "ran": False, "reason": "skipped: 65536 modeled MACs exceed the interpretation bound 1000"}
+
+
 def test_learned_strategy_streams_on_the_gpu(native, g, golden_learned_streams):
     """14 streams from the reference's learned-strategy generators, executed here: same output hashes and
     stats as the reference's interpreter recorded, same refusal for the oversized batch."""

@@ -15,6 +15,27 @@ from . import backend as g
 from .lowering import command_hash, gen_batched_reuse_b
 
 
+DEFAULT_INTERPRET_MACS_LIMIT = 4_000_000
+
+
+def interpret_commands(plan, commands, interpret_macs_limit=DEFAULT_INTERPRET_MACS_LIMIT):
+    """Exact interpretation of a candidate stream on the deterministic inputs, as the reference's search
+    controller does for every natively accepted candidate (blind_search.py:959-976, bound :65): the same
+    result dictionary (`ran`, `matches_reference`, `error` / `reason`), with the stream executed on the
+    GPU by `run_commands` and compared with `scalar_matmul`.  Diagnostic only, like the original: it never
+    stands in for the plan checker."""
+    macs = plan["m"] * plan["n"] * plan["k"]
+    if macs > interpret_macs_limit:
+        return {"ran": False,
+                "reason": "skipped: %d modeled MACs exceed the interpretation bound %d" % (macs, interpret_macs_limit)}
+    A, B = g.deterministic_inputs(plan["m"], plan["n"], plan["k"], 0)
+    try:
+        C, _stats = g.run_commands(commands, plan, A, B)
+    except g.GemminiError as exc:
+        return {"ran": True, "matches_reference": False, "error": str(exc)}
+    return {"ran": True, "matches_reference": C == g.scalar_matmul(A, B, plan["m"], plan["n"], plan["k"])}
+
+
 def objective(commands):
     counts = g.modeled_counts(commands)
     return (counts["dma_in_elems_int8"], counts["instructions"])

@@ -7,7 +7,9 @@
 //       (64*RM)x(64*RN).  K is consumed 16 at a time through two shared-memory buffers: global loads
 //       for step t+1 are issued into registers before the FFMAs of step t and stored (A transposed
 //       so the inner loop reads float4s along M) after them, one __syncthreads per step.
-//   sgemm_skinny_kernel       M <= 16 ("decode-like"): HBM-bound, B is streamed exactly once.  A CTA owns
+//   sgemm_small_kernel        products too small to fill the GPU with 64x64 tiles: 32x32 CTA tile, K in
+//       bursts of 256 split four ways inside the CTA (described at the kernel).
+//   sgemm_skinny_kernel       M <= 16 ("decode-like") in true fp32: B is streamed exactly once.  A CTA owns
 //       128 columns and a K range; B rows arrive through a 4-stage cp.async ring, its 4 warps take
 //       8-row slices of each 32-row stage, keep 16x4 accumulators per thread, and fold through shared memory.  With a K split the
 //       per-split partial tiles go to scratch memory and a second kernel sums them in split order

@@ -32,6 +32,10 @@ def install_aliases(force: bool = False) -> None:
         if present is not None and present is not mod and not force:
             raise ImportError("a different top-level module %r is already imported" % name)
         sys.modules[name] = mod
-    for sub in ("cpu_gemm", "gemmini_gemm"):
+    for sub, leaves in (("cpu_gemm", ("lower", "emit_c", "runner", "recognise")),
+                        ("gemmini_gemm", ("backend", "lowering", "evaluation", "schedule_ir"))):
         sys.modules["specializations." + sub] = importlib.import_module(__name__ + ".specializations." + sub)
+        for leaf in leaves:    # one module object per file, whichever name it is imported under
+            sys.modules["specializations.%s.%s" % (sub, leaf)] = importlib.import_module(
+                "%s.specializations.%s.%s" % (__name__, sub, leaf))
     sys.modules["specializations.catalog"] = importlib.import_module(__name__ + ".specializations.catalog")

@@ -159,6 +159,39 @@ int i8gemm_from_host(DeviceCtx* c, const int8_t* A, const int8_t* B, int32_t* C,
   return ctx_check_status(c, c->stream);
 }
 
+// Host-pointer fp32 GEMM on the 3xTF32 path, pipelined like the int8 one: B goes in whole and its lo
+// part is written once; A then arrives in row blocks, and each block's lo pass, GEMM and the copy of
+// its rows of C overlap the arrival of the next block.
+int sgemm_tf32x3_from_host(DeviceCtx* c, const float* A, const float* B, float* C, int64_t M, int64_t N, int64_t K) {
+  int64_t rows = ((M / 8 + 255) / 256) * 256;
+  if (rows < 512) rows = 512;
+  float* dA = static_cast<float*>(ctx_workspace(c, 0, size_t(M) * K * 4));
+  float* dB = static_cast<float*>(ctx_workspace(c, 1, size_t(K) * N * 4));
+  float* dC = static_cast<float*>(ctx_workspace(c, 2, size_t(M) * N * 4));
+  float* split = static_cast<float*>(ctx_workspace(c, 3, sgemm_tf32x3_workspace_bytes(rows, N, K)));
+  if (!dA || !dB || !dC || !split) return VT_ERR_CUDA;
+  cudaEvent_t ev_in = c->ev[1], ev_k = c->ev[2], ev_done = c->ev[3];
+  VT_CUDA(cudaMemcpyAsync(dB, B, size_t(K) * N * 4, cudaMemcpyHostToDevice, c->copy_in));
+  VT_CUDA(cudaEventRecord(ev_in, c->copy_in));
+  VT_CUDA(cudaStreamWaitEvent(c->stream, ev_in, 0));
+  int rc = launch_sgemm_tf32x3(c, dA, dB, dC, split, 0, N, K, c->stream, 2);   // B lo only
+  if (rc) return rc;
+  for (int64_t r0 = 0; r0 < M; r0 += rows) {
+    const int64_t r = (M - r0 < rows) ? (M - r0) : rows;
+    VT_CUDA(cudaMemcpyAsync(dA + r0 * K, A + r0 * K, size_t(r) * K * 4, cudaMemcpyHostToDevice, c->copy_in));
+    VT_CUDA(cudaEventRecord(ev_in, c->copy_in));
+    VT_CUDA(cudaStreamWaitEvent(c->stream, ev_in, 0));
+    rc = launch_sgemm_tf32x3(c, dA + r0 * K, dB, dC + r0 * N, split, r, N, K, c->stream, 1);   // this block's A lo
+    if (rc) return rc;
+    VT_CUDA(cudaEventRecord(ev_k, c->stream));
+    VT_CUDA(cudaStreamWaitEvent(c->copy_out, ev_k, 0));
+    VT_CUDA(cudaMemcpyAsync(C + r0 * N, dC + r0 * N, size_t(r) * N * 4, cudaMemcpyDeviceToHost, c->copy_out));
+  }
+  VT_CUDA(cudaEventRecord(ev_done, c->copy_out));
+  VT_CUDA(cudaStreamWaitEvent(c->stream, ev_done, 0));
+  return ctx_check_status(c, c->stream);
+}
+
 }  // namespace
 
 extern "C" {
@@ -284,6 +317,11 @@ int vt_sgemm(int dev, const float* A, const float* B, float* C, int64_t M, int64
   DeviceCtx* c = ctx_for(dev);
   if (!c) return VT_ERR_CUDA;
   cudaStream_t s = where == VT_HOST ? c->stream : pick_stream(c, stream);
+
+  // Large host-buffer products on the tensor-core path are pipelined against the PCIe copies.
+  if (where == VT_HOST && (variant == VT_SGEMM_AUTO || variant == VT_SGEMM_TF32X3) && M >= 1024 && N >= 256 && K >= 256 &&
+      double(M) * double(N) * double(K) >= 5.0e8 && N % 4 == 0 && K % 4 == 0)
+    return sgemm_tf32x3_from_host(c, A, B, C, M, N, K);
 
   const float* dA = A;
   const float* dB = B;

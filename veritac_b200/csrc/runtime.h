@@ -75,7 +75,7 @@ int launch_sgemm_skinny(DeviceCtx* c, const float* A, const float* B, float* C, 
 bool sgemm_tf32x3_supported(const float* A, const float* B, const float* C, int64_t M, int64_t N, int64_t K);
 size_t sgemm_tf32x3_workspace_bytes(int64_t M, int64_t N, int64_t K);
 int launch_sgemm_tf32x3(DeviceCtx* c, const float* A, const float* B, float* C, float* split, int64_t M, int64_t N,
-                        int64_t K, cudaStream_t s);
+                        int64_t K, cudaStream_t s, int parts = 3);
 void sgemm_skinny_tma_plan(int64_t N, int64_t K, int sm_count, int* ctas, int* slabs, int* max_parts);
 bool sgemm_skinny_tma_supported(const float* B, const float* C, int64_t M, int64_t N, int64_t K);
 int launch_sgemm_skinny_tma(DeviceCtx* c, const float* A, const float* B, float* C, float* partials, int* tickets,

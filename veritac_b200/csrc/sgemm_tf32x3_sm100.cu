@@ -306,18 +306,24 @@ size_t sgemm_tf32x3_workspace_bytes(int64_t M, int64_t N, int64_t K) {
   return (size_t(M) * K + size_t(K) * N) * sizeof(float);
 }
 
-// `split` holds A lo | B lo back to back (sgemm_tf32x3_workspace_bytes).
+// `split` holds B lo | A lo back to back (sgemm_tf32x3_workspace_bytes); B lo comes first so that callers
+// who feed A in row blocks against one B keep B lo where it is.
+//   parts: 1 = write A lo, 2 = write B lo, 3 = both (the whole product in one call)
 int launch_sgemm_tf32x3(DeviceCtx* c, const float* A, const float* B, float* C, float* split, int64_t M, int64_t N,
-                        int64_t K, cudaStream_t s) {
+                        int64_t K, cudaStream_t s, int parts) {
   if (!sgemm_tf32x3_supported(A, B, C, M, N, K))
     return fail(VT_ERR_UNSUPPORTED, "3xTF32 kernel needs N %% 4 == 0, K %% 4 == 0 and 16-byte aligned operands");
   const size_t na = size_t(M) * K, nb = size_t(K) * N;
-  float* Al = split;
-  float* Bl = Al + na;
-  const int blocks = c->sm_count * 8;
-  lo_parts_kernel<<<blocks, 256, 0, s>>>(reinterpret_cast<const float4*>(A), reinterpret_cast<float4*>(Al), int64_t(na / 4),
-                                         reinterpret_cast<const float4*>(B), reinterpret_cast<float4*>(Bl), int64_t(nb / 4));
-  count_launch();
+  float* Bl = split;
+  float* Al = Bl + nb;
+  if (parts & 3) {
+    const int blocks = c->sm_count * 8;
+    lo_parts_kernel<<<blocks, 256, 0, s>>>(reinterpret_cast<const float4*>(A), reinterpret_cast<float4*>(Al),
+                                           (parts & 1) ? int64_t(na / 4) : 0, reinterpret_cast<const float4*>(B),
+                                           reinterpret_cast<float4*>(Bl), (parts & 2) ? int64_t(nb / 4) : 0);
+    count_launch();
+  }
+  if (M == 0) return VT_OK;   // B lo only
 
   TileRaster rs;
   rs.mt = int((M + 255) / 256);

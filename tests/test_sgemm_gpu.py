@@ -81,7 +81,7 @@ def test_skinny_kernel(native, variant):
     rng = np.random.default_rng(20260917 + 5)
     for (m, n, k) in ((16, 8192, 8192), (16, 1024, 640), (7, 1024, 640), (1, 512, 4096), (16, 516, 100),
                       (3, 128, 64), (16, 132, 31), (5, 4, 7), (9, 260, 8), (16, 16384, 4096), (12, 60000, 512),
-                      (16, 4096, 16384), (2, 2048, 2050)):
+                      (16, 4096, 16384), (2, 2048, 2050), (16, 22700, 4001), (15, 20040, 3995)):
         a, b = uniform(rng, (m, k)), uniform(rng, (k, n))
         c = np.full((m, n), np.nan, dtype=np.float32)
         native.sgemm(a, b, c, m, n, k, variant=variant)

@@ -21,6 +21,7 @@
 //   K split   a slab's CTAs leave partial tiles in scratch memory; the CTA that finishes last
 //             (a ticket per slab) sums them in split order and writes C, so results do not depend
 //             on which CTA that is.  Tickets return to zero for the next launch.
+#include <cstdlib>
 #include "ptx_sm100.cuh"
 #include "runtime.h"
 #include "skinny_sched.cuh"
@@ -205,7 +206,8 @@ sgemm_skinny_tma_kernel(const __grid_constant__ CUtensorMap tmB, const float* __
         const int stage0 = it % KT_STAGES, stage1 = (it + 1) % KT_STAGES;
         const uint32_t phase0 = uint32_t(it / KT_STAGES) & 1u, phase1 = uint32_t((it + 1) / KT_STAGES) & 1u;
         if (i + 1 < nchunks) load_a(seg.chunk_beg + i + 1, a_odd);
-        ok = mbar_wait(&ps->full[stage0], phase0, abort_word, KSTAT_WAIT_EXPIRED_MMA);
+        // every lane polls; the vote brings the warp back together before the warp-wide MMAs below
+        ok = __all_sync(0xffffffffu, mbar_wait(&ps->full[stage0], phase0, abort_word, KSTAT_WAIT_EXPIRED_MMA));
         if (!ok) break;
         compute(stage0, a_even);
         __syncwarp();
@@ -213,7 +215,7 @@ sgemm_skinny_tma_kernel(const __grid_constant__ CUtensorMap tmB, const float* __
         ++it;
         if (i + 1 < nchunks) {
           if (i + 2 < nchunks) load_a(seg.chunk_beg + i + 2, a_even);
-          ok = mbar_wait(&ps->full[stage1], phase1, abort_word, KSTAT_WAIT_EXPIRED_MMA);
+          ok = __all_sync(0xffffffffu, mbar_wait(&ps->full[stage1], phase1, abort_word, KSTAT_WAIT_EXPIRED_MMA));
           if (!ok) break;
           compute(stage1, a_odd);
           __syncwarp();
@@ -282,7 +284,7 @@ int launch_sgemm_skinny_tma(DeviceCtx* c, const float* A, const float* B, float*
                                  int(KT_SMEM_BYTES)));
     c->func_attr_mask |= attr_bit;
   }
-  const bool vec_a = (K % 2 == 0) && (reinterpret_cast<uintptr_t>(A) % 8 == 0);
+  const bool vec_a = (K % 2 == 0) && (reinterpret_cast<uintptr_t>(A) % 8 == 0) && !getenv("VT_TMP_NOVEC");
   if (vec_a)
     sgemm_skinny_tma_kernel<true><<<ctas, KT_THREADS, KT_SMEM_BYTES, s>>>(tmB, A, C, partials, tickets, int(M), int(N),
                                                                          int(K), sc, c->status);

@@ -244,7 +244,10 @@ sgemm_skinny_umma_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_c
       // Adds this pipe's oldest undrained accumulator (both column groups) into master.
       auto drain = [&]() -> bool {
         const int buf = win & 1;
-        if (!mbar_wait(&ps->acc_full[pipe][buf], uint32_t(win >> 1) & 1u, abort_word, KSTAT_WAIT_EXPIRED_EPILOGUE)) return false;
+        // Every lane polls; the vote brings the warp back together before the warp-wide tcgen05 operations.
+        if (!__all_sync(0xffffffffu, mbar_wait(&ps->acc_full[pipe][buf], uint32_t(win >> 1) & 1u, abort_word,
+                                               KSTAT_WAIT_EXPIRED_EPILOGUE)))
+          return false;
         tc_fence_after_sync();
         uint32_t r[32];
         tmem_ld_32x32b_x32(lane_base + uint32_t(buf * 32), r);
@@ -261,7 +264,7 @@ sgemm_skinny_umma_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_c
       bool due = false;
       for (int i = 0; i < nchunks && ok; ++i) {
         if (int(turn) == pipe) {
-          ok = mbar_wait(&ps->raw_full[stage], phase, abort_word, KSTAT_WAIT_EXPIRED_EPILOGUE);
+          ok = __all_sync(0xffffffffu, mbar_wait(&ps->raw_full[stage], phase, abort_word, KSTAT_WAIT_EXPIRED_EPILOGUE));
           if (!ok) break;
           const uint8_t* stage_ptr = tiles + size_t(stage) * KU_STAGE_BYTES;
           // This thread's column of the slab, all 32 rows of the chunk.  Box `quarter`: rows of
@@ -282,7 +285,8 @@ sgemm_skinny_umma_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_c
           }
           // The MMAs that read this B lo buffer two of this pipe's chunks ago must have retired.
           const uint32_t lo_buf = mine & 1u;
-          ok = mbar_wait(&ps->lo_free[pipe][lo_buf], (uint32_t(mine >> 1) & 1u) ^ 1u, abort_word, KSTAT_WAIT_EXPIRED_EPILOGUE);
+          ok = __all_sync(0xffffffffu, mbar_wait(&ps->lo_free[pipe][lo_buf], (uint32_t(mine >> 1) & 1u) ^ 1u, abort_word,
+                                                 KSTAT_WAIT_EXPIRED_EPILOGUE));
           if (!ok) break;
           tc_fence_after_sync();
           tmem_st_32x32b_x16(lane_base + 64u + lo_buf * 32u, lo_a);

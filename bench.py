@@ -143,6 +143,16 @@ class ClockSampler:
     def _inside(self, t):
         return self.t_begin is None or self.t_end is None or self.t_begin <= t <= self.t_end
 
+    def window(self, t0: float, t1: float) -> dict | None:
+        """Median clock, reasons and peak power of the NVML samples taken in [t0, t1] (None without NVML)."""
+        if self.nvml is None:
+            return None
+        inside = [x for x in list(self.samples) if t0 <= x[0] <= t1]
+        sm = [x[1] for x in inside]
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_mhz_min": min(sm) if sm else None,
+                "reasons": sorted({name for x in inside for name, bit in self.REASON_BITS if x[2] & bit}),
+                "samples": len(sm), "power_w_max": max(x[3] for x in inside) if inside else None}
+
     def stop(self) -> dict:
         if self.nvml is not None:
             self.running = False
@@ -436,8 +446,33 @@ def run_gpu_arm(args, kind, M, N, K, batch, metric, unit):
         total_rows = float(tot.item())
     else:
         total_rows = float(rows)
-    clocks = sampler.stop() if rank == 0 else None
     ms_per_step = elapsed_ms / steps
+
+    # ---- the same step back to back for about a second: NVML's clock and power readings lag a region of a
+    # few milliseconds, so this is where the power cap shows; reported beside the timed region, not as it ----
+    sustained = None
+    if args.sustain_seconds > 0:
+        reps = max(steps, min(200000, int(args.sustain_seconds * 1e3 / max(ms_per_step, 1e-3))))
+        s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        t_s0 = time.perf_counter()
+        s0.record()
+        for _ in range(reps):
+            step()
+        s1.record()
+        barrier()
+        t_s1 = time.perf_counter()
+        sus_ms = s0.elapsed_time(s1) / reps
+        nv.sync(dev, st)
+        if world > 1:
+            t = torch.tensor([sus_ms], device="cuda", dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            sus_ms = float(t.item())
+        if rank == 0:
+            # the second half of the window: the readings have caught up with the load by then
+            sustained = sampler.window(0.5 * (t_s0 + t_s1), t_s1) or {}
+            sustained.update({"steps": reps, "ms_per_step": sus_ms, "seconds": t_s1 - t_s0})
+    clocks = sampler.stop() if rank == 0 else None
     ops_per_step_job = 2.0 * total_rows * N * K
     value = ops_per_step_job / (ms_per_step * 1e-3) / 1e12
 
@@ -527,6 +562,10 @@ def run_gpu_arm(args, kind, M, N, K, batch, metric, unit):
                    "l2": "working set per launch %.0f MiB > 126 MB L2; no flush between steps"
                          % ((rows * K * elem_in + K * N * elem_in + rows * N * elem_out) / 2**20)},
         "clocks": clocks,
+        "sustained": None if sustained is None else dict(
+            sustained, value=ops_per_step_job / (sustained["ms_per_step"] * 1e-3) / 1e12, unit=unit,
+            note="the same step repeated back to back after the timed region; clocks are NVML samples of the second "
+                 "half of that window"),
         "e2e": {"value": e2e_value, "unit": unit, "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
                 "steps": e2e_steps, "ms_per_step": e2e_s * 1e3 if e2e_s else None, "matches_device_run": e2e_ok},
         "gpu_launches": int(launches),
@@ -557,6 +596,9 @@ def main() -> int:
     ap.add_argument("--i8-variant", type=int, default=0, help="VT_I8_* kernel variant (0 = the library's choice)")
     ap.add_argument("--sgemm-variant", type=int, default=0, help="VT_SGEMM_* kernel variant (0 = the library's choice)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--sustain-seconds", type=float, default=1.0,
+                    help="after the timed region, repeat the step for about this long and report its rate and the "
+                         "clocks NVML shows under that load (0 = skip)")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
     args = ap.parse_args()
     kind, M, N, K, batch = WORKLOADS[args.workload]

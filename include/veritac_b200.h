@@ -81,7 +81,10 @@ enum {
  *                     (N % 4 == 0, K % 4 == 0, 16-byte aligned operands)
  *   SKINNY_TF32X3     M <= 16 on the tensor cores (3xTF32): one TMA-fed launch, tcgen05 with B used as it
  *                     lies in memory; when K % 4 != 0 or A is not 16-byte aligned, SKINNY_MMA_SYNC runs
- *   SKINNY_MMA_SYNC   the same stream of B with the products on mma.sync TF32 (any K, any alignment of A) */
+ *   SKINNY_MMA_SYNC   the same stream of B with the products on mma.sync TF32 (any K, any alignment of A)
+ *   PANEL_TF32X3      the SKINNY_TF32X3 kernel with taller panels of A (16, 32, 64 or 128 rows per launch, one
+ *                     launch per 128 rows of A), for products with few rows where B is the traffic
+ *                     (N % 4 == 0, K % 4 == 0, 16-byte aligned operands) */
 enum {
   VT_SGEMM_AUTO = 0,
   VT_SGEMM_TILE128 = 1,
@@ -90,7 +93,8 @@ enum {
   VT_SGEMM_TF32X3 = 4,
   VT_SGEMM_SKINNY_TF32X3 = 5,
   VT_SGEMM_SKINNY_MMA_SYNC = 6,
-  VT_SGEMM_TILE32 = 7
+  VT_SGEMM_TILE32 = 7,
+  VT_SGEMM_PANEL_TF32X3 = 8
 };
 
 /* Number of CUDA devices visible, or a negative VT_ERR_* code. */

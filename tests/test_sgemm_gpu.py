@@ -94,6 +94,44 @@ def test_skinny_kernel(native, variant):
                      variant=variant)
 
 
+def test_row_panel_kernel(native):
+    """PANEL_TF32X3: panels of 16, 32, 64 and 128 rows of A, one launch per 128 rows; ragged N and K, a last
+    panel of a few rows, K splits, same-sign data (the worst case for a truncating accumulator), reruns
+    bit-identical, and the automatic choice for few rows against a large B."""
+    import torch
+    gen = torch.Generator(device="cuda").manual_seed(20260917 + 8)
+    st = native.torch_stream()
+    for (m, n, k) in ((17, 512, 512), (32, 1024, 1024), (33, 1024, 1028), (48, 1000, 996), (64, 2048, 1024),
+                      (65, 1284, 2052), (100, 4096, 512), (128, 1024, 4096), (129, 1024, 1024), (200, 2052, 1000),
+                      (256, 4096, 4096), (300, 1024, 1024), (7, 1028, 1000), (128, 8192, 8192), (40, 16384, 2048),
+                      (96, 132, 8192), (20, 4, 4), (128, 60000, 256)):
+        for positive in (False, True):
+            A = torch.rand((m, k), device="cuda", generator=gen)
+            B = torch.rand((k, n), device="cuda", generator=gen)
+            if not positive:
+                A, B = A * 2 - 1, B * 2 - 1
+            ref = A.double() @ B.double()
+            C = torch.full((m, n), float("nan"), device="cuda")
+            native.sgemm(A, B, C, m, n, k, variant=native.VT_SGEMM_PANEL_TF32X3, where=native.VT_DEVICE, stream=st)
+            native.sync(0, st)
+            assert float((C.double() - ref).norm() / ref.norm()) <= TOL / 4, (m, n, k, positive)
+            C2 = torch.full((m, n), float("nan"), device="cuda")
+            native.sgemm(A, B, C2, m, n, k, variant=native.VT_SGEMM_PANEL_TF32X3, where=native.VT_DEVICE, stream=st)
+            native.sync(0, st)
+            assert torch.equal(C, C2), (m, n, k)
+    A = torch.rand((96, 4096), device="cuda", generator=gen) * 2 - 1
+    B = torch.rand((4096, 4096), device="cuda", generator=gen) * 2 - 1
+    C, Cp = torch.empty((96, 4096), device="cuda"), torch.empty((96, 4096), device="cuda")
+    native.sgemm(A, B, C, 96, 4096, 4096, where=native.VT_DEVICE, stream=st)
+    native.sgemm(A, B, Cp, 96, 4096, 4096, variant=native.VT_SGEMM_PANEL_TF32X3, where=native.VT_DEVICE, stream=st)
+    native.sync(0, st)
+    assert torch.equal(C, Cp)              # the automatic choice for this shape is the panel kernel
+    with pytest.raises(native.NativeError):
+        native.sgemm(torch.zeros((32, 66), device="cuda"), torch.zeros((66, 64), device="cuda"),
+                     torch.zeros((32, 64), device="cuda"), 32, 64, 66, variant=native.VT_SGEMM_PANEL_TF32X3,
+                     where=native.VT_DEVICE, stream=st)
+
+
 def test_config5_large_fp32(native):
     """BASELINE config 5: 8192^3 (device resident, checked on sampled rows in float64 on the GPU)
     and the skinny 16 x 8192 x 8192 shape."""

@@ -43,6 +43,7 @@ VT_SGEMM_TF32X3 = 4
 VT_SGEMM_SKINNY_TF32X3 = 5
 VT_SGEMM_SKINNY_MMA_SYNC = 6
 VT_SGEMM_TILE32 = 7
+VT_SGEMM_PANEL_TF32X3 = 8
 
 # Every symbol include/veritac_b200.h declares, with its ctypes signature.
 SIGNATURES = {

@@ -313,7 +313,7 @@ int vt_sgemm(int dev, const float* A, const float* B, float* C, int64_t M, int64
   if (where != VT_HOST && where != VT_DEVICE) return fail(VT_ERR_INVALID, "where must be VT_HOST or VT_DEVICE");
   if (M < 1 || N < 1 || K < 1) return fail(VT_ERR_INVALID, "dimensions must be positive");
   if (M > 0x7fffffffLL || N > 0x7fffffffLL || K > 0x7fffffffLL) return fail(VT_ERR_INVALID, "dimension overflows int");
-  if (variant < VT_SGEMM_AUTO || variant > VT_SGEMM_TILE32) return fail(VT_ERR_INVALID, "unknown sgemm variant %d", variant);
+  if (variant < VT_SGEMM_AUTO || variant > VT_SGEMM_PANEL_TF32X3) return fail(VT_ERR_INVALID, "unknown sgemm variant %d", variant);
   DeviceCtx* c = ctx_for(dev);
   if (!c) return VT_ERR_CUDA;
   cudaStream_t s = where == VT_HOST ? c->stream : pick_stream(c, stream);
@@ -343,12 +343,39 @@ int vt_sgemm(int dev, const float* A, const float* B, float* C, int64_t M, int64
   if (variant == VT_SGEMM_AUTO && M >= 256 && N >= 256 && K >= 256 && double(M) * double(N) * double(K) >= 5.0e8 &&
       sgemm_tf32x3_supported(dA, dB, dC, M, N, K))
     variant = VT_SGEMM_TF32X3;
+  // Few rows against a large B: B is the traffic, and the row-panel kernel streams it once per 128 rows of A.
+  // (measured against the tile kernels: from 1 Mi elements of B up to 32 rows, from 4 Mi up to 256 rows).
+  if (variant == VT_SGEMM_AUTO && M > 16 && M <= 2 * SKINNY_UMMA_MAX_ROWS && N >= 512 && K >= 512 &&
+      double(N) * double(K) >= (M <= 32 ? 1.0e6 : M <= 128 ? 4.0e6 : 8.0e6) && sgemm_skinny_umma_supported(dA, dB, dC, 1, N, K))
+    variant = VT_SGEMM_PANEL_TF32X3;
   int rc;
-  if (variant == VT_SGEMM_SKINNY_TF32X3 || variant == VT_SGEMM_SKINNY_MMA_SYNC) {
+  if (variant == VT_SGEMM_PANEL_TF32X3) {
+    if (!sgemm_skinny_umma_supported(dA, dB, dC, 1, N, K))
+      return fail(VT_ERR_UNSUPPORTED, "row-panel kernel needs N %% 4 == 0, K %% 4 == 0 and 16-byte aligned operands");
+    size_t pbytes = 0;
+    for (int64_t m0 = 0; m0 < M; m0 += SKINNY_UMMA_MAX_ROWS) {
+      const int64_t rows = M - m0 < SKINNY_UMMA_MAX_ROWS ? M - m0 : SKINNY_UMMA_MAX_ROWS;
+      int ctas, slabs, max_parts;
+      sgemm_skinny_umma_plan(rows, N, K, c->sm_count, &ctas, &slabs, &max_parts);
+      const size_t need = max_parts > 1 ? size_t(max_parts) * size_t(rows) * size_t(N) * 4 : 0;
+      if (need > pbytes) pbytes = need;
+    }
+    float* partials = nullptr;
+    if (pbytes) {
+      partials = static_cast<float*>(ctx_workspace(c, 3, pbytes));
+      if (!partials) return VT_ERR_CUDA;
+    }
+    rc = VT_OK;
+    // One launch per panel, in stream order: the partial tiles and the tickets are reused.
+    for (int64_t m0 = 0; m0 < M && rc == VT_OK; m0 += SKINNY_UMMA_MAX_ROWS) {
+      const int64_t rows = M - m0 < SKINNY_UMMA_MAX_ROWS ? M - m0 : SKINNY_UMMA_MAX_ROWS;
+      rc = launch_sgemm_skinny_umma(c, dA + m0 * K, dB, dC + m0 * N, partials, c->tickets, rows, N, K, s);
+    }
+  } else if (variant == VT_SGEMM_SKINNY_TF32X3 || variant == VT_SGEMM_SKINNY_MMA_SYNC) {
     if (!skinny_ok) return fail(VT_ERR_UNSUPPORTED, "skinny kernel needs M <= 16, N %% 4 == 0 and 16-byte aligned B, C");
     const bool umma = variant == VT_SGEMM_SKINNY_TF32X3 && sgemm_skinny_umma_supported(dA, dB, dC, M, N, K);
     int ctas, slabs, max_parts;
-    if (umma) sgemm_skinny_umma_plan(N, K, c->sm_count, &ctas, &slabs, &max_parts);
+    if (umma) sgemm_skinny_umma_plan(M, N, K, c->sm_count, &ctas, &slabs, &max_parts);
     else sgemm_skinny_tma_plan(N, K, c->sm_count, &ctas, &slabs, &max_parts);
     float* partials = nullptr;
     if (max_parts > 1) {

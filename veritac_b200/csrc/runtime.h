@@ -80,7 +80,8 @@ void sgemm_skinny_tma_plan(int64_t N, int64_t K, int sm_count, int* ctas, int* s
 bool sgemm_skinny_tma_supported(const float* B, const float* C, int64_t M, int64_t N, int64_t K);
 int launch_sgemm_skinny_tma(DeviceCtx* c, const float* A, const float* B, float* C, float* partials, int* tickets,
                             int64_t M, int64_t N, int64_t K, cudaStream_t s);
-void sgemm_skinny_umma_plan(int64_t N, int64_t K, int sm_count, int* ctas, int* slabs, int* max_parts);
+constexpr int SKINNY_UMMA_MAX_ROWS = 128;   // rows of A one launch of the row-panel tensor-core kernel takes
+void sgemm_skinny_umma_plan(int64_t M, int64_t N, int64_t K, int sm_count, int* ctas, int* slabs, int* max_parts);
 bool sgemm_skinny_umma_supported(const float* A, const float* B, const float* C, int64_t M, int64_t N, int64_t K);
 int launch_sgemm_skinny_umma(DeviceCtx* c, const float* A, const float* B, float* C, float* partials, int* tickets,
                              int64_t M, int64_t N, int64_t K, cudaStream_t s);

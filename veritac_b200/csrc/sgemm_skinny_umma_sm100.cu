@@ -36,33 +36,55 @@
 namespace vt {
 namespace {
 
-constexpr int KU_STAGES = 10;
 constexpr int KU_CTAS_PER_SM = 1;
 constexpr int KU_WINDOW = 4;                       // chunks a pipe accumulates in tensor memory between folds
-constexpr int KU_PIPES = 2;
-constexpr int KU_PIECE_OVERHEAD = 10;              // chunks' worth of time between two pieces of work (measured)
-constexpr int KU_THREADS = 32 * (1 + KU_PIPES + 4 * KU_PIPES);
+constexpr int KU_MAX_STAGES = 10;
+constexpr int KU_MAX_PIPES = 2;
 constexpr int KU_B_BYTES = SKINNY_KC * SKINNY_COLS * 4;   // 16 KiB: four boxes of 32 floats x 32 rows
 constexpr int KU_BOX_BYTES = 32 * 32 * 4;
-constexpr int KU_A_BYTES = 16 * SKINNY_KC * 4;            // 2 KiB
-constexpr int KU_STAGE_BYTES = KU_B_BYTES + 2 * KU_A_BYTES;   // B, A, A lo
-constexpr int KU_PIPE_COLS = 128;                  // per pipe: accumulators at +0 and +32, B lo at +64 and +96
-constexpr int KU_TMEM_COLS = KU_PIPES * KU_PIPE_COLS;
-constexpr int KU_EXCH_BYTES = (KU_PIPES - 1) * 16 * SKINNY_COLS * 4;
-constexpr size_t KU_SMEM_BYTES = 1024 + size_t(KU_STAGES) * KU_STAGE_BYTES + KU_EXCH_BYTES + 512;
-static_assert(KU_TMEM_COLS == 256 || KU_TMEM_COLS == 512 || KU_TMEM_COLS == 128, "TMEM allocations are powers of two");
+constexpr int KU_SMEM_LIMIT = 227 * 1024;
+
+// One shape of the kernel: MT rows of A (the panel height, a multiple of 16 up to 128), the number of
+// pipes, and whether a pipe has two accumulators (one being drained while the other is filled) or one.
+// Tensor memory per pipe: the accumulators, 2 * MT columns each ([hi*hi | hi*lo]), then two B lo
+// buffers of 32 columns.
+template <int MT, int PIPES, int ACC_BUFS>
+struct KuShape {
+  static constexpr int kRows = MT;
+  static constexpr int kPipes = PIPES;
+  static constexpr int kAccBufs = ACC_BUFS;
+  static constexpr int kThreads = 32 * (1 + PIPES + 4 * PIPES);
+  static constexpr int kABytes = MT * SKINNY_KC * 4;                // 2 KiB per 16 rows
+  static constexpr int kStageBytes = KU_B_BYTES + 2 * kABytes;      // B, A, A lo
+  static constexpr int kAccCols = 2 * MT;
+  static constexpr int kLoCol = ACC_BUFS * kAccCols;                // first B lo buffer; the second 32 columns on
+  static constexpr int kPipeCols = kLoCol + 64;
+  static constexpr int kTmemCols = PIPES * kPipeCols <= 128 ? 128 : PIPES * kPipeCols <= 256 ? 256 : 512;
+  static constexpr int kExchBytes = (PIPES - 1) * MT * SKINNY_COLS * 4;
+  static constexpr int kFit = (KU_SMEM_LIMIT - 1024 - 512 - kExchBytes) / kStageBytes;
+  static constexpr int kStages = kFit < KU_MAX_STAGES ? kFit : KU_MAX_STAGES;
+  static constexpr size_t kSmemBytes = 1024 + size_t(kStages) * kStageBytes + kExchBytes + 512;
+  // chunks' worth of time between two pieces of work (measured for the 16-row shape; the drain and
+  // the result tile grow with the panel)
+  static constexpr int kPieceOverhead = MT <= 16 ? 10 : MT <= 32 ? 10 : MT <= 64 ? 8 : 8;
+  static_assert(MT % 16 == 0 && MT >= 16 && MT <= 128, "panel height");
+  static_assert(PIPES >= 1 && PIPES <= KU_MAX_PIPES && (ACC_BUFS == 1 || ACC_BUFS == 2), "pipes and accumulators");
+  static_assert(PIPES * kPipeCols <= 512, "tensor memory has 512 columns");
+  static_assert(kStages >= 3, "the ring needs a few stages");
+};
 
 struct UmmaSkinnyPipe {
-  uint64_t raw_full[KU_STAGES];    // TMA bytes have landed
-  uint64_t split_done[KU_STAGES];  // the chunk's pipe has written the lo parts
-  uint64_t empty[KU_STAGES];       // the MMAs that read the stage have retired
-  uint64_t lo_free[KU_PIPES][2];   // the MMAs that read a B lo buffer in tensor memory have retired
-  uint64_t acc_full[KU_PIPES][2];
-  uint64_t acc_empty[KU_PIPES][2];
+  uint64_t raw_full[KU_MAX_STAGES];    // TMA bytes have landed
+  uint64_t split_done[KU_MAX_STAGES];  // the chunk's pipe has written the lo parts
+  uint64_t empty[KU_MAX_STAGES];       // the MMAs that read the stage have retired
+  uint64_t lo_free[KU_MAX_PIPES][2];   // the MMAs that read a B lo buffer in tensor memory have retired
+  uint64_t acc_full[KU_MAX_PIPES][2];
+  uint64_t acc_empty[KU_MAX_PIPES][2];
   uint32_t tmem_base;
   int abort_word;
   int last_flag;
 };
+static_assert(sizeof(UmmaSkinnyPipe) <= 512, "pipeline state has 512 bytes of shared memory");
 
 // lo part of x as the tensor core should see it: x minus its top 19 bits, then half of the cut-off
 // unit added to the bit pattern so that the core's own cut rounds to nearest.
@@ -71,10 +93,22 @@ __device__ __forceinline__ uint32_t lo_part(uint32_t bits) {
   return __float_as_uint(__uint_as_float(bits) - hi) + 0x1000u;
 }
 
-__global__ void __launch_bounds__(KU_THREADS, KU_CTAS_PER_SM)
+template <class Shape>
+__global__ void __launch_bounds__(Shape::kThreads, KU_CTAS_PER_SM)
 sgemm_skinny_umma_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmA,
                          float* __restrict__ C, float* __restrict__ partials, int* __restrict__ tickets, int M, int N,
                          SkinnySched sc, int* __restrict__ status) {
+  constexpr int MT = Shape::kRows;
+  constexpr int KU_PIPES = Shape::kPipes;
+  constexpr int KU_ACC_BUFS = Shape::kAccBufs;
+  constexpr int KU_STAGES = Shape::kStages;
+  constexpr int KU_A_BYTES = Shape::kABytes;
+  constexpr int KU_STAGE_BYTES = Shape::kStageBytes;
+  constexpr int KU_PIPE_COLS = Shape::kPipeCols;
+  constexpr int KU_ACC_COLS = Shape::kAccCols;
+  constexpr int KU_LO_COL = Shape::kLoCol;
+  constexpr int KU_TMEM_COLS = Shape::kTmemCols;
+  constexpr int KU_EXCH_BYTES = Shape::kExchBytes;
   extern __shared__ uint8_t ku_smem_raw[];
   uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(ku_smem_raw) + 1023) & ~uintptr_t(1023));
   float* exch = reinterpret_cast<float*>(tiles + size_t(KU_STAGES) * KU_STAGE_BYTES);
@@ -160,8 +194,8 @@ sgemm_skinny_umma_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_c
     // ------------------------------ MMA issuer of pipe (warp - 1) ------------------------------
     if (lane == 0) {
       const int pipe = warp - 1;
-      constexpr uint32_t idesc_pair = umma_instr_desc(UMMA_D_F32, UMMA_AB_TF32, true, false, 128, 32);
-      constexpr uint32_t idesc_lo = umma_instr_desc(UMMA_D_F32, UMMA_AB_TF32, false, false, 128, 16);
+      constexpr uint32_t idesc_pair = umma_instr_desc(UMMA_D_F32, UMMA_AB_TF32, true, false, 128, 2 * MT);
+      constexpr uint32_t idesc_lo = umma_instr_desc(UMMA_D_F32, UMMA_AB_TF32, false, false, 128, MT);
       // Descriptors are kept as a constant high word and a low word that only ever has a constant
       // added to it, and the ring position is counted, not divided.
       constexpr uint32_t kMn32Hi = (512u >> 4) | (1u << 14) | (1u << 29);    // stride offset, version, swizzle mode 1
@@ -183,11 +217,11 @@ sgemm_skinny_umma_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_c
         int in_window = 0;
         for (int i = 0; i < nchunks; ++i) {
           if (int(turn) == pipe) {
-            const int buf = win & 1;
+            const int buf = win % KU_ACC_BUFS;
             const uint32_t lo_buf = mine & 1u;
             const bool opens = in_window == 0;
-            if (opens &&
-                !mbar_wait(&ps->acc_empty[pipe][buf], (uint32_t(win >> 1) & 1u) ^ 1u, abort_word, KSTAT_WAIT_EXPIRED_MMA)) {
+            if (opens && !mbar_wait(&ps->acc_empty[pipe][buf], (uint32_t(win / KU_ACC_BUFS) & 1u) ^ 1u, abort_word,
+                                    KSTAT_WAIT_EXPIRED_MMA)) {
               ok = false;
               break;
             }
@@ -198,8 +232,8 @@ sgemm_skinny_umma_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_c
             tc_fence_after_sync();
             const uint32_t b_lo32 = (tiles_lo + stage * (KU_STAGE_BYTES >> 4)) | ((4096u >> 4) << 16);            // B as loaded
             const uint32_t a_lo32 = (tiles_lo + stage * (KU_STAGE_BYTES >> 4) + (KU_B_BYTES >> 4)) | (1u << 16);  // [A; A lo]
-            const uint32_t d_tmem = pipe_tmem + uint32_t(buf * 32);
-            const uint32_t lo_tmem = pipe_tmem + 64u + lo_buf * 32u;
+            const uint32_t d_tmem = pipe_tmem + uint32_t(buf * KU_ACC_COLS);
+            const uint32_t lo_tmem = pipe_tmem + uint32_t(KU_LO_COL) + lo_buf * 32u;
 #pragma unroll
             for (int ks = 0; ks < SKINNY_KC / 8; ++ks) {
               const uint64_t a_desc = make_desc(a_lo32 + ks * (32u >> 4), kSw128Hi);
@@ -238,22 +272,26 @@ sgemm_skinny_umma_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_c
     SkinnySegment seg;
     for (int idx = 0; sched_segment(sc, cta, idx, seg); ++idx) {
       const int nchunks = seg.chunk_end - seg.chunk_beg;
-      float master[16];
+      float master[MT];
 #pragma unroll
-      for (int m = 0; m < 16; ++m) master[m] = 0.f;
+      for (int m = 0; m < MT; ++m) master[m] = 0.f;
       // Adds this pipe's oldest undrained accumulator (both column groups) into master.
       auto drain = [&]() -> bool {
-        const int buf = win & 1;
+        const int buf = win % KU_ACC_BUFS;
         // Every lane polls; the vote brings the warp back together before the warp-wide tcgen05 operations.
-        if (!__all_sync(0xffffffffu, mbar_wait(&ps->acc_full[pipe][buf], uint32_t(win >> 1) & 1u, abort_word,
+        if (!__all_sync(0xffffffffu, mbar_wait(&ps->acc_full[pipe][buf], uint32_t(win / KU_ACC_BUFS) & 1u, abort_word,
                                                KSTAT_WAIT_EXPIRED_EPILOGUE)))
           return false;
         tc_fence_after_sync();
-        uint32_t r[32];
-        tmem_ld_32x32b_x32(lane_base + uint32_t(buf * 32), r);
-        tmem_ld_wait();
 #pragma unroll
-        for (int m = 0; m < 16; ++m) master[m] += __uint_as_float(r[m]) + __uint_as_float(r[16 + m]);
+        for (int g = 0; g < MT / 16; ++g) {
+          uint32_t r0[16], r1[16];
+          tmem_ld_32x32b_x16(lane_base + uint32_t(buf * KU_ACC_COLS + g * 16), r0);
+          tmem_ld_32x32b_x16(lane_base + uint32_t(buf * KU_ACC_COLS + MT + g * 16), r1);
+          tmem_ld_wait();
+#pragma unroll
+          for (int m = 0; m < 16; ++m) master[g * 16 + m] += __uint_as_float(r0[m]) + __uint_as_float(r1[m]);
+        }
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive(&ps->acc_empty[pipe][buf]);
@@ -277,8 +315,10 @@ sgemm_skinny_umma_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_c
 #pragma unroll
           for (int k = 16; k < 32; ++k)
             lo_b[k - 16] = lo_part(__float_as_uint(box[k * 32 + (((lane >> 3) ^ (k & 3)) << 3) + (lane & 7)]));
-          {
-            const uint32_t a_addr = smem_u32(stage_ptr + KU_B_BYTES) + uint32_t(t) * 16u;
+#pragma unroll
+          for (int v = 0; v < MT / 16; ++v) {
+            // A lo under A, position for position (both blocks carry the same swizzle)
+            const uint32_t a_addr = smem_u32(stage_ptr + KU_B_BYTES) + uint32_t(v * 128 + t) * 16u;
             uint32_t x0, x1, x2, x3;
             asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(x0), "=r"(x1), "=r"(x2), "=r"(x3) : "r"(a_addr));
             st_shared_v4(a_addr + KU_A_BYTES, lo_part(x0), lo_part(x1), lo_part(x2), lo_part(x3));
@@ -289,8 +329,8 @@ sgemm_skinny_umma_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_c
                                                  KSTAT_WAIT_EXPIRED_EPILOGUE));
           if (!ok) break;
           tc_fence_after_sync();
-          tmem_st_32x32b_x16(lane_base + 64u + lo_buf * 32u, lo_a);
-          tmem_st_32x32b_x16(lane_base + 64u + lo_buf * 32u + 16u, lo_b);
+          tmem_st_32x32b_x16(lane_base + uint32_t(KU_LO_COL) + lo_buf * 32u, lo_a);
+          tmem_st_32x32b_x16(lane_base + uint32_t(KU_LO_COL) + lo_buf * 32u + 16u, lo_b);
           tmem_st_wait();
           fence_proxy_async_smem();
           tc_fence_before_sync();
@@ -320,9 +360,9 @@ sgemm_skinny_umma_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_c
       // Pipes above 0 hand their sums to pipe 0, which adds them in pipe order.  Whether the CTA is
       // giving up is read between the two barriers, where no thread can still be in a wait, so all
       // splitting threads take the same way out.
-      if (pipe > 0) {
+      if (KU_PIPES > 1 && pipe > 0) {
 #pragma unroll
-        for (int m = 0; m < 16; ++m) exch[((pipe - 1) * 16 + m) * SKINNY_COLS + t] = master[m];
+        for (int m = 0; m < MT; ++m) exch[((pipe - 1) * MT + m) * SKINNY_COLS + t] = master[m];
       }
       asm volatile("bar.sync 2, %0;" ::"n"(128 * KU_PIPES) : "memory");
       const bool giving_up = *abort_word != 0;
@@ -330,7 +370,7 @@ sgemm_skinny_umma_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_c
 #pragma unroll
         for (int q = 1; q < KU_PIPES; ++q)
 #pragma unroll
-          for (int m = 0; m < 16; ++m) master[m] += exch[((q - 1) * 16 + m) * SKINNY_COLS + t];
+          for (int m = 0; m < MT; ++m) master[m] += exch[((q - 1) * MT + m) * SKINNY_COLS + t];
       }
       asm volatile("bar.sync 2, %0;" ::"n"(128 * KU_PIPES) : "memory");   // exch may be rewritten
       if (giving_up) break;
@@ -340,10 +380,10 @@ sgemm_skinny_umma_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_c
         const int col = seg.slab * SKINNY_COLS + quarter * 32 + lane;
         if (col < N) {
 #pragma unroll
-          for (int m = 0; m < 16; ++m)
+          for (int m = 0; m < MT; ++m)
             if (m < M) dst[size_t(m) * N + col] = master[m];
         }
-        if (seg.parts > 1) skinny_finish_piece<128>(seg, t, 1, &ps->last_flag, tickets, partials, C, M, N);
+        if (seg.parts > 1) skinny_finish_piece<128, MT>(seg, t, 1, &ps->last_flag, tickets, partials, C, M, N);
       }
     }
   }
@@ -353,26 +393,19 @@ sgemm_skinny_umma_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_c
   if (threadIdx.x == 0 && ps->abort_word != 0) atomicCAS(status, 0, ps->abort_word);
 }
 
-}  // namespace
+// The shapes the library builds, by panel height.  Small MMAs are bound by their issuing thread, hence
+// two pipes while tensor memory has room for them (2 x (2 x 2*MT + 64) columns); the 128-row panel
+// fills one accumulator of 256 columns per pipe and drains it in place.
+using KuShape16 = KuShape<16, 2, 2>;
+using KuShape32 = KuShape<32, 2, 2>;
+using KuShape64 = KuShape<64, 1, 2>;
+using KuShape128 = KuShape<128, 1, 1>;
 
-void sgemm_skinny_umma_plan(int64_t N, int64_t K, int sm_count, int* ctas, int* slabs, int* max_parts) {
-  const SkinnySched sc = make_skinny_sched(N, K, sm_count, KU_CTAS_PER_SM, KU_PIECE_OVERHEAD, ctas);
-  *slabs = sc.slabs;
-  *max_parts = skinny_max_parts(sc);
-}
-
-bool sgemm_skinny_umma_supported(const float* A, const float* B, const float* C, int64_t M, int64_t N, int64_t K) {
-  return M >= 1 && M <= 16 && N % 4 == 0 && N >= 4 && K % 4 == 0 && K >= 4 && N < (1LL << 31) && K < (1LL << 31) &&
-         ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(C)) & 15) == 0;
-}
-
-int launch_sgemm_skinny_umma(DeviceCtx* c, const float* A, const float* B, float* C, float* partials, int* tickets,
-                             int64_t M, int64_t N, int64_t K, cudaStream_t s) {
-  if (!sgemm_skinny_umma_supported(A, B, C, M, N, K))
-    return fail(VT_ERR_UNSUPPORTED,
-                "skinny tensor-core kernel needs M <= 16, N %% 4 == 0, K %% 4 == 0 and 16-byte aligned operands");
+template <class Shape>
+int launch_shape(DeviceCtx* c, uint32_t attr_bit, const float* A, const float* B, float* C, float* partials, int* tickets,
+                 int64_t M, int64_t N, int64_t K, cudaStream_t s) {
   int ctas;
-  const SkinnySched sc = make_skinny_sched(N, K, c->sm_count, KU_CTAS_PER_SM, KU_PIECE_OVERHEAD, &ctas);
+  const SkinnySched sc = make_skinny_sched(N, K, c->sm_count, KU_CTAS_PER_SM, Shape::kPieceOverhead, &ctas);
   if (skinny_max_parts(sc) > 1 && (!partials || !tickets)) return fail(VT_ERR_INVALID, "skinny K split needs scratch memory");
   if (sc.slabs > kTicketCount)
     return fail(VT_ERR_UNSUPPORTED, "N = %lld has more slabs than the library keeps tickets for", (long long)N);
@@ -380,19 +413,50 @@ int launch_sgemm_skinny_umma(DeviceCtx* c, const float* A, const float* B, float
   int rc = encode_tmap_2d(&tmB, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, B, uint64_t(N), uint64_t(K), uint64_t(N) * 4, 32, 32,
                           CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B);
   if (rc) return rc;
-  rc = encode_tmap_2d(&tmA, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, A, uint64_t(K), uint64_t(M), uint64_t(K) * 4, 32, 16);
+  rc = encode_tmap_2d(&tmA, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, A, uint64_t(K), uint64_t(M), uint64_t(K) * 4, 32,
+                      Shape::kRows);
   if (rc) return rc;
-  constexpr uint32_t attr_bit = 1u << 21;
   if (!(c->func_attr_mask & attr_bit)) {
-    VT_CUDA(cudaFuncSetAttribute(sgemm_skinny_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 int(KU_SMEM_BYTES)));
+    VT_CUDA(cudaFuncSetAttribute(sgemm_skinny_umma_kernel<Shape>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 int(Shape::kSmemBytes)));
     c->func_attr_mask |= attr_bit;
   }
-  sgemm_skinny_umma_kernel<<<ctas, KU_THREADS, KU_SMEM_BYTES, s>>>(tmB, tmA, C, partials, tickets, int(M), int(N), sc,
-                                                                    c->status);
+  sgemm_skinny_umma_kernel<Shape><<<ctas, Shape::kThreads, Shape::kSmemBytes, s>>>(tmB, tmA, C, partials, tickets, int(M),
+                                                                                     int(N), sc, c->status);
   count_launch();
   VT_CUDA(cudaGetLastError());
   return VT_OK;
+}
+
+int piece_overhead_for(int64_t M) {
+  return M <= 16 ? KuShape16::kPieceOverhead : M <= 32 ? KuShape32::kPieceOverhead
+         : M <= 64 ? KuShape64::kPieceOverhead : KuShape128::kPieceOverhead;
+}
+
+}  // namespace
+
+void sgemm_skinny_umma_plan(int64_t M, int64_t N, int64_t K, int sm_count, int* ctas, int* slabs, int* max_parts) {
+  const SkinnySched sc = make_skinny_sched(N, K, sm_count, KU_CTAS_PER_SM, piece_overhead_for(M), ctas);
+  *slabs = sc.slabs;
+  *max_parts = skinny_max_parts(sc);
+}
+
+bool sgemm_skinny_umma_supported(const float* A, const float* B, const float* C, int64_t M, int64_t N, int64_t K) {
+  return M >= 1 && M <= SKINNY_UMMA_MAX_ROWS && N % 4 == 0 && N >= 4 && K % 4 == 0 && K >= 4 && N < (1LL << 31) &&
+         K < (1LL << 31) &&
+         ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(C)) & 15) == 0;
+}
+
+int launch_sgemm_skinny_umma(DeviceCtx* c, const float* A, const float* B, float* C, float* partials, int* tickets,
+                             int64_t M, int64_t N, int64_t K, cudaStream_t s) {
+  if (!sgemm_skinny_umma_supported(A, B, C, M, N, K))
+    return fail(VT_ERR_UNSUPPORTED,
+                "row-panel tensor-core kernel needs M <= %d, N %% 4 == 0, K %% 4 == 0 and 16-byte aligned operands",
+                SKINNY_UMMA_MAX_ROWS);
+  if (M <= 16) return launch_shape<KuShape16>(c, 1u << 21, A, B, C, partials, tickets, M, N, K, s);
+  if (M <= 32) return launch_shape<KuShape32>(c, 1u << 22, A, B, C, partials, tickets, M, N, K, s);
+  if (M <= 64) return launch_shape<KuShape64>(c, 1u << 23, A, B, C, partials, tickets, M, N, K, s);
+  return launch_shape<KuShape128>(c, 1u << 24, A, B, C, partials, tickets, M, N, K, s);
 }
 
 }  // namespace vt

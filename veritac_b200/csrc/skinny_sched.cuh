@@ -129,7 +129,7 @@ inline int skinny_max_parts(const SkinnySched& sc) {
 // a piece's partial tile: takes a ticket for the slab and, in the CTA that holds the last one, sums
 // the slab's partial tiles in piece order into C and returns the ticket counter to zero.  The
 // loads of several pieces are in flight together; the additions keep piece order.
-template <int kThreads>
+template <int kThreads, int kRows = 16>
 __device__ __forceinline__ void skinny_finish_piece(const SkinnySegment& seg, int tid, int bar_id, int* last_flag,
                                                     int* __restrict__ tickets, const float* __restrict__ partials,
                                                     float* __restrict__ C, int M, int N) {
@@ -144,41 +144,43 @@ __device__ __forceinline__ void skinny_finish_piece(const SkinnySegment& seg, in
     __threadfence();
     const int n0 = seg.slab * SKINNY_COLS;
     const size_t piece = size_t(M) * size_t(N);
-    constexpr int kSlots = 16 * SKINNY_COLS / 4 / kThreads;   // float4 per thread: rows of 512 bytes
+    constexpr int kSlots = 16 * SKINNY_COLS / 4 / kThreads;   // float4 per thread and block of 16 rows: rows of 512 bytes
     constexpr int kBatch = kSlots <= 2 ? 4 : 2;               // pieces loaded together
-    size_t off[kSlots];
-    bool live[kSlots];
-    float4 sum[kSlots];
+    for (int row0 = 0; row0 < kRows && row0 < M; row0 += 16) {
+      size_t off[kSlots];
+      bool live[kSlots];
+      float4 sum[kSlots];
 #pragma unroll
-    for (int i = 0; i < kSlots; ++i) {
-      const int v = tid + kThreads * i;
-      const int m = v >> 5, col = n0 + (v & 31) * 4;
-      live[i] = m < M && col < N;
-      off[i] = size_t(m) * N + col;
-      sum[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-    }
-    for (int p0 = 0; p0 < seg.parts; p0 += kBatch) {
-      float4 x[kSlots][kBatch];
+      for (int i = 0; i < kSlots; ++i) {
+        const int v = tid + kThreads * i;
+        const int m = row0 + (v >> 5), col = n0 + (v & 31) * 4;
+        live[i] = m < M && col < N;
+        off[i] = size_t(m) * N + col;
+        sum[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+      for (int p0 = 0; p0 < seg.parts; p0 += kBatch) {
+        float4 x[kSlots][kBatch];
+#pragma unroll
+        for (int i = 0; i < kSlots; ++i)
+#pragma unroll
+          for (int q = 0; q < kBatch; ++q)
+            x[i][q] = (live[i] && p0 + q < seg.parts)
+                          ? __ldcg(reinterpret_cast<const float4*>(partials + size_t(p0 + q) * piece + off[i]))
+                          : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int i = 0; i < kSlots; ++i)
+#pragma unroll
+          for (int q = 0; q < kBatch; ++q) {
+            sum[i].x += x[i][q].x;
+            sum[i].y += x[i][q].y;
+            sum[i].z += x[i][q].z;
+            sum[i].w += x[i][q].w;
+          }
+      }
 #pragma unroll
       for (int i = 0; i < kSlots; ++i)
-#pragma unroll
-        for (int q = 0; q < kBatch; ++q)
-          x[i][q] = (live[i] && p0 + q < seg.parts)
-                        ? __ldcg(reinterpret_cast<const float4*>(partials + size_t(p0 + q) * piece + off[i]))
-                        : make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-      for (int i = 0; i < kSlots; ++i)
-#pragma unroll
-        for (int q = 0; q < kBatch; ++q) {
-          sum[i].x += x[i][q].x;
-          sum[i].y += x[i][q].y;
-          sum[i].z += x[i][q].z;
-          sum[i].w += x[i][q].w;
-        }
+        if (live[i]) *reinterpret_cast<float4*>(C + off[i]) = sum[i];
     }
-#pragma unroll
-    for (int i = 0; i < kSlots; ++i)
-      if (live[i]) *reinterpret_cast<float4*>(C + off[i]) = sum[i];
     if (tid == 0) tickets[seg.slab] = 0;
   }
   asm volatile("bar.sync %0, %1;" ::"r"(bar_id), "n"(kThreads) : "memory");   // last_flag is rewritten by the next piece

@@ -114,7 +114,7 @@ def test_row_panel_kernel(native):
             C = torch.full((m, n), float("nan"), device="cuda")
             native.sgemm(A, B, C, m, n, k, variant=native.VT_SGEMM_PANEL_TF32X3, where=native.VT_DEVICE, stream=st)
             native.sync(0, st)
-            assert float((C.double() - ref).norm() / ref.norm()) <= TOL / 4, (m, n, k, positive)
+            assert float((C.double() - ref).norm() / ref.norm()) <= TOL / 3, (m, n, k, positive)
             C2 = torch.full((m, n), float("nan"), device="cuda")
             native.sgemm(A, B, C2, m, n, k, variant=native.VT_SGEMM_PANEL_TF32X3, where=native.VT_DEVICE, stream=st)
             native.sync(0, st)

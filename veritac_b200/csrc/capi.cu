@@ -344,9 +344,9 @@ int vt_sgemm(int dev, const float* A, const float* B, float* C, int64_t M, int64
       sgemm_tf32x3_supported(dA, dB, dC, M, N, K))
     variant = VT_SGEMM_TF32X3;
   // Few rows against a large B: B is the traffic, and the row-panel kernel streams it once per 128 rows of A.
-  // (measured against the tile kernels: from 1 Mi elements of B up to 32 rows, from 4 Mi up to 256 rows).
+  // (measured against the tile kernels: ahead from 1 Mi elements of B up to 32 rows, from 4 Mi up to 256 rows).
   if (variant == VT_SGEMM_AUTO && M > 16 && M <= 2 * SKINNY_UMMA_MAX_ROWS && N >= 512 && K >= 512 &&
-      double(N) * double(K) >= (M <= 32 ? 1.0e6 : M <= 128 ? 4.0e6 : 8.0e6) && sgemm_skinny_umma_supported(dA, dB, dC, 1, N, K))
+      double(N) * double(K) >= (M <= 32 ? 1.0e6 : 4.0e6) && sgemm_skinny_umma_supported(dA, dB, dC, 1, N, K))
     variant = VT_SGEMM_PANEL_TF32X3;
   int rc;
   if (variant == VT_SGEMM_PANEL_TF32X3) {

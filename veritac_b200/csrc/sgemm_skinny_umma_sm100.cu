@@ -1,4 +1,4 @@
-// Skinny fp32 GEMM (M <= 16) on the 5th-generation tensor cores: one HBM-bound stream of B.
+// fp32 GEMM with few rows of A (a panel of up to 128) on the 5th-generation tensor cores: one stream of B.
 //
 // The product is computed transposed, C^T (n x m) = B^T (n x k) * A^T (k x m), so that the streamed
 // matrix is the tensor core's 128-row operand:
@@ -7,28 +7,29 @@
 //              "128-byte swizzle with 32-byte atoms" layout: TMA boxes of 32 floats x 32 rows
 //              written with that swizzle, descriptors with leading offset = one box (4 KiB) and
 //              stride offset = four rows (512 B); a K step of 8 rows moves 1 KiB.
-//   B operand  the matching 16 x 32 block of A (k contiguous: K-major, plain 128-byte swizzle);
-//              rows past M are zero-filled by TMA.
-//   D          128 lanes (n) x 32 columns of fp32 in tensor memory.
+//   B operand  the matching MT x 32 block of A (k contiguous: K-major, plain 128-byte swizzle), MT
+//              the panel height (16, 32, 64 or 128); rows past M are zero-filled by TMA.
+//   D          128 lanes (n) x MT (or 2 x MT) columns of fp32 in tensor memory.
 // fp32 accuracy comes from the 3xTF32 split, done without a pass over global memory.  The tensor
 // core reads only the top 19 bits of each 32-bit operand, so the data as loaded *is* the hi part
 // (cut, not rounded).  The lo parts, lo = x - hi (exact; its own cut-off point pre-rounded), are
 // computed by warps of the CTA:
 //   B lo  goes straight into tensor memory (tcgen05.st, 32 columns per chunk) and is used from
 //         there as the A operand of its MMA, so B crosses shared memory once;
-//   A lo  is written under A in shared memory, which makes [A; A lo] one 32-row operand.
-// Two MMAs per K step of 8:  B (smem) x [A; A lo] -> columns 0-15 (hi*hi) and 16-31 (hi*lo);
-//                            B lo (tmem) x A      -> added into columns 0-15 (lo*hi).
-// Accumulators are folded into fp32 registers every KU_WINDOW chunks (the tensor core's own
-// accumulation truncates), adding the two column groups.
+//   A lo  is written under A in shared memory, which makes [A; A lo] one operand of 2 x MT rows.
+// Per K step of 8, stacked form:  B (smem) x [A; A lo] -> columns 0..MT-1 (hi*hi) and MT..2MT-1 (hi*lo);
+//                                 B lo (tmem) x A      -> added into columns 0..MT-1 (lo*hi).
+// The 128-row panel issues B x A, B x A lo and B lo x A into one accumulator of 128 columns instead,
+// so that two accumulators fit tensor memory.  Accumulators are folded into fp32 registers every
+// KU_WINDOW chunks (the tensor core's own accumulation truncates).
 //
-// One CTA per SM.  Warp 0 is the TMA producer (a ring of KU_STAGES x 18 KiB in flight).  MMAs this
-// small cost their issuing thread, and the warps that feed them, more time than the loads take, so
+// One CTA per SM.  Warp 0 is the TMA producer (a ring of stages of B, A and room for A lo).  Small MMAs
+// cost their issuing thread, and the warps that feed them, more time than the loads take, so
 // the chunks of the ring are dealt to KU_PIPES independent pipes (chunk at ring position p goes to
-// pipe p mod KU_PIPES).  A pipe is one MMA-issuing warp plus four splitting warps (one per TMEM
-// lane quarter) with its own accumulators and B lo buffers; at the end of a piece of work the pipes'
-// sums are added in pipe order through shared memory.  Work split and K-split reduction: see
-// skinny_sched.cuh.  Every wait is bounded.
+// pipe p mod KU_PIPES).  A pipe is one MMA-issuing warp plus one or more sets of four splitting warps
+// (one warp per TMEM lane quarter) with its own accumulators and B lo buffers; at the end of a piece of
+// work the pipes' sums are added in pipe order through shared memory.  Work split and K-split
+// reduction: see skinny_sched.cuh.  Every wait is bounded.
 #include "ptx_sm100.cuh"
 #include "runtime.h"
 #include "skinny_sched.cuh"
@@ -44,21 +45,31 @@ constexpr int KU_B_BYTES = SKINNY_KC * SKINNY_COLS * 4;   // 16 KiB: four boxes 
 constexpr int KU_BOX_BYTES = 32 * 32 * 4;
 constexpr int KU_SMEM_LIMIT = 227 * 1024;
 
-// One shape of the kernel: MT rows of A (the panel height, a multiple of 16 up to 128), the number of
-// pipes, and whether a pipe has two accumulators (one being drained while the other is filled) or one.
-// Tensor memory per pipe: the accumulators, 2 * MT columns each ([hi*hi | hi*lo]), then two B lo
-// buffers of 32 columns.
-template <int MT, int PIPES, int ACC_BUFS>
+// One shape of the kernel:
+//   MT       rows of A (the panel height, a multiple of 16 up to 128);
+//   PIPES    independent pipes (MMA issuer, accumulators, B lo buffers, splitting warps);
+//   SETS     sets of four splitting warps per pipe.  The pipe's chunks go to its sets in turn (the time a
+//            set takes over a chunk is a chain of latencies, so sets overlap them), and every set drains
+//            its own MT / SETS columns of each accumulator, so the running sums spread over the sets' registers;
+//   STACKED  [A; A lo] as one operand of 2 * MT rows (two MMAs per K step, accumulators of 2 * MT columns:
+//            [hi*hi | hi*lo]) or A and A lo as two operands into one accumulator of MT columns (three MMAs).
+// Tensor memory per pipe: two accumulators (one drained while the other fills), then the B lo buffers of
+// 32 columns each.
+template <int MT, int PIPES, int SETS, bool STACKED>
 struct KuShape {
   static constexpr int kRows = MT;
   static constexpr int kPipes = PIPES;
-  static constexpr int kAccBufs = ACC_BUFS;
-  static constexpr int kThreads = 32 * (1 + PIPES + 4 * PIPES);
+  static constexpr int kSets = SETS;
+  static constexpr bool kStacked = STACKED;
+  static constexpr int kAccBufs = 2;
+  static constexpr int kLoBufs = SETS < 2 ? 2 : SETS;
+  static constexpr int kSetRows = MT / SETS;                        // accumulator columns one set drains
+  static constexpr int kThreads = 32 * (1 + PIPES + 4 * PIPES * SETS);
   static constexpr int kABytes = MT * SKINNY_KC * 4;                // 2 KiB per 16 rows
   static constexpr int kStageBytes = KU_B_BYTES + 2 * kABytes;      // B, A, A lo
-  static constexpr int kAccCols = 2 * MT;
-  static constexpr int kLoCol = ACC_BUFS * kAccCols;                // first B lo buffer; the second 32 columns on
-  static constexpr int kPipeCols = kLoCol + 64;
+  static constexpr int kAccCols = STACKED ? 2 * MT : MT;
+  static constexpr int kLoCol = kAccBufs * kAccCols;                // first B lo buffer; the others 32 columns on each
+  static constexpr int kPipeCols = kLoCol + 32 * kLoBufs;
   static constexpr int kTmemCols = PIPES * kPipeCols <= 128 ? 128 : PIPES * kPipeCols <= 256 ? 256 : 512;
   static constexpr int kExchBytes = (PIPES - 1) * MT * SKINNY_COLS * 4;
   static constexpr int kFit = (KU_SMEM_LIMIT - 1024 - 512 - kExchBytes) / kStageBytes;
@@ -68,7 +79,9 @@ struct KuShape {
   // the result tile grow with the panel)
   static constexpr int kPieceOverhead = MT <= 16 ? 10 : MT <= 32 ? 10 : MT <= 64 ? 8 : 8;
   static_assert(MT % 16 == 0 && MT >= 16 && MT <= 128, "panel height");
-  static_assert(PIPES >= 1 && PIPES <= KU_MAX_PIPES && (ACC_BUFS == 1 || ACC_BUFS == 2), "pipes and accumulators");
+  static_assert(PIPES >= 1 && PIPES <= KU_MAX_PIPES && SETS >= 1 && SETS <= 4, "pipes and sets");
+  static_assert(MT % SETS == 0 && kSetRows % 16 == 0, "a set drains whole groups of 16 columns");
+  static_assert(kThreads <= 1024, "threads per CTA");
   static_assert(PIPES * kPipeCols <= 512, "tensor memory has 512 columns");
   static_assert(kStages >= 3, "the ring needs a few stages");
 };
@@ -77,7 +90,7 @@ struct UmmaSkinnyPipe {
   uint64_t raw_full[KU_MAX_STAGES];    // TMA bytes have landed
   uint64_t split_done[KU_MAX_STAGES];  // the chunk's pipe has written the lo parts
   uint64_t empty[KU_MAX_STAGES];       // the MMAs that read the stage have retired
-  uint64_t lo_free[KU_MAX_PIPES][2];   // the MMAs that read a B lo buffer in tensor memory have retired
+  uint64_t lo_free[KU_MAX_PIPES][4];   // the MMAs that read a B lo buffer in tensor memory have retired
   uint64_t acc_full[KU_MAX_PIPES][2];
   uint64_t acc_empty[KU_MAX_PIPES][2];
   uint32_t tmem_base;
@@ -101,6 +114,10 @@ sgemm_skinny_umma_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_c
   constexpr int MT = Shape::kRows;
   constexpr int KU_PIPES = Shape::kPipes;
   constexpr int KU_ACC_BUFS = Shape::kAccBufs;
+  constexpr int KU_SETS = Shape::kSets;
+  constexpr int KU_LO_BUFS = Shape::kLoBufs;
+  constexpr int MS = Shape::kSetRows;
+  constexpr bool KU_STACKED = Shape::kStacked;
   constexpr int KU_STAGES = Shape::kStages;
   constexpr int KU_A_BYTES = Shape::kABytes;
   constexpr int KU_STAGE_BYTES = Shape::kStageBytes;
@@ -123,12 +140,13 @@ sgemm_skinny_umma_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_c
       mbar_init(&ps->split_done[s], 4);
       mbar_init(&ps->empty[s], 1);
     }
-    for (int p = 0; p < KU_PIPES; ++p)
-      for (int b = 0; b < 2; ++b) {
-        mbar_init(&ps->lo_free[p][b], 1);
+    for (int p = 0; p < KU_PIPES; ++p) {
+      for (int b = 0; b < KU_LO_BUFS; ++b) mbar_init(&ps->lo_free[p][b], 1);
+      for (int b = 0; b < KU_ACC_BUFS; ++b) {
         mbar_init(&ps->acc_full[p][b], 1);
-        mbar_init(&ps->acc_empty[p][b], 4);
+        mbar_init(&ps->acc_empty[p][b], 4 * KU_SETS);
       }
+    }
     ps->abort_word = 0;
     ps->last_flag = 0;
     fence_mbar_init();
@@ -194,7 +212,7 @@ sgemm_skinny_umma_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_c
     // ------------------------------ MMA issuer of pipe (warp - 1) ------------------------------
     if (lane == 0) {
       const int pipe = warp - 1;
-      constexpr uint32_t idesc_pair = umma_instr_desc(UMMA_D_F32, UMMA_AB_TF32, true, false, 128, 2 * MT);
+      constexpr uint32_t idesc_pair = umma_instr_desc(UMMA_D_F32, UMMA_AB_TF32, true, false, 128, KU_STACKED ? 2 * MT : MT);
       constexpr uint32_t idesc_lo = umma_instr_desc(UMMA_D_F32, UMMA_AB_TF32, false, false, 128, MT);
       // Descriptors are kept as a constant high word and a low word that only ever has a constant
       // added to it, and the ring position is counted, not divided.
@@ -208,7 +226,7 @@ sgemm_skinny_umma_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_c
       };
       const uint32_t pipe_tmem = tmem_base + uint32_t(pipe * KU_PIPE_COLS);
       uint32_t stage = 0, phase = 0, turn = 0;   // ring position of the next chunk; turn = position mod KU_PIPES
-      uint32_t mine = 0;                         // chunks this pipe has taken: B lo buffer = mine & 1
+      uint32_t mine = 0;                         // chunks this pipe has taken: B lo buffer = mine mod KU_LO_BUFS
       int win = 0;
       bool ok = true;
       SkinnySegment seg;
@@ -218,7 +236,7 @@ sgemm_skinny_umma_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_c
         for (int i = 0; i < nchunks; ++i) {
           if (int(turn) == pipe) {
             const int buf = win % KU_ACC_BUFS;
-            const uint32_t lo_buf = mine & 1u;
+            const uint32_t lo_buf = mine % KU_LO_BUFS;
             const bool opens = in_window == 0;
             if (opens && !mbar_wait(&ps->acc_empty[pipe][buf], (uint32_t(win / KU_ACC_BUFS) & 1u) ^ 1u, abort_word,
                                     KSTAT_WAIT_EXPIRED_MMA)) {
@@ -239,6 +257,10 @@ sgemm_skinny_umma_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_c
               const uint64_t a_desc = make_desc(a_lo32 + ks * (32u >> 4), kSw128Hi);
               const uint64_t b_desc = make_desc(b_lo32 + ks * (1024u >> 4), kMn32Hi);
               umma_tf32<1>(d_tmem, b_desc, a_desc, idesc_pair, (ks == 0 && opens) ? 0u : 1u);
+              if (!KU_STACKED) {
+                const uint64_t a_lo_desc = make_desc(a_lo32 + (uint32_t(KU_A_BYTES) >> 4) + ks * (32u >> 4), kSw128Hi);
+                umma_tf32<1>(d_tmem, b_desc, a_lo_desc, idesc_pair, 1u);
+              }
               umma_tf32_a_tmem(d_tmem, lo_tmem + uint32_t(ks * 8), a_desc, idesc_lo, 1u);
             }
             umma_commit(&ps->empty[stage]);
@@ -262,9 +284,10 @@ sgemm_skinny_umma_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_c
     __syncwarp();
   } else {
     // ------------- splitting warps of a pipe: lo parts, accumulator drain, result -------------
-    const int pipe = (warp - 1 - KU_PIPES) >> 2;
+    const int pipe = (warp - 1 - KU_PIPES) / (4 * KU_SETS);
+    const int set = ((warp - 1 - KU_PIPES) >> 2) % KU_SETS;
     const int quarter = warp & 3;                                 // the TMEM lanes (and the TMA box) of this warp
-    const int t = ((warp - 1 - KU_PIPES) & 3) * 32 + lane;        // 0..127 within the pipe
+    const int t = ((warp - 1 - KU_PIPES) & 3) * 32 + lane;        // 0..127 within the set
     const uint32_t lane_base = tmem_base + (uint32_t(quarter * 32) << 16) + uint32_t(pipe * KU_PIPE_COLS);
     uint32_t stage = 0, phase = 0, turn = 0, mine = 0;
     int win = 0;
@@ -272,10 +295,10 @@ sgemm_skinny_umma_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_c
     SkinnySegment seg;
     for (int idx = 0; sched_segment(sc, cta, idx, seg); ++idx) {
       const int nchunks = seg.chunk_end - seg.chunk_beg;
-      float master[MT];
+      float master[MS];            // rows set * MS .. + MS of the panel, at this thread's column of the slab
 #pragma unroll
-      for (int m = 0; m < MT; ++m) master[m] = 0.f;
-      // Adds this pipe's oldest undrained accumulator (both column groups) into master.
+      for (int m = 0; m < MS; ++m) master[m] = 0.f;
+      // Adds this set's columns of the pipe's oldest undrained accumulator into master.
       auto drain = [&]() -> bool {
         const int buf = win % KU_ACC_BUFS;
         // Every lane polls; the vote brings the warp back together before the warp-wide tcgen05 operations.
@@ -284,13 +307,21 @@ sgemm_skinny_umma_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_c
           return false;
         tc_fence_after_sync();
 #pragma unroll
-        for (int g = 0; g < MT / 16; ++g) {
-          uint32_t r0[16], r1[16];
-          tmem_ld_32x32b_x16(lane_base + uint32_t(buf * KU_ACC_COLS + g * 16), r0);
-          tmem_ld_32x32b_x16(lane_base + uint32_t(buf * KU_ACC_COLS + MT + g * 16), r1);
-          tmem_ld_wait();
+        for (int g = 0; g < MS / 16; ++g) {
+          const uint32_t col = lane_base + uint32_t(buf * KU_ACC_COLS + set * MS + g * 16);
+          uint32_t r0[16];
+          tmem_ld_32x32b_x16(col, r0);
+          if (KU_STACKED) {
+            uint32_t r1[16];
+            tmem_ld_32x32b_x16(col + uint32_t(MT), r1);
+            tmem_ld_wait();
 #pragma unroll
-          for (int m = 0; m < 16; ++m) master[g * 16 + m] += __uint_as_float(r0[m]) + __uint_as_float(r1[m]);
+            for (int m = 0; m < 16; ++m) master[g * 16 + m] += __uint_as_float(r0[m]) + __uint_as_float(r1[m]);
+          } else {
+            tmem_ld_wait();
+#pragma unroll
+            for (int m = 0; m < 16; ++m) master[g * 16 + m] += __uint_as_float(r0[m]);
+          }
         }
         tc_fence_before_sync();
         __syncwarp();
@@ -298,10 +329,12 @@ sgemm_skinny_umma_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_c
         ++win;
         return true;
       };
-      int taken = 0, drained = 0;
-      bool due = false;
+      int seen = 0, drained = 0;   // chunks of this pipe so far in the piece; accumulators this set has drained
       for (int i = 0; i < nchunks && ok; ++i) {
-        if (int(turn) == pipe) {
+        if (int(turn) == pipe && int(mine % KU_SETS) != set) {
+          ++seen;
+          ++mine;
+        } else if (int(turn) == pipe) {
           ok = __all_sync(0xffffffffu, mbar_wait(&ps->raw_full[stage], phase, abort_word, KSTAT_WAIT_EXPIRED_EPILOGUE));
           if (!ok) break;
           const uint8_t* stage_ptr = tiles + size_t(stage) * KU_STAGE_BYTES;
@@ -323,10 +356,10 @@ sgemm_skinny_umma_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_c
             asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(x0), "=r"(x1), "=r"(x2), "=r"(x3) : "r"(a_addr));
             st_shared_v4(a_addr + KU_A_BYTES, lo_part(x0), lo_part(x1), lo_part(x2), lo_part(x3));
           }
-          // The MMAs that read this B lo buffer two of this pipe's chunks ago must have retired.
-          const uint32_t lo_buf = mine & 1u;
-          ok = __all_sync(0xffffffffu, mbar_wait(&ps->lo_free[pipe][lo_buf], (uint32_t(mine >> 1) & 1u) ^ 1u, abort_word,
-                                                 KSTAT_WAIT_EXPIRED_EPILOGUE));
+          // The MMAs that read this B lo buffer KU_LO_BUFS of this pipe's chunks ago must have retired.
+          const uint32_t lo_buf = mine % KU_LO_BUFS;
+          ok = __all_sync(0xffffffffu, mbar_wait(&ps->lo_free[pipe][lo_buf], (uint32_t(mine / KU_LO_BUFS) & 1u) ^ 1u,
+                                                 abort_word, KSTAT_WAIT_EXPIRED_EPILOGUE));
           if (!ok) break;
           tc_fence_after_sync();
           tmem_st_32x32b_x16(lane_base + uint32_t(KU_LO_COL) + lo_buf * 32u, lo_a);
@@ -336,13 +369,12 @@ sgemm_skinny_umma_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_c
           tc_fence_before_sync();
           __syncwarp();
           if (lane == 0) mbar_arrive(&ps->split_done[stage]);
-          // A window that closed with this pipe's previous chunk has had this whole split to finish.
-          if (due) {
+          // Accumulators that closed before this chunk have had this whole split to finish.
+          while (ok && drained < seen / KU_WINDOW) {
             ok = drain();
             ++drained;
-            due = false;
           }
-          if (++taken % KU_WINDOW == 0) due = true;
+          ++seen;
           ++mine;
         }
         if (++turn == KU_PIPES) turn = 0;
@@ -351,7 +383,7 @@ sgemm_skinny_umma_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_c
           phase ^= 1u;
         }
       }
-      const int windows = (taken + KU_WINDOW - 1) / KU_WINDOW;
+      const int windows = (seen + KU_WINDOW - 1) / KU_WINDOW;
       while (ok && drained < windows) {
         ok = drain();
         ++drained;
@@ -362,17 +394,17 @@ sgemm_skinny_umma_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_c
       // splitting threads take the same way out.
       if (KU_PIPES > 1 && pipe > 0) {
 #pragma unroll
-        for (int m = 0; m < MT; ++m) exch[((pipe - 1) * MT + m) * SKINNY_COLS + t] = master[m];
+        for (int m = 0; m < MS; ++m) exch[((pipe - 1) * MT + set * MS + m) * SKINNY_COLS + t] = master[m];
       }
-      asm volatile("bar.sync 2, %0;" ::"n"(128 * KU_PIPES) : "memory");
+      asm volatile("bar.sync 2, %0;" ::"n"(128 * KU_PIPES * KU_SETS) : "memory");
       const bool giving_up = *abort_word != 0;
       if (pipe == 0) {
 #pragma unroll
         for (int q = 1; q < KU_PIPES; ++q)
 #pragma unroll
-          for (int m = 0; m < MT; ++m) master[m] += exch[((q - 1) * MT + m) * SKINNY_COLS + t];
+          for (int m = 0; m < MS; ++m) master[m] += exch[((q - 1) * MT + set * MS + m) * SKINNY_COLS + t];
       }
-      asm volatile("bar.sync 2, %0;" ::"n"(128 * KU_PIPES) : "memory");   // exch may be rewritten
+      asm volatile("bar.sync 2, %0;" ::"n"(128 * KU_PIPES * KU_SETS) : "memory");   // exch may be rewritten
       if (giving_up) break;
       if (pipe == 0) {
         // The tile of this piece goes to C (the slab has one piece) or to its slot among the slab's partial tiles.
@@ -380,10 +412,11 @@ sgemm_skinny_umma_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_c
         const int col = seg.slab * SKINNY_COLS + quarter * 32 + lane;
         if (col < N) {
 #pragma unroll
-          for (int m = 0; m < MT; ++m)
-            if (m < M) dst[size_t(m) * N + col] = master[m];
+          for (int m = 0; m < MS; ++m)
+            if (set * MS + m < M) dst[size_t(set * MS + m) * N + col] = master[m];
         }
-        if (seg.parts > 1) skinny_finish_piece<128, MT>(seg, t, 1, &ps->last_flag, tickets, partials, C, M, N);
+        if (seg.parts > 1)
+          skinny_finish_piece<128 * KU_SETS, MT>(seg, set * 128 + t, 1, &ps->last_flag, tickets, partials, C, M, N);
       }
     }
   }
@@ -396,10 +429,10 @@ sgemm_skinny_umma_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_c
 // The shapes the library builds, by panel height.  Small MMAs are bound by their issuing thread, hence
 // two pipes while tensor memory has room for them (2 x (2 x 2*MT + 64) columns); the 128-row panel
 // fills one accumulator of 256 columns per pipe and drains it in place.
-using KuShape16 = KuShape<16, 2, 2>;
-using KuShape32 = KuShape<32, 2, 2>;
-using KuShape64 = KuShape<64, 1, 2>;
-using KuShape128 = KuShape<128, 1, 1>;
+using KuShape16 = KuShape<16, 2, 1, true>;
+using KuShape32 = KuShape<32, 2, 1, true>;
+using KuShape64 = KuShape<64, 1, 2, true>;
+using KuShape128 = KuShape<128, 1, 2, false>;
 
 template <class Shape>
 int launch_shape(DeviceCtx* c, uint32_t attr_bit, const float* A, const float* B, float* C, float* partials, int* tickets,

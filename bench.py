@@ -54,6 +54,8 @@ WORKLOADS = {
     "sgemm_8192": ("f32", 8192, 8192, 8192, 1),
     "sgemm_256": ("f32", 256, 256, 256, 1),
     "sgemm_skinny": ("f32", 16, 8192, 8192, 1),
+    "sgemm_panel_64": ("f32", 64, 8192, 8192, 1),         # few rows against a large B: the row-panel kernel
+    "sgemm_panel_128": ("f32", 128, 8192, 8192, 1),
 }
 
 
@@ -521,7 +523,7 @@ def run_gpu_arm(args, kind, M, N, K, batch, metric, unit):
     # ---- roofline of the dominant kernel (this rank's launch) ----
     launch_ms = ms_per_step
     ops_per_launch = 2.0 * rows * N * K
-    if args.workload == "sgemm_skinny":
+    if args.workload in ("sgemm_skinny", "sgemm_panel_64", "sgemm_panel_128"):
         algo_bytes = (K * N + rows * K + rows * N) * 4.0
         achieved = algo_bytes / (launch_ms * 1e-3) / 1e9
         roof = {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",

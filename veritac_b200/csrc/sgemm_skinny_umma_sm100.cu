@@ -19,9 +19,9 @@
 //   A lo  is written under A in shared memory, which makes [A; A lo] one operand of 2 x MT rows.
 // Per K step of 8, stacked form:  B (smem) x [A; A lo] -> columns 0..MT-1 (hi*hi) and MT..2MT-1 (hi*lo);
 //                                 B lo (tmem) x A      -> added into columns 0..MT-1 (lo*hi).
-// The 128-row panel issues B x A, B x A lo and B lo x A into one accumulator of 128 columns instead,
-// so that two accumulators fit tensor memory.  Accumulators are folded into fp32 registers every
-// KU_WINDOW chunks (the tensor core's own accumulation truncates).
+// (The unstacked form, B x A, B x A lo and B lo x A into one accumulator of MT columns, is kept as an
+// option of the shape.)  Accumulators are folded into fp32 registers every few chunks (the tensor
+// core's own accumulation truncates).
 //
 // One CTA per SM.  Warp 0 is the TMA producer (a ring of stages of B, A and room for A lo).  Small MMAs
 // cost their issuing thread, and the warps that feed them, more time than the loads take, so
@@ -38,7 +38,6 @@ namespace vt {
 namespace {
 
 constexpr int KU_CTAS_PER_SM = 1;
-constexpr int KU_WINDOW = 4;                       // chunks a pipe accumulates in tensor memory between folds
 constexpr int KU_MAX_STAGES = 10;
 constexpr int KU_MAX_PIPES = 2;
 constexpr int KU_B_BYTES = SKINNY_KC * SKINNY_COLS * 4;   // 16 KiB: four boxes of 32 floats x 32 rows
@@ -53,15 +52,18 @@ constexpr int KU_SMEM_LIMIT = 227 * 1024;
 //            its own MT / SETS columns of each accumulator, so the running sums spread over the sets' registers;
 //   STACKED  [A; A lo] as one operand of 2 * MT rows (two MMAs per K step, accumulators of 2 * MT columns:
 //            [hi*hi | hi*lo]) or A and A lo as two operands into one accumulator of MT columns (three MMAs).
-// Tensor memory per pipe: two accumulators (one drained while the other fills), then the B lo buffers of
-// 32 columns each.
-template <int MT, int PIPES, int SETS, bool STACKED>
+//   ACC_BUFS accumulators per pipe: two (one drained while the other fills) or one (the pipe's MMAs wait
+//            while it is drained);
+//   WINDOW   chunks a pipe accumulates in tensor memory between folds into registers.
+// Tensor memory per pipe: the accumulators, then the B lo buffers of 32 columns each.
+template <int MT, int PIPES, int SETS, bool STACKED, int ACC_BUFS, int WINDOW>
 struct KuShape {
   static constexpr int kRows = MT;
   static constexpr int kPipes = PIPES;
   static constexpr int kSets = SETS;
   static constexpr bool kStacked = STACKED;
-  static constexpr int kAccBufs = 2;
+  static constexpr int kAccBufs = ACC_BUFS;
+  static constexpr int kWindow = WINDOW;
   static constexpr int kLoBufs = SETS < 2 ? 2 : SETS;
   static constexpr int kSetRows = MT / SETS;                        // accumulator columns one set drains
   static constexpr int kThreads = 32 * (1 + PIPES + 4 * PIPES * SETS);
@@ -80,6 +82,7 @@ struct KuShape {
   static constexpr int kPieceOverhead = MT <= 16 ? 10 : MT <= 32 ? 10 : MT <= 64 ? 8 : 8;
   static_assert(MT % 16 == 0 && MT >= 16 && MT <= 128, "panel height");
   static_assert(PIPES >= 1 && PIPES <= KU_MAX_PIPES && SETS >= 1 && SETS <= 4, "pipes and sets");
+  static_assert((ACC_BUFS == 1 || ACC_BUFS == 2) && WINDOW >= 1, "accumulators");
   static_assert(MT % SETS == 0 && kSetRows % 16 == 0, "a set drains whole groups of 16 columns");
   static_assert(kThreads <= 1024, "threads per CTA");
   static_assert(PIPES * kPipeCols <= 512, "tensor memory has 512 columns");
@@ -115,6 +118,7 @@ sgemm_skinny_umma_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_c
   constexpr int KU_PIPES = Shape::kPipes;
   constexpr int KU_ACC_BUFS = Shape::kAccBufs;
   constexpr int KU_SETS = Shape::kSets;
+  constexpr int KU_WINDOW = Shape::kWindow;
   constexpr int KU_LO_BUFS = Shape::kLoBufs;
   constexpr int MS = Shape::kSetRows;
   constexpr bool KU_STACKED = Shape::kStacked;
@@ -429,10 +433,19 @@ sgemm_skinny_umma_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_c
 // The shapes the library builds, by panel height.  Small MMAs are bound by their issuing thread, hence
 // two pipes while tensor memory has room for them (2 x (2 x 2*MT + 64) columns); the 128-row panel
 // fills one accumulator of 256 columns per pipe and drains it in place.
-using KuShape16 = KuShape<16, 2, 1, true>;
-using KuShape32 = KuShape<32, 2, 1, true>;
-using KuShape64 = KuShape<64, 1, 2, true>;
-using KuShape128 = KuShape<128, 1, 2, false>;
+// Measured at 8192^2 / 4096^2 / 1024^2 elements of B, in us.  64 rows: one pipe of two sets 83 / 31 / 15, two pipes
+// of one accumulator each 74 / 34 / 19.  128 rows: 107-109 / 42-45 in every form tried: stacked with one
+// accumulator (this one, the most accurate), unstacked with two, A lo loaded from a pass over A instead of
+// computed here, B itself copied to tensor memory so that no MMA reads it from shared memory, waits that keep
+// draining finished accumulators, and (timing only) a six-stage ring.  What bounds it is the one thread that
+// issues the MMAs: about 700 cycles per chunk for eight MMAs and two commits, plus its waits for the lo parts
+// and for the drained accumulator, against 800 cycles of tensor-core work; one MMA for both SMs of a CTA pair
+// (cta_group::2) would halve the issue cost per SM.
+using KuShape16 = KuShape<16, 2, 1, true, 2, 4>;
+using KuShape32 = KuShape<32, 2, 1, true, 2, 4>;
+using KuShape64 = KuShape<64, 1, 2, true, 2, 4>;
+using KuShape64Large = KuShape<64, 2, 1, true, 1, 4>;     // from 32 Mi elements of B
+using KuShape128 = KuShape<128, 1, 2, true, 1, 4>;
 
 template <class Shape>
 int launch_shape(DeviceCtx* c, uint32_t attr_bit, const float* A, const float* B, float* C, float* partials, int* tickets,
@@ -488,6 +501,8 @@ int launch_sgemm_skinny_umma(DeviceCtx* c, const float* A, const float* B, float
                 SKINNY_UMMA_MAX_ROWS);
   if (M <= 16) return launch_shape<KuShape16>(c, 1u << 21, A, B, C, partials, tickets, M, N, K, s);
   if (M <= 32) return launch_shape<KuShape32>(c, 1u << 22, A, B, C, partials, tickets, M, N, K, s);
+  if (M <= 64 && double(N) * double(K) >= 3.2e7)
+    return launch_shape<KuShape64Large>(c, 1u << 25, A, B, C, partials, tickets, M, N, K, s);
   if (M <= 64) return launch_shape<KuShape64>(c, 1u << 23, A, B, C, partials, tickets, M, N, K, s);
   return launch_shape<KuShape128>(c, 1u << 24, A, B, C, partials, tickets, M, N, K, s);
 }

@@ -43,7 +43,7 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustain
 
 # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the ncu captures
 # summarised under profiles/; None until a capture exists for the workload.
-NCU_TRAFFIC_BYTES = {"sgemm_skinny": 273.9e6, "i8_8192": 608.8e6, "i8_batched_32": 654.4e6, "i8_batched": 8 * 654.4e6}
+NCU_TRAFFIC_BYTES = {"sgemm_skinny": 273.9e6, "sgemm_panel_128": 282.9e6, "i8_8192": 608.8e6, "i8_batched_32": 654.4e6, "i8_batched": 8 * 654.4e6}
 
 WORKLOADS = {
     # name: (kind, M, N, K, batch)
@@ -523,11 +523,21 @@ def run_gpu_arm(args, kind, M, N, K, batch, metric, unit):
     # ---- roofline of the dominant kernel (this rank's launch) ----
     launch_ms = ms_per_step
     ops_per_launch = 2.0 * rows * N * K
-    if args.workload in ("sgemm_skinny", "sgemm_panel_64", "sgemm_panel_128"):
-        algo_bytes = (K * N + rows * K + rows * N) * 4.0
+    algo_bytes = (K * N + rows * K + rows * N) * 4.0
+    tf32x3_peak = peaks["bf16_tflops"] / 2.0 / 3.0       # three TF32 MMAs per fp32 product; TF32 at half the bf16 rate
+    panel = args.workload in ("sgemm_skinny", "sgemm_panel_64", "sgemm_panel_128")
+    if panel and algo_bytes / (peaks["hbm_gbs"] * 1e9) >= ops_per_launch / (tf32x3_peak * 1e12):
         achieved = algo_bytes / (launch_ms * 1e-3) / 1e9
         roof = {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                 "frac": achieved / peaks["hbm_gbs"], "peak_source": "%s hbm_gbs" % peaks_src}
+    elif panel:
+        # enough rows that the three TF32 MMAs per product take longer than streaming B
+        achieved = ops_per_launch / (launch_ms * 1e-3) / 1e12
+        roof = {"bound": "tensor", "achieved": achieved, "peak": tf32x3_peak, "unit": "TFLOP/s",
+                "frac": achieved / tf32x3_peak,
+                "peak_source": "%s bf16_tflops / 2 (TF32 rate) / 3 (MMAs per fp32 product); streaming B at %s hbm_gbs "
+                               "would take less" % (peaks_src, peaks_src),
+                "hbm_gbs_achieved": algo_bytes / (launch_ms * 1e-3) / 1e9}
     elif kind == "f32":
         achieved = ops_per_launch / (launch_ms * 1e-3) / 1e12
         tensor_path = args.sgemm_variant == nv.VT_SGEMM_TF32X3 or (

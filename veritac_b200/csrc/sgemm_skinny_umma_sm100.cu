@@ -439,8 +439,11 @@ sgemm_skinny_umma_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_c
 // computed here, B itself copied to tensor memory so that no MMA reads it from shared memory, waits that keep
 // draining finished accumulators, and (timing only) a six-stage ring.  What bounds it is the one thread that
 // issues the MMAs: about 700 cycles per chunk for eight MMAs and two commits, plus its waits for the lo parts
-// and for the drained accumulator, against 800 cycles of tensor-core work; one MMA for both SMs of a CTA pair
-// (cta_group::2) would halve the issue cost per SM.
+// and for the drained accumulator, against 800 cycles of tensor-core work.  The same pipeline on CTA pairs
+// (cta_group::2: one MMA of 256 rows for two neighbouring slabs, the N-side split between the CTAs made to
+// coincide with the A / A lo split) was built and was bit-for-bit as accurate, but slower: 143 us at 128 rows,
+// 130 us at 64; its issuing thread spent 630 cycles per chunk pair issuing and 1000-1100 waiting for lo parts
+// and drained accumulators that cross the cluster.
 using KuShape16 = KuShape<16, 2, 1, true, 2, 4>;
 using KuShape32 = KuShape<32, 2, 1, true, 2, 4>;
 using KuShape64 = KuShape<64, 1, 2, true, 2, 4>;

@@ -132,6 +132,39 @@ def test_row_panel_kernel(native):
                      where=native.VT_DEVICE, stream=st)
 
 
+def test_non_finite_inputs(native):
+    """Infinities and NaNs: the true-fp32 kernels give IEEE results (same NaN and infinity pattern as a float32
+    product).  The 3xTF32 kernels compute x * inf as hi * inf + lo * inf, which is NaN where lo is zero or of the
+    other sign, so there only the rows and columns that hold a non-finite input may differ, and only by NaN
+    standing where the float32 product has an infinity; everything else stays inside the tolerance."""
+    import torch
+    gen = torch.Generator(device="cuda").manual_seed(20260917 + 9)
+    st = native.torch_stream()
+    for (m, n, k, variants) in ((16, 1024, 1024, (3, 5, 6)), (96, 2048, 2048, (2, 8)), (512, 1024, 1024, (1, 2, 4, 7)),
+                                (64, 64, 64, (0,))):
+        A = torch.rand((m, k), device="cuda", generator=gen) * 2 - 1
+        B = torch.rand((k, n), device="cuda", generator=gen) * 2 - 1
+        A[0, 0], B[3, 5], A[2, 2] = float("inf"), float("-inf"), float("nan")
+        ref = (A.double() @ B.double()).float()
+        touched = torch.zeros((m, n), dtype=torch.bool, device="cuda")
+        touched[0, :] = True
+        touched[2, :] = True
+        touched[:, 5] = True
+        for variant in variants:
+            C = torch.empty((m, n), device="cuda")
+            native.sgemm(A, B, C, m, n, k, variant=variant, where=native.VT_DEVICE, stream=st)
+            native.sync(0, st)
+            clean = ~touched
+            err = float((C[clean].double() - ref[clean].double()).norm() / ref[clean].double().norm())
+            assert err <= TOL, (m, n, k, variant)
+            assert bool(torch.isnan(C[2]).all()), (m, n, k, variant)
+            if variant in (1, 2, 3, 7) or (variant == 0 and m == 64):
+                assert torch.equal(torch.isnan(C), torch.isnan(ref)), (m, n, k, variant)
+                assert torch.equal(C[torch.isinf(ref)], ref[torch.isinf(ref)]), (m, n, k, variant)
+            else:
+                assert bool((torch.isnan(C) | (C == ref))[torch.isinf(ref)].all()), (m, n, k, variant)
+
+
 def test_config5_large_fp32(native):
     """BASELINE config 5: 8192^3 (device resident, checked on sampled rows in float64 on the GPU)
     and the skinny 16 x 8192 x 8192 shape."""

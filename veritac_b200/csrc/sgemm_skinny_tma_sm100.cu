@@ -145,9 +145,15 @@ sgemm_skinny_tma_kernel(const __grid_constant__ CUtensorMap tmB, const float* __
     };
     // hi = the value rounded to TF32's 10 mantissa bits (half away from zero, in integer arithmetic
     // on the bit pattern), lo = the exact rest; the tensor core reads lo's top bits.
+    // The rounding must not carry a finite value into infinity, and an infinity or NaN has no lo part
+    // (inf - inf would turn every product of the row into NaN).
     auto split = [](float x, uint32_t& hi, uint32_t& lo) {
-      hi = (__float_as_uint(x) + 0x1000u) & 0xffffe000u;
-      lo = __float_as_uint(x - __uint_as_float(hi));
+      const uint32_t bits = __float_as_uint(x);
+      uint32_t h = (bits + 0x1000u) & 0xffffe000u;
+      if ((h & 0x7f800000u) == 0x7f800000u) h = bits & 0xffffe000u;
+      const float rest = x - __uint_as_float(h);
+      hi = h;
+      lo = rest == rest ? __float_as_uint(rest) : 0u;
     };
     // Lane-constant offsets of this lane's B elements inside a box, per n-tile.
     int off0[4], off1[4];

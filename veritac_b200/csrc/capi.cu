@@ -337,17 +337,31 @@ int vt_sgemm(int dev, const float* A, const float* B, float* C, int64_t M, int64
   }
   const bool skinny_ok = M <= 16 && N % 4 == 0 &&
                          ((reinterpret_cast<uintptr_t>(dB) | reinterpret_cast<uintptr_t>(dC)) & 15) == 0;
-  if (variant == VT_SGEMM_AUTO && skinny_ok && N >= 512 && K >= 512) variant = VT_SGEMM_SKINNY_TF32X3;
-  // Large products go to the tensor cores (3xTF32, measured ~1e-6 relative Frobenius error at any K);
-  // below ~1 GFLOP the two split passes cost more than they save and the FFMA kernel runs.
-  if (variant == VT_SGEMM_AUTO && M >= 256 && N >= 256 && K >= 256 && double(M) * double(N) * double(K) >= 5.0e8 &&
-      sgemm_tf32x3_supported(dA, dB, dC, M, N, K))
-    variant = VT_SGEMM_TF32X3;
+  if (variant == VT_SGEMM_AUTO && skinny_ok && K >= 512 && (N >= 512 || (N >= 128 && double(N) * double(K) >= 1.0e6)))
+    variant = VT_SGEMM_SKINNY_TF32X3;
   // Few rows against a large B: B is the traffic, and the row-panel kernel streams it once per 128 rows of A.
-  // (measured against the tile kernels: ahead from 1 Mi elements of B up to 32 rows, from 4 Mi up to 256 rows).
-  if (variant == VT_SGEMM_AUTO && M > 16 && M <= 2 * SKINNY_UMMA_MAX_ROWS && N >= 512 && K >= 512 &&
-      double(N) * double(K) >= (M <= 32 ? 1.0e6 : 4.0e6) && sgemm_skinny_umma_supported(dA, dB, dC, 1, N, K))
+  // (measured against the tile kernels and the 3xTF32 pair kernel: ahead from 1 Mi elements of B up to 32 rows,
+  // from 4 Mi up to 256 rows, from 16 Mi up to 384 rows).
+  if (variant == VT_SGEMM_AUTO && M > 16 && M <= 3 * SKINNY_UMMA_MAX_ROWS && N >= 128 && K >= 512 &&
+      double(N) * double(K) >= (M <= 32 ? 1.0e6 : M <= 2 * SKINNY_UMMA_MAX_ROWS ? 4.0e6 : 1.6e7) &&
+      sgemm_skinny_umma_supported(dA, dB, dC, 1, N, K))
     variant = VT_SGEMM_PANEL_TF32X3;
+  // Large products go to the tensor cores (3xTF32, measured ~1e-6 relative Frobenius error at any K) when that
+  // is clearly faster than the best FFMA tile kernel.  Its time is modelled as two launches (6 us), the pass that
+  // writes the lo parts and the write of C (8 bytes per element of A and B, 4 per element of C, at ~5.5 TB/s) and
+  // K x 34 ns for every wave of 256x256 tiles over the 74 CTA pairs (8192^3: 4.1 ms).  Below ~0.5 GFLOP the two
+  // passes cost more than they save.
+  if (variant == VT_SGEMM_AUTO && M >= 128 && N >= 16 && K >= 64 && double(M) * double(N) * double(K) >= 5.0e8 &&
+      sgemm_tf32x3_supported(dA, dB, dC, M, N, K)) {
+    int tile_variant;
+    const double t_tile = sgemm_tile_choice(dA, dB, dC, M, N, K, c->sm_count, &tile_variant);
+    const double pair_tiles = double((M + 255) / 256) * double((N + 255) / 256);
+    const double pairs = c->sm_count / 2;
+    const double waves = pair_tiles <= pairs ? 1.0 : double(int64_t((pair_tiles + pairs - 1) / pairs));
+    const double t_tc = 6.0e-6 + ((double(M) * K + double(K) * N) * 8.0 + double(M) * N * 4.0) / 5.5e12 +
+                        waves * double(K) * 3.4e-8;
+    if (t_tc < 0.9 * t_tile) variant = VT_SGEMM_TF32X3;
+  }
   int rc;
   if (variant == VT_SGEMM_PANEL_TF32X3) {
     if (!sgemm_skinny_umma_supported(dA, dB, dC, 1, N, K))

@@ -70,6 +70,8 @@ int launch_i8gemm(DeviceCtx* c, const int8_t* A, const int8_t* B, int32_t* C, in
                   int raster_mode, int group, int variant, cudaStream_t s, int64_t ldb = 0, int64_t ldc = 0);
 int launch_sgemm(DeviceCtx* c, const float* A, const float* B, float* C, int64_t M, int64_t N, int64_t K,
                  int variant, cudaStream_t s);
+double sgemm_tile_choice(const float* A, const float* B, const float* C, int64_t M, int64_t N, int64_t K, int sm_count,
+                         int* variant);
 int launch_sgemm_skinny(DeviceCtx* c, const float* A, const float* B, float* C, float* partials, int64_t M,
                         int64_t N, int64_t K, int ksplit, cudaStream_t s);
 bool sgemm_tf32x3_supported(const float* A, const float* B, const float* C, int64_t M, int64_t N, int64_t K);

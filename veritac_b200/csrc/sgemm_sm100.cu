@@ -537,19 +537,39 @@ int launch_sgemm_skinny(DeviceCtx* c, const float* A, const float* B, float* C, 
   return VT_OK;
 }
 
+// Which FFMA tile kernel to run, and about how long it will take (seconds): the work of the padded tile
+// grid over the rate that tile shape reaches (measured: 53, 32 and 32 TFLOPS for 128-, 64- and 32-wide
+// tiles with every SM busy), scaled down while the grid has fewer tiles than SMs; the smallest tile has
+// to win by 10 %.  Measured points the rule reproduces: 256^3 6.6 (32-wide) against 12.3 us (64-wide),
+// 512^3 13.3 against 20.5 us, 768^3 32.7 against 28.8 us, 8192 x 16 x 8192 151 against 399 us,
+// 65536 x 16 x 1024 140 against 281 us, 8192 x 256 x 8192 0.91 ms (128-wide) against 1.07 ms.
+double sgemm_tile_choice(const float* A, const float* B, const float* C, int64_t M, int64_t N, int64_t K, int sm_count,
+                         int* variant) {
+  const bool small_ok = sgemm_small_ok(A, B, C, N, K);
+  static const double kRate[3] = {53e12, 32e12, 32e12};
+  static const double kBias[3] = {1.0, 1.0, 1.1};
+  static const int kTile[3] = {128, 64, 32};
+  static const int kVariant[3] = {VT_SGEMM_TILE128, VT_SGEMM_TILE64, VT_SGEMM_TILE32};
+  double best = 0;
+  *variant = VT_SGEMM_TILE64;
+  for (int i = 0; i < 3; ++i) {
+    if (i == 2 && !small_ok) continue;
+    const double tm = double((M + kTile[i] - 1) / kTile[i]), tn = double((N + kTile[i] - 1) / kTile[i]);
+    const double work = 2.0 * tm * tn * kTile[i] * kTile[i] * double(K);
+    const double busy = tm * tn < sm_count ? tm * tn / sm_count : 1.0;
+    const double t = work / (kRate[i] * busy) * kBias[i];
+    if (best == 0 || t < best) {
+      best = t;
+      *variant = kVariant[i];
+    }
+  }
+  return best;
+}
+
 int launch_sgemm(DeviceCtx* c, const float* A, const float* B, float* C, int64_t M, int64_t N, int64_t K,
                  int variant, cudaStream_t s) {
   if (M > 0x7fffffffLL || N > 0x7fffffffLL || K > 0x7fffffffLL) return fail(VT_ERR_INVALID, "dimension overflows int");
-  if (variant == 0) {
-    // Large problems: 128x128 tiles.  When that grid cannot fill the GPU use 64x64 tiles, and when
-    // those fill less than half of it, 32x32 tiles that take K in bursts of 256 (measured: 256^3
-    // 6.6 against 12.3 us, 512^3 13.3 against 20.5 us, 768^3 32.7 against 28.8 us).
-    const long long big_tiles = ((M + 127) / 128) * ((N + 127) / 128);
-    const long long mid_tiles = ((M + 63) / 64) * ((N + 63) / 64);
-    variant = big_tiles >= c->sm_count ? VT_SGEMM_TILE128
-              : (2 * mid_tiles > c->sm_count || !sgemm_small_ok(A, B, C, N, K)) ? VT_SGEMM_TILE64
-                                                                            : VT_SGEMM_TILE32;
-  }
+  if (variant == 0) sgemm_tile_choice(A, B, C, M, N, K, c->sm_count, &variant);
   if (variant == VT_SGEMM_TILE32) return launch_small(A, B, C, int(M), int(N), int(K), s);
   if (variant == 1) return launch_tile<2, 2>(A, B, C, int(M), int(N), int(K), s);
   if (variant == 2) return launch_tile<1, 1>(A, B, C, int(M), int(N), int(K), s);

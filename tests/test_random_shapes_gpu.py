@@ -76,6 +76,25 @@ def test_random_row_panel_shapes(native):
             assert relfro(C.cpu().numpy(), ref) <= TOL, (m, n, k)
 
 
+def test_random_tall_shapes(native):
+    import torch
+    rng = np.random.default_rng(20260917 + 25)
+    st = native.torch_stream()
+    for _ in range(40):
+        m = int(rng.integers(1, 6000))
+        n = 4 * int(rng.integers(1, 17))
+        k = 4 * int(rng.integers(1, 1500))
+        a = rng.random((m, k), dtype=np.float32) * 2 - 1
+        b = rng.random((k, n), dtype=np.float32) * 2 - 1
+        ref = a.astype(np.float64) @ b.astype(np.float64)
+        A, B = torch.from_numpy(a).cuda(), torch.from_numpy(b).cuda()
+        for _rep in range(2):
+            C = torch.full((m, n), float("nan"), device="cuda")
+            native.sgemm(A, B, C, m, n, k, variant=native.VT_SGEMM_TALL_TF32X3, where=native.VT_DEVICE, stream=st)
+            native.sync(0, st)
+            assert relfro(C.cpu().numpy(), ref) <= TOL, (m, n, k)
+
+
 def test_random_int8_shapes(native):
     import torch
     rng = np.random.default_rng(20260917 + 23)

@@ -132,6 +132,43 @@ def test_row_panel_kernel(native):
                      where=native.VT_DEVICE, stream=st)
 
 
+def test_tall_kernel(native):
+    """TALL_TF32X3: A streamed in slabs of 128 rows against up to 16, 32 or 64 columns; ragged M, N and K, K splits,
+    one slab, same-sign data, reruns bit-identical, the automatic choice, and refusal of N > 64 or N % 4 != 0."""
+    import torch
+    gen = torch.Generator(device="cuda").manual_seed(20260917 + 10)
+    st = native.torch_stream()
+    for (m, n, k) in ((128, 16, 128), (128, 4, 64), (300, 12, 100), (1000, 32, 1028), (999, 64, 516), (2048, 8, 2048),
+                      (4096, 48, 512), (130, 20, 36), (1, 4, 4), (8192, 16, 8192), (8192, 64, 8192), (65536, 16, 1024),
+                      (1024, 64, 16384), (20000, 36, 260), (257, 64, 8192), (100, 16, 65536)):
+        for positive in (False, True):
+            A = torch.rand((m, k), device="cuda", generator=gen)
+            B = torch.rand((k, n), device="cuda", generator=gen)
+            if not positive:
+                A, B = A * 2 - 1, B * 2 - 1
+            ref = A.double() @ B.double()
+            C = torch.full((m, n), float("nan"), device="cuda")
+            native.sgemm(A, B, C, m, n, k, variant=native.VT_SGEMM_TALL_TF32X3, where=native.VT_DEVICE, stream=st)
+            native.sync(0, st)
+            assert float((C.double() - ref).norm() / ref.norm()) <= TOL / 3, (m, n, k, positive)
+            C2 = torch.full((m, n), float("nan"), device="cuda")
+            native.sgemm(A, B, C2, m, n, k, variant=native.VT_SGEMM_TALL_TF32X3, where=native.VT_DEVICE, stream=st)
+            native.sync(0, st)
+            assert torch.equal(C, C2), (m, n, k)
+    A = torch.rand((4096, 4096), device="cuda", generator=gen) * 2 - 1
+    B = torch.rand((4096, 32), device="cuda", generator=gen) * 2 - 1
+    C, Ct = torch.empty((4096, 32), device="cuda"), torch.empty((4096, 32), device="cuda")
+    native.sgemm(A, B, C, 4096, 32, 4096, where=native.VT_DEVICE, stream=st)
+    native.sgemm(A, B, Ct, 4096, 32, 4096, variant=native.VT_SGEMM_TALL_TF32X3, where=native.VT_DEVICE, stream=st)
+    native.sync(0, st)
+    assert torch.equal(C, Ct)              # the automatic choice for this shape is the tall kernel
+    for (m, n, k) in ((256, 68, 256), (256, 18, 256), (256, 16, 258)):
+        with pytest.raises(native.NativeError):
+            native.sgemm(torch.zeros((m, k), device="cuda"), torch.zeros((k, n), device="cuda"),
+                         torch.zeros((m, n), device="cuda"), m, n, k, variant=native.VT_SGEMM_TALL_TF32X3,
+                         where=native.VT_DEVICE, stream=st)
+
+
 def test_non_finite_inputs(native):
     """Infinities and NaNs: the true-fp32 kernels give IEEE results (same NaN and infinity pattern as a float32
     product).  The 3xTF32 kernels compute x * inf as hi * inf + lo * inf, which is NaN where lo is zero or of the
@@ -141,7 +178,7 @@ def test_non_finite_inputs(native):
     gen = torch.Generator(device="cuda").manual_seed(20260917 + 9)
     st = native.torch_stream()
     for (m, n, k, variants) in ((16, 1024, 1024, (3, 5, 6)), (96, 2048, 2048, (2, 8)), (512, 1024, 1024, (1, 2, 4, 7)),
-                                (64, 64, 64, (0,))):
+                                (2048, 32, 1024, (7, 9)), (64, 64, 64, (0,))):
         A = torch.rand((m, k), device="cuda", generator=gen) * 2 - 1
         B = torch.rand((k, n), device="cuda", generator=gen) * 2 - 1
         A[0, 0], B[3, 5], A[2, 2] = float("inf"), float("-inf"), float("nan")

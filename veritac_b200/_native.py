@@ -44,6 +44,7 @@ VT_SGEMM_SKINNY_TF32X3 = 5
 VT_SGEMM_SKINNY_MMA_SYNC = 6
 VT_SGEMM_TILE32 = 7
 VT_SGEMM_PANEL_TF32X3 = 8
+VT_SGEMM_TALL_TF32X3 = 9
 
 # Every symbol include/veritac_b200.h declares, with its ctypes signature.
 SIGNATURES = {

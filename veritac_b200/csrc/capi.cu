@@ -313,7 +313,7 @@ int vt_sgemm(int dev, const float* A, const float* B, float* C, int64_t M, int64
   if (where != VT_HOST && where != VT_DEVICE) return fail(VT_ERR_INVALID, "where must be VT_HOST or VT_DEVICE");
   if (M < 1 || N < 1 || K < 1) return fail(VT_ERR_INVALID, "dimensions must be positive");
   if (M > 0x7fffffffLL || N > 0x7fffffffLL || K > 0x7fffffffLL) return fail(VT_ERR_INVALID, "dimension overflows int");
-  if (variant < VT_SGEMM_AUTO || variant > VT_SGEMM_PANEL_TF32X3) return fail(VT_ERR_INVALID, "unknown sgemm variant %d", variant);
+  if (variant < VT_SGEMM_AUTO || variant > VT_SGEMM_TALL_TF32X3) return fail(VT_ERR_INVALID, "unknown sgemm variant %d", variant);
   DeviceCtx* c = ctx_for(dev);
   if (!c) return VT_ERR_CUDA;
   cudaStream_t s = where == VT_HOST ? c->stream : pick_stream(c, stream);
@@ -346,6 +346,11 @@ int vt_sgemm(int dev, const float* A, const float* B, float* C, int64_t M, int64
       double(N) * double(K) >= (M <= 32 ? 1.0e6 : M <= 2 * SKINNY_UMMA_MAX_ROWS ? 4.0e6 : 1.6e7) &&
       sgemm_skinny_umma_supported(dA, dB, dC, 1, N, K))
     variant = VT_SGEMM_PANEL_TF32X3;
+  // Few columns against a large A: the mirror image (measured ahead of the 32-wide tile kernel from 4 Mi elements of
+  // A up to 32 columns, from 12 Mi up to 64).
+  if (variant == VT_SGEMM_AUTO && N <= 64 && K >= 256 && double(M) * double(K) >= (N <= 32 ? 4.0e6 : 1.2e7) &&
+      sgemm_tall_umma_supported(dA, dB, dC, M, N, K))
+    variant = VT_SGEMM_TALL_TF32X3;
   // Large products go to the tensor cores (3xTF32, measured ~1e-6 relative Frobenius error at any K) when that
   // is clearly faster than the best FFMA tile kernel.  Its time is modelled as two launches (6 us), the pass that
   // writes the lo parts and the write of C (8 bytes per element of A and B, 4 per element of C, at ~5.5 TB/s) and
@@ -363,7 +368,19 @@ int vt_sgemm(int dev, const float* A, const float* B, float* C, int64_t M, int64
     if (t_tc < 0.9 * t_tile) variant = VT_SGEMM_TF32X3;
   }
   int rc;
-  if (variant == VT_SGEMM_PANEL_TF32X3) {
+  if (variant == VT_SGEMM_TALL_TF32X3) {
+    if (!sgemm_tall_umma_supported(dA, dB, dC, M, N, K))
+      return fail(VT_ERR_UNSUPPORTED,
+                  "tall tensor-core kernel needs N <= 64, N %% 4 == 0, K %% 4 == 0 and 16-byte aligned A and C");
+    int max_parts;
+    size_t cat_bytes;
+    sgemm_tall_umma_plan(M, N, K, c->sm_count, &max_parts, &cat_bytes);
+    // One scratch block: the partial tiles, then [B | B lo].
+    const size_t pbytes = max_parts > 1 ? ((size_t(max_parts) * size_t(M) * size_t(N) * 4 + 255) & ~size_t(255)) : 0;
+    float* scratch = static_cast<float*>(ctx_workspace(c, 3, pbytes + cat_bytes));
+    if (!scratch) return VT_ERR_CUDA;
+    rc = launch_sgemm_tall_umma(c, dA, dB, dC, pbytes ? scratch : nullptr, c->tickets, scratch + pbytes / 4, M, N, K, s);
+  } else if (variant == VT_SGEMM_PANEL_TF32X3) {
     if (!sgemm_skinny_umma_supported(dA, dB, dC, 1, N, K))
       return fail(VT_ERR_UNSUPPORTED, "row-panel kernel needs N %% 4 == 0, K %% 4 == 0 and 16-byte aligned operands");
     size_t pbytes = 0;

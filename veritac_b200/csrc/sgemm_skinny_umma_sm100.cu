@@ -56,8 +56,15 @@ constexpr int KU_SMEM_LIMIT = 227 * 1024;
 //            while it is drained);
 //   WINDOW   chunks a pipe accumulates in tensor memory between folds into registers.
 // Tensor memory per pipe: the accumulators, then the B lo buffers of 32 columns each.
-template <int MT, int PIPES, int SETS, bool STACKED, int ACC_BUFS, int WINDOW>
+//   TALL     the mirror image, for C (M x N) = A (M x K) * B (K x N) with few columns (N <= MT) and A the
+//            traffic: the streamed matrix is A, whose 128-row slabs are the tensor core's 128-row operand in the
+//            ordinary K-major layout (so the product is not transposed and a TMEM lane is a row of C); the
+//            small operand is [B | B lo], N-major as B lies in memory (MN-major TF32, the 32-byte-atom swizzle),
+//            prepared once per call in a scratch array of K x 2 MT floats; the splitting warps write A lo to
+//            tensor memory and have nothing to write to shared memory.
+template <int MT, int PIPES, int SETS, bool STACKED, int ACC_BUFS, int WINDOW, bool TALL = false>
 struct KuShape {
+  static constexpr bool kTall = TALL;
   static constexpr int kRows = MT;
   static constexpr int kPipes = PIPES;
   static constexpr int kSets = SETS;
@@ -114,6 +121,10 @@ __global__ void __launch_bounds__(Shape::kThreads, KU_CTAS_PER_SM)
 sgemm_skinny_umma_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmA,
                          float* __restrict__ C, float* __restrict__ partials, int* __restrict__ tickets, int M, int N,
                          SkinnySched sc, int* __restrict__ status) {
+  // Names follow the wide form (B streamed, A the small operand).  In the tall form `tmB` is the map of the
+  // streamed matrix (A: boxes of 32 floats of K x 128 rows) and `tmA` that of the small one ([B | B lo]: boxes
+  // of 32 columns x 32 rows of K); M and N are the rows and columns of C in both.
+  constexpr bool TALL = Shape::kTall;
   constexpr int MT = Shape::kRows;
   constexpr int KU_PIPES = Shape::kPipes;
   constexpr int KU_ACC_BUFS = Shape::kAccBufs;
@@ -174,7 +185,7 @@ sgemm_skinny_umma_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_c
       bool ok = true;
       SkinnySegment seg;
       for (int idx = 0; ok && sched_segment(sc, cta, idx, seg); ++idx) {
-        const int n0 = seg.slab * SKINNY_COLS;
+        const int n0 = seg.slab * SKINNY_COLS;     // first column of B (wide) or first row of A (tall) of the slab
         for (int ch = seg.chunk_beg; ch < seg.chunk_end; ++ch) {
           if (!mbar_wait(&ps->empty[stage], phase ^ 1, abort_word, KSTAT_WAIT_EXPIRED_PRODUCER)) {
             ok = false;
@@ -182,10 +193,18 @@ sgemm_skinny_umma_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_c
           }
           uint64_t* full = &ps->raw_full[stage];
           uint8_t* dst = tiles + size_t(stage) * KU_STAGE_BYTES;
-          mbar_arrive_expect_tx(full, KU_B_BYTES + KU_A_BYTES);
+          if (TALL) {
+            mbar_arrive_expect_tx(full, KU_B_BYTES + 2 * KU_A_BYTES);
+            tma_load_2d(dst, &tmB, full, ch * SKINNY_KC, n0);
 #pragma unroll
-          for (int b = 0; b < 4; ++b) tma_load_2d(dst + b * KU_BOX_BYTES, &tmB, full, n0 + 32 * b, ch * SKINNY_KC);
-          tma_load_2d(dst + KU_B_BYTES, &tmA, full, ch * SKINNY_KC, 0);
+            for (int b = 0; b < 2 * MT / 32; ++b)
+              tma_load_2d(dst + KU_B_BYTES + b * KU_BOX_BYTES, &tmA, full, 32 * b, ch * SKINNY_KC);
+          } else {
+            mbar_arrive_expect_tx(full, KU_B_BYTES + KU_A_BYTES);
+#pragma unroll
+            for (int b = 0; b < 4; ++b) tma_load_2d(dst + b * KU_BOX_BYTES, &tmB, full, n0 + 32 * b, ch * SKINNY_KC);
+            tma_load_2d(dst + KU_B_BYTES, &tmA, full, ch * SKINNY_KC, 0);
+          }
           filled |= 1u << stage;
           fill_parity = (fill_parity & ~(1u << stage)) | (phase << stage);
           if (++stage == KU_STAGES) {
@@ -216,8 +235,11 @@ sgemm_skinny_umma_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_c
     // ------------------------------ MMA issuer of pipe (warp - 1) ------------------------------
     if (lane == 0) {
       const int pipe = warp - 1;
-      constexpr uint32_t idesc_pair = umma_instr_desc(UMMA_D_F32, UMMA_AB_TF32, true, false, 128, KU_STACKED ? 2 * MT : MT);
-      constexpr uint32_t idesc_lo = umma_instr_desc(UMMA_D_F32, UMMA_AB_TF32, false, false, 128, MT);
+      // wide: 128-row operand MN-major (B as stored), small operand K-major; tall: 128-row operand K-major
+      // (A as stored), small operand MN-major ([B | B lo] as stored)
+      constexpr uint32_t idesc_pair =
+          umma_instr_desc(UMMA_D_F32, UMMA_AB_TF32, !TALL, TALL, 128, KU_STACKED ? 2 * MT : MT);
+      constexpr uint32_t idesc_lo = umma_instr_desc(UMMA_D_F32, UMMA_AB_TF32, false, TALL, 128, MT);
       // Descriptors are kept as a constant high word and a low word that only ever has a constant
       // added to it, and the ring position is counted, not divided.
       constexpr uint32_t kMn32Hi = (512u >> 4) | (1u << 14) | (1u << 29);    // stride offset, version, swizzle mode 1
@@ -258,6 +280,16 @@ sgemm_skinny_umma_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_c
             const uint32_t lo_tmem = pipe_tmem + uint32_t(KU_LO_COL) + lo_buf * 32u;
 #pragma unroll
             for (int ks = 0; ks < SKINNY_KC / 8; ++ks) {
+              if (TALL) {
+                static_assert(!TALL || KU_STACKED, "the tall form is stacked");
+                // streamed A: K-major, 32 bytes per K step; [B | B lo]: N-major boxes, 1 KiB (8 rows) per K step
+                const uint64_t big = make_desc(((tiles_lo + stage * (KU_STAGE_BYTES >> 4)) | (1u << 16)) + ks * (32u >> 4), kSw128Hi);
+                const uint64_t small = make_desc(
+                    ((tiles_lo + stage * (KU_STAGE_BYTES >> 4) + (KU_B_BYTES >> 4)) | ((4096u >> 4) << 16)) + ks * (1024u >> 4), kMn32Hi);
+                umma_tf32<1>(d_tmem, big, small, idesc_pair, (ks == 0 && opens) ? 0u : 1u);
+                umma_tf32_a_tmem(d_tmem, lo_tmem + uint32_t(ks * 8), small, idesc_lo, 1u);
+                continue;
+              }
               const uint64_t a_desc = make_desc(a_lo32 + ks * (32u >> 4), kSw128Hi);
               const uint64_t b_desc = make_desc(b_lo32 + ks * (1024u >> 4), kMn32Hi);
               umma_tf32<1>(d_tmem, b_desc, a_desc, idesc_pair, (ks == 0 && opens) ? 0u : 1u);
@@ -346,14 +378,32 @@ sgemm_skinny_umma_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_c
           // 128 bytes, 32-byte units XOR-swizzled with (row % 4).
           const float* box = reinterpret_cast<const float*>(stage_ptr + quarter * KU_BOX_BYTES);
           uint32_t lo_a[16], lo_b[16];
+          if (TALL) {
+            // This thread's row of the slab: 128 bytes, 16-byte units XOR-swizzled with (row % 8).
+            const int row = quarter * 32 + lane;
+            const uint32_t row_addr = smem_u32(stage_ptr) + uint32_t(row) * 128u;
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+              uint32_t x0, x1, x2, x3;
+              asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                           : "=r"(x0), "=r"(x1), "=r"(x2), "=r"(x3)
+                           : "r"(row_addr + (uint32_t(u ^ (row & 7)) << 4)));
+              uint32_t* out = u < 4 ? &lo_a[4 * u] : &lo_b[4 * (u - 4)];
+              out[0] = lo_part(x0);
+              out[1] = lo_part(x1);
+              out[2] = lo_part(x2);
+              out[3] = lo_part(x3);
+            }
+          } else {
 #pragma unroll
           for (int k = 0; k < 16; ++k)
             lo_a[k] = lo_part(__float_as_uint(box[k * 32 + (((lane >> 3) ^ (k & 3)) << 3) + (lane & 7)]));
 #pragma unroll
           for (int k = 16; k < 32; ++k)
             lo_b[k - 16] = lo_part(__float_as_uint(box[k * 32 + (((lane >> 3) ^ (k & 3)) << 3) + (lane & 7)]));
+          }
 #pragma unroll
-          for (int v = 0; v < MT / 16; ++v) {
+          for (int v = 0; v < (TALL ? 0 : MT / 16); ++v) {
             // A lo under A, position for position (both blocks carry the same swizzle)
             const uint32_t a_addr = smem_u32(stage_ptr + KU_B_BYTES) + uint32_t(v * 128 + t) * 16u;
             uint32_t x0, x1, x2, x3;
@@ -414,6 +464,20 @@ sgemm_skinny_umma_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_c
         // The tile of this piece goes to C (the slab has one piece) or to its slot among the slab's partial tiles.
         float* dst = seg.parts == 1 ? C : partials + size_t(seg.part) * size_t(M) * size_t(N);
         const int col = seg.slab * SKINNY_COLS + quarter * 32 + lane;
+        if (TALL) {
+          // `col` is this thread's row of C; its MS sums are consecutive columns of that row
+          if (col < M) {
+#pragma unroll
+            for (int m = 0; m < MS; ++m)
+              if (set * MS + m < N) dst[size_t(col) * N + set * MS + m] = master[m];
+          }
+          if (seg.parts > 1) {
+            const int rows = M - seg.slab * SKINNY_COLS < SKINNY_COLS ? M - seg.slab * SKINNY_COLS : SKINNY_COLS;
+            skinny_finish_block<128 * KU_SETS>(seg, set * 128 + t, 1, &ps->last_flag, tickets, partials, C,
+                                               size_t(M) * size_t(N), size_t(seg.slab) * SKINNY_COLS * size_t(N),
+                                               rows * N);
+          }
+        } else {
         if (col < N) {
 #pragma unroll
           for (int m = 0; m < MS; ++m)
@@ -421,6 +485,7 @@ sgemm_skinny_umma_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_c
         }
         if (seg.parts > 1)
           skinny_finish_piece<128 * KU_SETS, MT>(seg, set * 128 + t, 1, &ps->last_flag, tickets, partials, C, M, N);
+        }
       }
     }
   }
@@ -477,6 +542,61 @@ int launch_shape(DeviceCtx* c, uint32_t attr_bit, const float* A, const float* B
   return VT_OK;
 }
 
+// Tall form: up to 16, 32 or 64 columns of C.
+using KuTall16 = KuShape<16, 2, 1, true, 2, 4, true>;
+using KuTall32 = KuShape<32, 2, 1, true, 2, 4, true>;
+using KuTall64 = KuShape<64, 1, 2, true, 2, 4, true>;
+using KuTall64Large = KuShape<64, 2, 1, true, 1, 4, true>;   // from 32 Mi elements of A
+
+// [B | B lo] for the tall form: row k holds B[k][0..N) padded with zeros to `nt` columns, then their lo parts.
+__global__ void __launch_bounds__(256) tall_b_and_lo_kernel(const float* __restrict__ B, float* __restrict__ out, int64_t K,
+                                                            int N, int nt) {
+  const int64_t total = K * 2 * nt;
+  const int64_t stride = int64_t(gridDim.x) * blockDim.x;
+  for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const int64_t k = i / (2 * nt);
+    const int j = int(i - k * 2 * nt);
+    const int col = j < nt ? j : j - nt;
+    float v = 0.f;
+    if (col < N) {
+      v = B[k * N + col];
+      if (j >= nt) v = __uint_as_float(lo_part(__float_as_uint(v)));
+    }
+    out[i] = v;
+  }
+}
+
+template <class Shape>
+int launch_tall_shape(DeviceCtx* c, uint32_t attr_bit, const float* A, const float* B, float* C, float* partials,
+                      int* tickets, float* b_and_lo, int64_t M, int64_t N, int64_t K, cudaStream_t s) {
+  constexpr int NT = Shape::kRows;
+  int ctas;
+  const SkinnySched sc = make_skinny_sched(M, K, c->sm_count, KU_CTAS_PER_SM, Shape::kPieceOverhead, &ctas);
+  if (skinny_max_parts(sc) > 1 && (!partials || !tickets)) return fail(VT_ERR_INVALID, "tall K split needs scratch memory");
+  if (sc.slabs > kTicketCount)
+    return fail(VT_ERR_UNSUPPORTED, "M = %lld has more slabs than the library keeps tickets for", (long long)M);
+  const int64_t total = K * 2 * NT;
+  const int blocks = int(total / 256 + 1 < int64_t(c->sm_count) * 8 ? total / 256 + 1 : int64_t(c->sm_count) * 8);
+  tall_b_and_lo_kernel<<<blocks, 256, 0, s>>>(B, b_and_lo, K, int(N), NT);
+  count_launch();
+  CUtensorMap tmBig, tmSmall;
+  int rc = encode_tmap_2d(&tmBig, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, A, uint64_t(K), uint64_t(M), uint64_t(K) * 4, 32, 128);
+  if (rc) return rc;
+  rc = encode_tmap_2d(&tmSmall, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, b_and_lo, uint64_t(2 * NT), uint64_t(K),
+                      uint64_t(2 * NT) * 4, 32, 32, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B);
+  if (rc) return rc;
+  if (!(c->func_attr_mask & attr_bit)) {
+    VT_CUDA(cudaFuncSetAttribute(sgemm_skinny_umma_kernel<Shape>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 int(Shape::kSmemBytes)));
+    c->func_attr_mask |= attr_bit;
+  }
+  sgemm_skinny_umma_kernel<Shape><<<ctas, Shape::kThreads, Shape::kSmemBytes, s>>>(tmBig, tmSmall, C, partials, tickets,
+                                                                                     int(M), int(N), sc, c->status);
+  count_launch();
+  VT_CUDA(cudaGetLastError());
+  return VT_OK;
+}
+
 int piece_overhead_for(int64_t M) {
   return M <= 16 ? KuShape16::kPieceOverhead : M <= 32 ? KuShape32::kPieceOverhead
          : M <= 64 ? KuShape64::kPieceOverhead : KuShape128::kPieceOverhead;
@@ -488,6 +608,36 @@ void sgemm_skinny_umma_plan(int64_t M, int64_t N, int64_t K, int sm_count, int* 
   const SkinnySched sc = make_skinny_sched(N, K, sm_count, KU_CTAS_PER_SM, piece_overhead_for(M), ctas);
   *slabs = sc.slabs;
   *max_parts = skinny_max_parts(sc);
+}
+
+// Tall form: C (M x N) = A (M x K) * B (K x N) with N <= 64 and A streamed once.
+int sgemm_tall_umma_panel(int64_t N) { return N <= 16 ? 16 : N <= 32 ? 32 : 64; }
+
+void sgemm_tall_umma_plan(int64_t M, int64_t N, int64_t K, int sm_count, int* max_parts, size_t* b_and_lo_bytes) {
+  int ctas;
+  const int overhead = N <= 16 ? KuTall16::kPieceOverhead : N <= 32 ? KuTall32::kPieceOverhead : KuTall64::kPieceOverhead;
+  const SkinnySched sc = make_skinny_sched(M, K, sm_count, KU_CTAS_PER_SM, overhead, &ctas);
+  *max_parts = skinny_max_parts(sc);
+  *b_and_lo_bytes = size_t(K) * 2 * size_t(sgemm_tall_umma_panel(N)) * 4;
+}
+
+bool sgemm_tall_umma_supported(const float* A, const float* B, const float* C, int64_t M, int64_t N, int64_t K) {
+  (void)B;
+  return N >= 4 && N <= 64 && N % 4 == 0 && M >= 1 && K % 4 == 0 && K >= 4 && M < (1LL << 31) && K < (1LL << 31) &&
+         ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(C)) & 15) == 0;
+}
+
+int launch_sgemm_tall_umma(DeviceCtx* c, const float* A, const float* B, float* C, float* partials, int* tickets,
+                           float* b_and_lo, int64_t M, int64_t N, int64_t K, cudaStream_t s) {
+  if (!sgemm_tall_umma_supported(A, B, C, M, N, K))
+    return fail(VT_ERR_UNSUPPORTED,
+                "tall tensor-core kernel needs N <= 64, N %% 4 == 0, K %% 4 == 0 and 16-byte aligned A and C");
+  if (!b_and_lo) return fail(VT_ERR_INVALID, "tall kernel needs scratch memory for [B | B lo]");
+  if (N <= 16) return launch_tall_shape<KuTall16>(c, 1u << 26, A, B, C, partials, tickets, b_and_lo, M, N, K, s);
+  if (N <= 32) return launch_tall_shape<KuTall32>(c, 1u << 27, A, B, C, partials, tickets, b_and_lo, M, N, K, s);
+  if (double(M) * double(K) >= 3.2e7)
+    return launch_tall_shape<KuTall64Large>(c, 1u << 29, A, B, C, partials, tickets, b_and_lo, M, N, K, s);
+  return launch_tall_shape<KuTall64>(c, 1u << 28, A, B, C, partials, tickets, b_and_lo, M, N, K, s);
 }
 
 bool sgemm_skinny_umma_supported(const float* A, const float* B, const float* C, int64_t M, int64_t N, int64_t K) {

@@ -185,6 +185,47 @@ __device__ __forceinline__ void skinny_finish_piece(const SkinnySegment& seg, in
   }
   asm volatile("bar.sync %0, %1;" ::"r"(bar_id), "n"(kThreads) : "memory");   // last_flag is rewritten by the next piece
 }
+
+// The same for a slab whose tile is one contiguous block of C (the tall form: 128 whole rows of C):
+// `block_elems` floats (a multiple of 4) starting `block_off` floats into C and into every piece's copy.
+template <int kThreads>
+__device__ __forceinline__ void skinny_finish_block(const SkinnySegment& seg, int tid, int bar_id, int* last_flag,
+                                                    int* __restrict__ tickets, const float* __restrict__ partials,
+                                                    float* __restrict__ C, size_t piece, size_t block_off,
+                                                    int block_elems) {
+  __threadfence();
+  asm volatile("bar.sync %0, %1;" ::"r"(bar_id), "n"(kThreads) : "memory");
+  if (tid == 0) {
+    const int arrived = atomicAdd(&tickets[seg.slab], 1);
+    *last_flag = (arrived == seg.parts - 1) ? 1 : 0;
+  }
+  asm volatile("bar.sync %0, %1;" ::"r"(bar_id), "n"(kThreads) : "memory");
+  if (*last_flag) {
+    __threadfence();
+    constexpr int kBatch = 4;   // pieces loaded together
+    for (int v = tid; v < block_elems / 4; v += kThreads) {
+      const size_t off = block_off + size_t(v) * 4;
+      float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int p0 = 0; p0 < seg.parts; p0 += kBatch) {
+        float4 x[kBatch];
+#pragma unroll
+        for (int q = 0; q < kBatch; ++q)
+          x[q] = p0 + q < seg.parts ? __ldcg(reinterpret_cast<const float4*>(partials + size_t(p0 + q) * piece + off))
+                                    : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int q = 0; q < kBatch; ++q) {
+          sum.x += x[q].x;
+          sum.y += x[q].y;
+          sum.z += x[q].z;
+          sum.w += x[q].w;
+        }
+      }
+      *reinterpret_cast<float4*>(C + off) = sum;
+    }
+    if (tid == 0) tickets[seg.slab] = 0;
+  }
+  asm volatile("bar.sync %0, %1;" ::"r"(bar_id), "n"(kThreads) : "memory");   // last_flag is rewritten by the next piece
+}
 #endif
 
 }  // namespace vt

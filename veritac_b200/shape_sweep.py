@@ -27,7 +27,7 @@ def main(argv) -> int:
     torch.backends.cuda.matmul.allow_tf32 = False
     shapes = [tuple(int(x) for x in a.lower().split("x")) for a in argv] or list(GRID)
     names = {nv.VT_SGEMM_TILE128: "tile128", nv.VT_SGEMM_TILE64: "tile64", nv.VT_SGEMM_TILE32: "tile32",
-             nv.VT_SGEMM_TF32X3: "tf32x3", nv.VT_SGEMM_PANEL_TF32X3: "panel"}
+             nv.VT_SGEMM_TF32X3: "tf32x3", nv.VT_SGEMM_PANEL_TF32X3: "panel", nv.VT_SGEMM_TALL_TF32X3: "tall"}
     st = nv.torch_stream()
 
     def timed(fn) -> float:

@@ -23,6 +23,9 @@
 // option of the shape.)  Accumulators are folded into fp32 registers every few chunks (the tensor
 // core's own accumulation truncates).
 //
+// The tall form (few columns of B against a large A) is the same pipeline with the roles exchanged; see
+// KuShape below.
+//
 // One CTA per SM.  Warp 0 is the TMA producer (a ring of stages of B, A and room for A lo).  Small MMAs
 // cost their issuing thread, and the warps that feed them, more time than the loads take, so
 // the chunks of the ring are dealt to KU_PIPES independent pipes (chunk at ring position p goes to

@@ -82,8 +82,9 @@ enum {
  *   SKINNY_TF32X3     M <= 16 on the tensor cores (3xTF32): one TMA-fed launch, tcgen05 with B used as it
  *                     lies in memory; when K % 4 != 0 or A is not 16-byte aligned, SKINNY_MMA_SYNC runs
  *   SKINNY_MMA_SYNC   the same stream of B with the products on mma.sync TF32 (any K, any alignment of A)
- *   TALL_TF32X3       the mirror image of PANEL_TF32X3 for few columns (N <= 64, N % 4 == 0, K % 4 == 0, 16-byte
- *                     aligned A and C): A is streamed once, 128 rows at a time, against [B | B lo]
+ *   TALL_TF32X3       the mirror image of PANEL_TF32X3 for few columns (N % 4 == 0, K % 4 == 0, 16-byte aligned A
+ *                     and C): A is streamed once per panel of up to 128 columns, 128 rows at a time, against
+ *                     [B | B lo] of the panel
  *   (3xTF32 forms and non-finite inputs: x * inf is formed as hi * inf + lo * inf, which is NaN where lo is zero
  *    or of the other sign; where an operand row or column holds an infinity, the TILE* and SKINNY variants give
  *    the IEEE result and the 3xTF32 forms may give NaN in its place.)

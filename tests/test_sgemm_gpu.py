@@ -133,14 +133,16 @@ def test_row_panel_kernel(native):
 
 
 def test_tall_kernel(native):
-    """TALL_TF32X3: A streamed in slabs of 128 rows against up to 16, 32 or 64 columns; ragged M, N and K, K splits,
-    one slab, same-sign data, reruns bit-identical, the automatic choice, and refusal of N > 64 or N % 4 != 0."""
+    """TALL_TF32X3: A streamed in slabs of 128 rows against panels of up to 16, 32, 64 or 128 columns (wider C in
+    several panels); ragged M, N and K, K splits, one slab, same-sign data, reruns bit-identical, the automatic
+    choice, and refusal of N % 4 != 0 or K % 4 != 0."""
     import torch
     gen = torch.Generator(device="cuda").manual_seed(20260917 + 10)
     st = native.torch_stream()
     for (m, n, k) in ((128, 16, 128), (128, 4, 64), (300, 12, 100), (1000, 32, 1028), (999, 64, 516), (2048, 8, 2048),
                       (4096, 48, 512), (130, 20, 36), (1, 4, 4), (8192, 16, 8192), (8192, 64, 8192), (65536, 16, 1024),
-                      (1024, 64, 16384), (20000, 36, 260), (257, 64, 8192), (100, 16, 65536)):
+                      (1024, 64, 16384), (20000, 36, 260), (257, 64, 8192), (100, 16, 65536), (512, 128, 512),
+                      (1000, 200, 1000), (700, 256, 2048), (300, 132, 260), (4096, 300, 1024), (8192, 128, 8192)):
         for positive in (False, True):
             A = torch.rand((m, k), device="cuda", generator=gen)
             B = torch.rand((k, n), device="cuda", generator=gen)
@@ -162,7 +164,7 @@ def test_tall_kernel(native):
     native.sgemm(A, B, Ct, 4096, 32, 4096, variant=native.VT_SGEMM_TALL_TF32X3, where=native.VT_DEVICE, stream=st)
     native.sync(0, st)
     assert torch.equal(C, Ct)              # the automatic choice for this shape is the tall kernel
-    for (m, n, k) in ((256, 68, 256), (256, 18, 256), (256, 16, 258)):
+    for (m, n, k) in ((256, 18, 256), (256, 16, 258)):
         with pytest.raises(native.NativeError):
             native.sgemm(torch.zeros((m, k), device="cuda"), torch.zeros((k, n), device="cuda"),
                          torch.zeros((m, n), device="cuda"), m, n, k, variant=native.VT_SGEMM_TALL_TF32X3,

@@ -346,10 +346,11 @@ int vt_sgemm(int dev, const float* A, const float* B, float* C, int64_t M, int64
       double(N) * double(K) >= (M <= 32 ? 1.0e6 : M <= 2 * SKINNY_UMMA_MAX_ROWS ? 4.0e6 : 1.6e7) &&
       sgemm_skinny_umma_supported(dA, dB, dC, 1, N, K))
     variant = VT_SGEMM_PANEL_TF32X3;
-  // Few columns against a large A: the mirror image (measured ahead of the 32-wide tile kernel from 4 Mi elements of
-  // A up to 32 columns, from 12 Mi up to 64).
-  if (variant == VT_SGEMM_AUTO && N <= 64 && K >= 256 && double(M) * double(K) >= (N <= 32 ? 4.0e6 : 1.2e7) &&
-      sgemm_tall_umma_supported(dA, dB, dC, M, N, K))
+  // Few columns against a large A: the mirror image (measured ahead of the tile kernels and the 3xTF32 pair kernel
+  // from 4 Mi elements of A up to 32 columns, from 12 Mi up to 64, from 16 Mi up to 128; two panels of 128 columns
+  // are level with the pair kernel and stay there).
+  if (variant == VT_SGEMM_AUTO && N <= SKINNY_UMMA_MAX_ROWS && K >= 256 &&
+      double(M) * double(K) >= (N <= 32 ? 4.0e6 : N <= 64 ? 1.2e7 : 1.6e7) && sgemm_tall_umma_supported(dA, dB, dC, M, N, K))
     variant = VT_SGEMM_TALL_TF32X3;
   // Large products go to the tensor cores (3xTF32, measured ~1e-6 relative Frobenius error at any K) when that
   // is clearly faster than the best FFMA tile kernel.  Its time is modelled as two launches (6 us), the pass that
@@ -370,16 +371,28 @@ int vt_sgemm(int dev, const float* A, const float* B, float* C, int64_t M, int64
   int rc;
   if (variant == VT_SGEMM_TALL_TF32X3) {
     if (!sgemm_tall_umma_supported(dA, dB, dC, M, N, K))
-      return fail(VT_ERR_UNSUPPORTED,
-                  "tall tensor-core kernel needs N <= 64, N %% 4 == 0, K %% 4 == 0 and 16-byte aligned A and C");
-    int max_parts;
-    size_t cat_bytes;
-    sgemm_tall_umma_plan(M, N, K, c->sm_count, &max_parts, &cat_bytes);
-    // One scratch block: the partial tiles, then [B | B lo].
-    const size_t pbytes = max_parts > 1 ? ((size_t(max_parts) * size_t(M) * size_t(N) * 4 + 255) & ~size_t(255)) : 0;
+      return fail(VT_ERR_UNSUPPORTED, "tall tensor-core kernel needs N %% 4 == 0, K %% 4 == 0 and 16-byte aligned A and C");
+    // Panels of up to 128 columns, one launch each, in stream order: the scratch (partial tiles, then [B | B lo])
+    // and the tickets are reused.
+    size_t pbytes = 0, cat_bytes = 0;
+    for (int64_t n0 = 0; n0 < N; n0 += SKINNY_UMMA_MAX_ROWS) {
+      const int64_t width = N - n0 < SKINNY_UMMA_MAX_ROWS ? N - n0 : SKINNY_UMMA_MAX_ROWS;
+      int max_parts;
+      size_t cat;
+      sgemm_tall_umma_plan(M, width, K, c->sm_count, &max_parts, &cat);
+      const size_t need = max_parts > 1 ? size_t(max_parts) * size_t(M) * size_t(width) * 4 : 0;
+      if (need > pbytes) pbytes = need;
+      if (cat > cat_bytes) cat_bytes = cat;
+    }
+    pbytes = (pbytes + 255) & ~size_t(255);
     float* scratch = static_cast<float*>(ctx_workspace(c, 3, pbytes + cat_bytes));
     if (!scratch) return VT_ERR_CUDA;
-    rc = launch_sgemm_tall_umma(c, dA, dB, dC, pbytes ? scratch : nullptr, c->tickets, scratch + pbytes / 4, M, N, K, s);
+    rc = VT_OK;
+    for (int64_t n0 = 0; n0 < N && rc == VT_OK; n0 += SKINNY_UMMA_MAX_ROWS) {
+      const int64_t width = N - n0 < SKINNY_UMMA_MAX_ROWS ? N - n0 : SKINNY_UMMA_MAX_ROWS;
+      rc = launch_sgemm_tall_umma(c, dA, dB + n0, dC + n0, pbytes ? scratch : nullptr, c->tickets, scratch + pbytes / 4, M,
+                                  width, K, N, N, s);
+    }
   } else if (variant == VT_SGEMM_PANEL_TF32X3) {
     if (!sgemm_skinny_umma_supported(dA, dB, dC, 1, N, K))
       return fail(VT_ERR_UNSUPPORTED, "row-panel kernel needs N %% 4 == 0, K %% 4 == 0 and 16-byte aligned operands");

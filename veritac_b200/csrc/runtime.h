@@ -90,7 +90,7 @@ int launch_sgemm_skinny_umma(DeviceCtx* c, const float* A, const float* B, float
 void sgemm_tall_umma_plan(int64_t M, int64_t N, int64_t K, int sm_count, int* max_parts, size_t* b_and_lo_bytes);
 bool sgemm_tall_umma_supported(const float* A, const float* B, const float* C, int64_t M, int64_t N, int64_t K);
 int launch_sgemm_tall_umma(DeviceCtx* c, const float* A, const float* B, float* C, float* partials, int* tickets,
-                           float* b_and_lo, int64_t M, int64_t N, int64_t K, cudaStream_t s);
+                           float* b_and_lo, int64_t M, int64_t N, int64_t K, int64_t ldb, int64_t ldc, cudaStream_t s);
 size_t sgemm_skinny_partials_bytes(int64_t M, int64_t N, int64_t K, int sm_count, int* ksplit_out);
 int launch_i8_tile_program(DeviceCtx* c, const int8_t* A, const int8_t* B, int32_t* C, int64_t lda, int64_t ldb,
                            int64_t ldc, int64_t n_tiles, const int64_t* d_c_off, const int64_t* d_term_begin,

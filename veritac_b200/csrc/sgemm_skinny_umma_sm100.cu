@@ -123,10 +123,11 @@ template <class Shape>
 __global__ void __launch_bounds__(Shape::kThreads, KU_CTAS_PER_SM)
 sgemm_skinny_umma_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmA,
                          float* __restrict__ C, float* __restrict__ partials, int* __restrict__ tickets, int M, int N,
-                         SkinnySched sc, int* __restrict__ status) {
+                         int ldc, SkinnySched sc, int* __restrict__ status) {
   // Names follow the wide form (B streamed, A the small operand).  In the tall form `tmB` is the map of the
   // streamed matrix (A: boxes of 32 floats of K x 128 rows) and `tmA` that of the small one ([B | B lo]: boxes
-  // of 32 columns x 32 rows of K); M and N are the rows and columns of C in both.
+  // of 32 columns x 32 rows of K); M and N are the rows and columns of C in both.  `ldc` is the row pitch of C
+  // (tall form only: a launch may compute a panel of columns of a wider C; the partial tiles have pitch N).
   constexpr bool TALL = Shape::kTall;
   constexpr int MT = Shape::kRows;
   constexpr int KU_PIPES = Shape::kPipes;
@@ -470,15 +471,15 @@ sgemm_skinny_umma_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_c
         if (TALL) {
           // `col` is this thread's row of C; its MS sums are consecutive columns of that row
           if (col < M) {
+            const size_t pitch = seg.parts == 1 ? size_t(ldc) : size_t(N);
 #pragma unroll
             for (int m = 0; m < MS; ++m)
-              if (set * MS + m < N) dst[size_t(col) * N + set * MS + m] = master[m];
+              if (set * MS + m < N) dst[size_t(col) * pitch + set * MS + m] = master[m];
           }
           if (seg.parts > 1) {
             const int rows = M - seg.slab * SKINNY_COLS < SKINNY_COLS ? M - seg.slab * SKINNY_COLS : SKINNY_COLS;
             skinny_finish_block<128 * KU_SETS>(seg, set * 128 + t, 1, &ps->last_flag, tickets, partials, C,
-                                               size_t(M) * size_t(N), size_t(seg.slab) * SKINNY_COLS * size_t(N),
-                                               rows * N);
+                                               size_t(M) * size_t(N), seg.slab * SKINNY_COLS, rows, N, ldc);
           }
         } else {
         if (col < N) {
@@ -539,7 +540,7 @@ int launch_shape(DeviceCtx* c, uint32_t attr_bit, const float* A, const float* B
     c->func_attr_mask |= attr_bit;
   }
   sgemm_skinny_umma_kernel<Shape><<<ctas, Shape::kThreads, Shape::kSmemBytes, s>>>(tmB, tmA, C, partials, tickets, int(M),
-                                                                                     int(N), sc, c->status);
+                                                                                     int(N), int(N), sc, c->status);
   count_launch();
   VT_CUDA(cudaGetLastError());
   return VT_OK;
@@ -550,10 +551,12 @@ using KuTall16 = KuShape<16, 2, 1, true, 2, 4, true>;
 using KuTall32 = KuShape<32, 2, 1, true, 2, 4, true>;
 using KuTall64 = KuShape<64, 1, 2, true, 2, 4, true>;
 using KuTall64Large = KuShape<64, 2, 1, true, 1, 4, true>;   // from 32 Mi elements of A
+using KuTall128 = KuShape<128, 1, 2, true, 1, 4, true>;
 
 // [B | B lo] for the tall form: row k holds B[k][0..N) padded with zeros to `nt` columns, then their lo parts.
+// (B has row pitch `ldb`; the N columns are a panel of it.)
 __global__ void __launch_bounds__(256) tall_b_and_lo_kernel(const float* __restrict__ B, float* __restrict__ out, int64_t K,
-                                                            int N, int nt) {
+                                                            int N, int nt, int64_t ldb) {
   const int64_t total = K * 2 * nt;
   const int64_t stride = int64_t(gridDim.x) * blockDim.x;
   for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
@@ -562,7 +565,7 @@ __global__ void __launch_bounds__(256) tall_b_and_lo_kernel(const float* __restr
     const int col = j < nt ? j : j - nt;
     float v = 0.f;
     if (col < N) {
-      v = B[k * N + col];
+      v = B[k * ldb + col];
       if (j >= nt) v = __uint_as_float(lo_part(__float_as_uint(v)));
     }
     out[i] = v;
@@ -571,7 +574,8 @@ __global__ void __launch_bounds__(256) tall_b_and_lo_kernel(const float* __restr
 
 template <class Shape>
 int launch_tall_shape(DeviceCtx* c, uint32_t attr_bit, const float* A, const float* B, float* C, float* partials,
-                      int* tickets, float* b_and_lo, int64_t M, int64_t N, int64_t K, cudaStream_t s) {
+                      int* tickets, float* b_and_lo, int64_t M, int64_t N, int64_t K, int64_t ldb, int64_t ldc,
+                      cudaStream_t s) {
   constexpr int NT = Shape::kRows;
   int ctas;
   const SkinnySched sc = make_skinny_sched(M, K, c->sm_count, KU_CTAS_PER_SM, Shape::kPieceOverhead, &ctas);
@@ -580,7 +584,7 @@ int launch_tall_shape(DeviceCtx* c, uint32_t attr_bit, const float* A, const flo
     return fail(VT_ERR_UNSUPPORTED, "M = %lld has more slabs than the library keeps tickets for", (long long)M);
   const int64_t total = K * 2 * NT;
   const int blocks = int(total / 256 + 1 < int64_t(c->sm_count) * 8 ? total / 256 + 1 : int64_t(c->sm_count) * 8);
-  tall_b_and_lo_kernel<<<blocks, 256, 0, s>>>(B, b_and_lo, K, int(N), NT);
+  tall_b_and_lo_kernel<<<blocks, 256, 0, s>>>(B, b_and_lo, K, int(N), NT, ldb);
   count_launch();
   CUtensorMap tmBig, tmSmall;
   int rc = encode_tmap_2d(&tmBig, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, A, uint64_t(K), uint64_t(M), uint64_t(K) * 4, 32, 128);
@@ -594,7 +598,7 @@ int launch_tall_shape(DeviceCtx* c, uint32_t attr_bit, const float* A, const flo
     c->func_attr_mask |= attr_bit;
   }
   sgemm_skinny_umma_kernel<Shape><<<ctas, Shape::kThreads, Shape::kSmemBytes, s>>>(tmBig, tmSmall, C, partials, tickets,
-                                                                                     int(M), int(N), sc, c->status);
+                                                                                     int(M), int(N), int(ldc), sc, c->status);
   count_launch();
   VT_CUDA(cudaGetLastError());
   return VT_OK;
@@ -613,12 +617,14 @@ void sgemm_skinny_umma_plan(int64_t M, int64_t N, int64_t K, int sm_count, int* 
   *max_parts = skinny_max_parts(sc);
 }
 
-// Tall form: C (M x N) = A (M x K) * B (K x N) with N <= 64 and A streamed once.
-int sgemm_tall_umma_panel(int64_t N) { return N <= 16 ? 16 : N <= 32 ? 32 : 64; }
+// Tall form: a panel of up to 128 columns of C (M x N, row pitch ldc) = A (M x K) * the same columns of B (row pitch
+// ldb), A streamed once per panel.
+int sgemm_tall_umma_panel(int64_t N) { return N <= 16 ? 16 : N <= 32 ? 32 : N <= 64 ? 64 : 128; }
 
 void sgemm_tall_umma_plan(int64_t M, int64_t N, int64_t K, int sm_count, int* max_parts, size_t* b_and_lo_bytes) {
   int ctas;
-  const int overhead = N <= 16 ? KuTall16::kPieceOverhead : N <= 32 ? KuTall32::kPieceOverhead : KuTall64::kPieceOverhead;
+  const int overhead = N <= 16 ? KuTall16::kPieceOverhead : N <= 32 ? KuTall32::kPieceOverhead
+                       : N <= 64 ? KuTall64::kPieceOverhead : KuTall128::kPieceOverhead;
   const SkinnySched sc = make_skinny_sched(M, K, sm_count, KU_CTAS_PER_SM, overhead, &ctas);
   *max_parts = skinny_max_parts(sc);
   *b_and_lo_bytes = size_t(K) * 2 * size_t(sgemm_tall_umma_panel(N)) * 4;
@@ -626,21 +632,22 @@ void sgemm_tall_umma_plan(int64_t M, int64_t N, int64_t K, int sm_count, int* ma
 
 bool sgemm_tall_umma_supported(const float* A, const float* B, const float* C, int64_t M, int64_t N, int64_t K) {
   (void)B;
-  return N >= 4 && N <= 64 && N % 4 == 0 && M >= 1 && K % 4 == 0 && K >= 4 && M < (1LL << 31) && K < (1LL << 31) &&
+  return N >= 4 && N % 4 == 0 && M >= 1 && K % 4 == 0 && K >= 4 && M < (1LL << 31) && K < (1LL << 31) && N < (1LL << 31) &&
          ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(C)) & 15) == 0;
 }
 
 int launch_sgemm_tall_umma(DeviceCtx* c, const float* A, const float* B, float* C, float* partials, int* tickets,
-                           float* b_and_lo, int64_t M, int64_t N, int64_t K, cudaStream_t s) {
-  if (!sgemm_tall_umma_supported(A, B, C, M, N, K))
+                           float* b_and_lo, int64_t M, int64_t N, int64_t K, int64_t ldb, int64_t ldc, cudaStream_t s) {
+  if (!sgemm_tall_umma_supported(A, B, C, M, N, K) || N > SKINNY_UMMA_MAX_ROWS || ldc % 4 != 0)
     return fail(VT_ERR_UNSUPPORTED,
-                "tall tensor-core kernel needs N <= 64, N %% 4 == 0, K %% 4 == 0 and 16-byte aligned A and C");
+                "tall tensor-core kernel needs panels of N <= 128, N %% 4 == 0, K %% 4 == 0 and 16-byte aligned A and C");
   if (!b_and_lo) return fail(VT_ERR_INVALID, "tall kernel needs scratch memory for [B | B lo]");
-  if (N <= 16) return launch_tall_shape<KuTall16>(c, 1u << 26, A, B, C, partials, tickets, b_and_lo, M, N, K, s);
-  if (N <= 32) return launch_tall_shape<KuTall32>(c, 1u << 27, A, B, C, partials, tickets, b_and_lo, M, N, K, s);
+  if (N <= 16) return launch_tall_shape<KuTall16>(c, 1u << 26, A, B, C, partials, tickets, b_and_lo, M, N, K, ldb, ldc, s);
+  if (N <= 32) return launch_tall_shape<KuTall32>(c, 1u << 27, A, B, C, partials, tickets, b_and_lo, M, N, K, ldb, ldc, s);
+  if (N > 64) return launch_tall_shape<KuTall128>(c, 1u << 30, A, B, C, partials, tickets, b_and_lo, M, N, K, ldb, ldc, s);
   if (double(M) * double(K) >= 3.2e7)
-    return launch_tall_shape<KuTall64Large>(c, 1u << 29, A, B, C, partials, tickets, b_and_lo, M, N, K, s);
-  return launch_tall_shape<KuTall64>(c, 1u << 28, A, B, C, partials, tickets, b_and_lo, M, N, K, s);
+    return launch_tall_shape<KuTall64Large>(c, 1u << 29, A, B, C, partials, tickets, b_and_lo, M, N, K, ldb, ldc, s);
+  return launch_tall_shape<KuTall64>(c, 1u << 28, A, B, C, partials, tickets, b_and_lo, M, N, K, ldb, ldc, s);
 }
 
 bool sgemm_skinny_umma_supported(const float* A, const float* B, const float* C, int64_t M, int64_t N, int64_t K) {

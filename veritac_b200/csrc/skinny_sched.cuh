@@ -186,13 +186,13 @@ __device__ __forceinline__ void skinny_finish_piece(const SkinnySegment& seg, in
   asm volatile("bar.sync %0, %1;" ::"r"(bar_id), "n"(kThreads) : "memory");   // last_flag is rewritten by the next piece
 }
 
-// The same for a slab whose tile is one contiguous block of C (the tall form: 128 whole rows of C):
-// `block_elems` floats (a multiple of 4) starting `block_off` floats into C and into every piece's copy.
+// The same for a slab whose tile is whole rows of C (the tall form): `rows` rows from row `row0`, `width` columns
+// (a multiple of 4); the pieces' copies have row pitch `width`, C has row pitch `c_pitch`.
 template <int kThreads>
 __device__ __forceinline__ void skinny_finish_block(const SkinnySegment& seg, int tid, int bar_id, int* last_flag,
                                                     int* __restrict__ tickets, const float* __restrict__ partials,
-                                                    float* __restrict__ C, size_t piece, size_t block_off,
-                                                    int block_elems) {
+                                                    float* __restrict__ C, size_t piece, int row0, int rows, int width,
+                                                    int c_pitch) {
   __threadfence();
   asm volatile("bar.sync %0, %1;" ::"r"(bar_id), "n"(kThreads) : "memory");
   if (tid == 0) {
@@ -203,8 +203,10 @@ __device__ __forceinline__ void skinny_finish_block(const SkinnySegment& seg, in
   if (*last_flag) {
     __threadfence();
     constexpr int kBatch = 4;   // pieces loaded together
-    for (int v = tid; v < block_elems / 4; v += kThreads) {
-      const size_t off = block_off + size_t(v) * 4;
+    const int per_row = width / 4;
+    for (int v = tid; v < rows * per_row; v += kThreads) {
+      const int r = v / per_row, q4 = v - r * per_row;
+      const size_t off = size_t(row0 + r) * width + size_t(q4) * 4;
       float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
       for (int p0 = 0; p0 < seg.parts; p0 += kBatch) {
         float4 x[kBatch];
@@ -220,7 +222,7 @@ __device__ __forceinline__ void skinny_finish_block(const SkinnySegment& seg, in
           sum.w += x[q].w;
         }
       }
-      *reinterpret_cast<float4*>(C + off) = sum;
+      *reinterpret_cast<float4*>(C + size_t(row0 + r) * c_pitch + size_t(q4) * 4) = sum;
     }
     if (tid == 0) tickets[seg.slab] = 0;
   }

@@ -43,7 +43,7 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustain
 
 # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the ncu captures
 # summarised under profiles/; None until a capture exists for the workload.
-NCU_TRAFFIC_BYTES = {"sgemm_skinny": 273.9e6, "sgemm_panel_128": 282.9e6, "i8_8192": 608.8e6, "i8_batched_32": 654.4e6, "i8_batched": 8 * 654.4e6}
+NCU_TRAFFIC_BYTES = {"sgemm_skinny": 273.9e6, "sgemm_panel_128": 282.9e6, "sgemm_tall_16": 275.8e6, "i8_8192": 608.8e6, "i8_batched_32": 654.4e6, "i8_batched": 8 * 654.4e6}
 
 WORKLOADS = {
     # name: (kind, M, N, K, batch)
@@ -56,6 +56,7 @@ WORKLOADS = {
     "sgemm_skinny": ("f32", 16, 8192, 8192, 1),
     "sgemm_panel_64": ("f32", 64, 8192, 8192, 1),         # few rows against a large B: the row-panel kernel
     "sgemm_panel_128": ("f32", 128, 8192, 8192, 1),
+    "sgemm_tall_16": ("f32", 8192, 16, 8192, 1),          # few columns against a large A: the tall form
 }
 
 
@@ -525,7 +526,7 @@ def run_gpu_arm(args, kind, M, N, K, batch, metric, unit):
     ops_per_launch = 2.0 * rows * N * K
     algo_bytes = (K * N + rows * K + rows * N) * 4.0
     tf32x3_peak = peaks["bf16_tflops"] / 2.0 / 3.0       # three TF32 MMAs per fp32 product; TF32 at half the bf16 rate
-    panel = args.workload in ("sgemm_skinny", "sgemm_panel_64", "sgemm_panel_128")
+    panel = args.workload in ("sgemm_skinny", "sgemm_panel_64", "sgemm_panel_128", "sgemm_tall_16")
     if panel and algo_bytes / (peaks["hbm_gbs"] * 1e9) >= ops_per_launch / (tf32x3_peak * 1e12):
         achieved = algo_bytes / (launch_ms * 1e-3) / 1e9
         roof = {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",

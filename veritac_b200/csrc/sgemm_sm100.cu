@@ -7,6 +7,11 @@
 //       (64*RM)x(64*RN).  K is consumed 16 at a time through two shared-memory buffers: global loads
 //       for step t+1 are issued into registers before the FFMAs of step t and stored (A transposed
 //       so the inner loop reads float4s along M) after them, one __syncthreads per step.
+//       The 128x128 form is limited by instruction issue, so it uses the packed fma.rn.f32x2 (two
+//       rows of one column per instruction: the row pair comes straight from the float4 of A, the
+//       column value is copied into both halves of a register pair), brings B in by cp.async (no
+//       staging registers, which is what lets the packed form fit 128 registers without spills) and
+//       lays a warp out as 4 x 8 threads.
 //   sgemm_small_kernel        products too small to fill the GPU with 64x64 tiles: 32x32 CTA tile, K in
 //       bursts of 256 split four ways inside the CTA (described at the kernel).
 //   sgemm_skinny_kernel       M <= 16 ("decode-like") in true fp32: B is streamed exactly once.  A CTA owns
@@ -58,7 +63,12 @@ sgemm_tile_kernel(const float* __restrict__ A, const float* __restrict__ B, floa
   }
   const int m0 = tm * BM, n0 = tn * BN;
   const int tid = threadIdx.x;
-  const int tx = tid & 15, ty = tid >> 4;
+  // Packed form: a warp is 4 (M) x 8 (N) threads and the 8 warps are 4 (M) x 2 (N), so that per K step a warp
+  // reads 4 distinct float4s of A and 8 of B instead of 2 and 16.
+  constexpr bool kPacked = RM * RN >= 4;
+  const int tx = kPacked ? ((tid >> 5) & 1) * 8 + (tid & 7) : tid & 15;
+  const int ty = kPacked ? (tid >> 6) * 4 + ((tid >> 3) & 3) : tid >> 4;
+  constexpr bool kAsyncB = kPacked && !kGuard;
 
   const int a_row = tid >> 2;        // 0..63 (+64 per pass)
   const int a_k = (tid & 3) * 4;     // 0,4,8,12
@@ -73,7 +83,7 @@ sgemm_tile_kernel(const float* __restrict__ A, const float* __restrict__ B, floa
   const float* b_ptr = B + size_t(b_k) * N + n0 + b_n;
   const size_t a_pass = size_t(64) * K, b_pass = size_t(B_ROWS_PER_PASS) * N;
 
-  auto load_tile = [&](int k0) {
+  auto load_tile = [&](int k0, int nbuf) {
 #pragma unroll
     for (int i = 0; i < RM; ++i) {
       const int row = m0 + a_row + 64 * i;
@@ -91,7 +101,9 @@ sgemm_tile_kernel(const float* __restrict__ A, const float* __restrict__ B, floa
     for (int i = 0; i < RN; ++i) {
       const int k = k0 + b_k + B_ROWS_PER_PASS * i;
       const int col = n0 + b_n;
-      if constexpr (!kGuard) {
+      if constexpr (kAsyncB) {
+        cp_async_16_zfill(&Bs[nbuf][b_k + B_ROWS_PER_PASS * i][b_n], b_ptr + i * b_pass, true);
+      } else if constexpr (!kGuard) {
         pb[i] = __ldg(reinterpret_cast<const float4*>(b_ptr + i * b_pass));
       } else {
         float v[4];
@@ -114,26 +126,32 @@ sgemm_tile_kernel(const float* __restrict__ A, const float* __restrict__ B, floa
       As[buf][a_k + 2][r] = pa[i].z;
       As[buf][a_k + 3][r] = pa[i].w;
     }
+    if constexpr (kAsyncB) {
+      cp_async_commit();
+      cp_async_wait<0>();             // this thread's part of B has landed; the barrier publishes it
+    } else {
 #pragma unroll
-    for (int i = 0; i < RN; ++i)
-      *reinterpret_cast<float4*>(&Bs[buf][b_k + B_ROWS_PER_PASS * i][b_n]) = pb[i];
+      for (int i = 0; i < RN; ++i)
+        *reinterpret_cast<float4*>(&Bs[buf][b_k + B_ROWS_PER_PASS * i][b_n]) = pb[i];
+    }
   };
 
-  float acc[4 * RM][4 * RN];
+  // acc[p][j] = rows (2p, 2p+1) of column j of this thread's (4*RM) x (4*RN) outputs.
+  float2 acc[2 * RM][4 * RN];
 #pragma unroll
-  for (int i = 0; i < 4 * RM; ++i)
+  for (int p = 0; p < 2 * RM; ++p)
 #pragma unroll
-    for (int j = 0; j < 4 * RN; ++j) acc[i][j] = 0.f;
+    for (int j = 0; j < 4 * RN; ++j) acc[p][j] = make_float2(0.f, 0.f);
 
   const int ktiles = (K + SG_BK - 1) / SG_BK;
-  load_tile(0);
+  load_tile(0, 0);
   store_tile(0);
   __syncthreads();
 
   for (int kt = 0; kt < ktiles; ++kt) {
     const int buf = kt & 1;
-    if (kt + 1 < ktiles) load_tile((kt + 1) * SG_BK);
-#pragma unroll
+    if (kt + 1 < ktiles) load_tile((kt + 1) * SG_BK, buf ^ 1);
+#pragma unroll(kPacked ? 8 : SG_BK)
     for (int k = 0; k < SG_BK; ++k) {
       float a[4 * RM], b[4 * RN];
 #pragma unroll
@@ -146,15 +164,28 @@ sgemm_tile_kernel(const float* __restrict__ A, const float* __restrict__ B, floa
         const float4 v = *reinterpret_cast<const float4*>(&Bs[buf][k][64 * j + tx * 4]);
         b[4 * j + 0] = v.x; b[4 * j + 1] = v.y; b[4 * j + 2] = v.z; b[4 * j + 3] = v.w;
       }
+      if constexpr (kPacked) {
 #pragma unroll
-      for (int i = 0; i < 4 * RM; ++i)
+        for (int j = 0; j < 4 * RN; ++j) {
+          const float2 bb = make_float2(b[j], b[j]);
 #pragma unroll
-        for (int j = 0; j < 4 * RN; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+          for (int p = 0; p < 2 * RM; ++p) acc[p][j] = __ffma2_rn(make_float2(a[2 * p], a[2 * p + 1]), bb, acc[p][j]);
+        }
+      } else {
+#pragma unroll
+        for (int p = 0; p < 2 * RM; ++p)
+#pragma unroll
+          for (int j = 0; j < 4 * RN; ++j) {
+            acc[p][j].x = fmaf(a[2 * p], b[j], acc[p][j].x);
+            acc[p][j].y = fmaf(a[2 * p + 1], b[j], acc[p][j].y);
+          }
+      }
     }
     if (kt + 1 < ktiles) store_tile(buf ^ 1);
     __syncthreads();
   }
 
+  auto cell = [&](int i, int j) { return (i & 1) ? acc[i >> 1][j].y : acc[i >> 1][j].x; };
 #pragma unroll
   for (int i = 0; i < 4 * RM; ++i) {
     const int row = m0 + 64 * (i >> 2) + ty * 4 + (i & 3);
@@ -163,12 +194,12 @@ sgemm_tile_kernel(const float* __restrict__ A, const float* __restrict__ B, floa
       const int col = n0 + 64 * j + tx * 4;
       if constexpr (!kGuard) {
         *reinterpret_cast<float4*>(C + size_t(row) * N + col) =
-            make_float4(acc[i][4 * j], acc[i][4 * j + 1], acc[i][4 * j + 2], acc[i][4 * j + 3]);
+            make_float4(cell(i, 4 * j), cell(i, 4 * j + 1), cell(i, 4 * j + 2), cell(i, 4 * j + 3));
       } else {
         if (row < M) {
 #pragma unroll
           for (int e = 0; e < 4; ++e)
-            if (col + e < N) C[size_t(row) * N + col + e] = acc[i][4 * j + e];
+            if (col + e < N) C[size_t(row) * N + col + e] = cell(i, 4 * j + e);
         }
       }
     }
@@ -546,7 +577,7 @@ int launch_sgemm_skinny(DeviceCtx* c, const float* A, const float* B, float* C, 
 double sgemm_tile_choice(const float* A, const float* B, const float* C, int64_t M, int64_t N, int64_t K, int sm_count,
                          int* variant) {
   const bool small_ok = sgemm_small_ok(A, B, C, N, K);
-  static const double kRate[3] = {53e12, 32e12, 32e12};
+  static const double kRate[3] = {58e12, 32e12, 32e12};
   static const double kBias[3] = {1.0, 1.0, 1.1};
   static const int kTile[3] = {128, 64, 32};
   static const int kVariant[3] = {VT_SGEMM_TILE128, VT_SGEMM_TILE64, VT_SGEMM_TILE32};

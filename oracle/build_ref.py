@@ -1,7 +1,7 @@
 """TEST INFRASTRUCTURE — builds artefacts of the *reference itself* into oracle/_ref/ (git-ignored).
 
 The reference's cpu_gemm path is a Python emitter whose product is generated OpenMP C.  Where the
-reference tree is present (REFERENCE_ROOT, default /root/reference) this script imports its
+reference tree is present (the directory REFERENCE_ROOT names) this script imports its
 unmodified emitter (CodeGen/emit_c.py, CodeGen/lower.py), has it print `matmul()` for the 256^3 nest —
 untuned, and after the schedule its README quotes (tactics applied by oracle/loopnest_oracle.py,
 because the Lean CLI that applies them cannot be built here) — and compiles each text to a shared

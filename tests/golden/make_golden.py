@@ -1,7 +1,7 @@
 """Regenerates tests/golden/gemmini.json, cpu_gemm.json, learned_streams.json and schedule_ir.json from the
 reference tree.
 
-Needs the reference checkout (default /root/reference, or REFERENCE_ROOT) — it is imported and its
+Needs the reference checkout (the directory REFERENCE_ROOT names) — it is imported and its
 recorded evidence files are read — so it runs only where that tree exists; the fixtures it writes are
 committed and are what the tests read.  The reference's Lean plan checker cannot be built here; its
 documented override VERITAC_GEMMINI_CHECK_BIN (reference specializations/gemmini_gemm/backend.py:

@@ -87,6 +87,8 @@ i8gemm_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = ps->tmem_base;
+  grid_dependency_wait();                            // see the CTA-pair kernel
+  grid_launch_dependents();
 
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
@@ -292,6 +294,10 @@ i8gemm_umma_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
   cluster_sync_all();                                // peer barriers exist before anything signals them
   tc_fence_after_sync();
   const uint32_t tmem_base = ps->tmem_base;
+  // The set-up above may overlap the end of the kernel before this one on the stream; operands, C and the
+  // status word are not touched before that kernel has completed.
+  grid_dependency_wait();
+  grid_launch_dependents();
 
   if (warp == 0) {
     // ------------------------------ TMA producer (both CTAs) ------------------------------
@@ -435,7 +441,8 @@ int launch_with_smem(DeviceCtx* c, uint32_t attr_bit, KernelT kernel, size_t sme
     VT_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
     c->func_attr_mask |= attr_bit;
   }
-  kernel<<<grid, NUM_THREADS, smem, s>>>(tmA, tmB, tmC, C, M, N, K, rs, c->status);
+  VT_CUDA(launch_overlapped(kernel, unsigned(grid), unsigned(NUM_THREADS), smem, s, tmA, tmB, tmC, C, M, N, K, rs,
+                            c->status));
   count_launch();
   VT_CUDA(cudaGetLastError());
   return VT_OK;

@@ -36,6 +36,16 @@ __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t arrivals) {
 __device__ __forceinline__ void fence_mbar_init() {
   asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
 }
+// Programmatic dependent launch.  A kernel launched with launch_overlapped() (runtime.h) may start while the
+// kernel before it on the stream is still running: its CTAs take SMs as that kernel's CTAs leave them and run
+// their set-up (barriers, tensor memory, descriptor prefetch) there.  grid_dependency_wait() returns once the
+// earlier kernel has completed and its writes are visible, so it must come before the first access to global
+// memory; grid_launch_dependents() then lets the kernel after this one do the same.  Calling it only after the
+// wait keeps the overlap to one kernel ahead.  Both are no-ops in a kernel launched the ordinary way.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
 __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }

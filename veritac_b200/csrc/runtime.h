@@ -60,6 +60,25 @@ int encode_tmap_2d(CUtensorMap* out, CUtensorMapDataType dtype, int elem_bytes, 
     if (_e != cudaSuccess) return vt::fail_cuda(_e, #expr); \
   } while (0)
 
+// Launches `kernel` so that its set-up may overlap the tail of the kernel before it on the stream
+// (programmatic stream serialization).  The kernel must call grid_dependency_wait() (ptx_sm100.cuh) before
+// it touches global memory.
+template <class... KArgs, class... Args>
+cudaError_t launch_overlapped(void (*kernel)(KArgs...), unsigned grid, unsigned block, size_t smem, cudaStream_t s,
+                              Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(block);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 // ---- kernel launchers (device pointers only) ------------------------------------------------
 // raster_mode: 0 row-major tiles, 1 column-major tiles, 2 grouped (group = tile-rows per sweep).
 // variant: VT_I8_B_AS_STORED (B consumed as K x N row-major, an MN-major operand),

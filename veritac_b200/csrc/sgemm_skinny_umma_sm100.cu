@@ -174,16 +174,22 @@ sgemm_skinny_umma_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_c
     tmem_alloc<1>(&ps->tmem_base, KU_TMEM_COLS);
     tmem_relinquish<1>();
   }
+  if (warp == 0 && lane == 0) {
+    tma_prefetch_desc(&tmB);
+    tma_prefetch_desc(&tmA);
+  }
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = ps->tmem_base;
+  // Everything above may run while the kernel before this one on the stream is still finishing; nothing below
+  // (operands, partial tiles, tickets, C, the status word) is touched before it has completed.
+  grid_dependency_wait();
+  grid_launch_dependents();
 
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
     if (lane == 0) {
-      tma_prefetch_desc(&tmB);
-      tma_prefetch_desc(&tmA);
       uint32_t filled = 0, fill_parity = 0;
       uint32_t stage = 0, phase = 0;
       bool ok = true;
@@ -539,8 +545,9 @@ int launch_shape(DeviceCtx* c, uint32_t attr_bit, const float* A, const float* B
                                  int(Shape::kSmemBytes)));
     c->func_attr_mask |= attr_bit;
   }
-  sgemm_skinny_umma_kernel<Shape><<<ctas, Shape::kThreads, Shape::kSmemBytes, s>>>(tmB, tmA, C, partials, tickets, int(M),
-                                                                                     int(N), int(N), sc, c->status);
+  VT_CUDA(launch_overlapped(sgemm_skinny_umma_kernel<Shape>, unsigned(ctas), unsigned(Shape::kThreads),
+                            size_t(Shape::kSmemBytes), s, tmB, tmA, C, partials, tickets, int(M), int(N), int(N), sc,
+                            c->status));
   count_launch();
   VT_CUDA(cudaGetLastError());
   return VT_OK;
@@ -597,8 +604,9 @@ int launch_tall_shape(DeviceCtx* c, uint32_t attr_bit, const float* A, const flo
                                  int(Shape::kSmemBytes)));
     c->func_attr_mask |= attr_bit;
   }
-  sgemm_skinny_umma_kernel<Shape><<<ctas, Shape::kThreads, Shape::kSmemBytes, s>>>(tmBig, tmSmall, C, partials, tickets,
-                                                                                     int(M), int(N), int(ldc), sc, c->status);
+  VT_CUDA(launch_overlapped(sgemm_skinny_umma_kernel<Shape>, unsigned(ctas), unsigned(Shape::kThreads),
+                            size_t(Shape::kSmemBytes), s, tmBig, tmSmall, C, partials, tickets, int(M), int(N), int(ldc),
+                            sc, c->status));
   count_launch();
   VT_CUDA(cudaGetLastError());
   return VT_OK;

@@ -21,6 +21,7 @@
 //       (deterministic, no atomics).
 #include <mutex>
 
+#include "ptx_sm100.cuh"
 #include "runtime.h"
 
 namespace vt {
@@ -391,6 +392,12 @@ sgemm_small_kernel(const float* __restrict__ A, const float* __restrict__ B, flo
 #pragma unroll
     for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
 
+  // This kernel is a few microseconds long, about as long as the gap between two launches: it is launched so
+  // that its CTAs may be placed while the kernel before it on the stream is still running, and waits here,
+  // before its first access to global memory, for that kernel to complete.
+  grid_dependency_wait();
+  grid_launch_dependents();
+
   for (int k0 = 0; k0 < K; k0 += SS_KC) {
     if (k0 > 0) __syncthreads();                  // everyone is done with the previous burst
     // A: 32 rows x 64 float4; B: 256 rows x 8 float4.  2048 copies each, 8 + 8 per thread.
@@ -487,7 +494,8 @@ int launch_small(const float* A, const float* B, float* C, int M, int N, int K, 
   const long long tiles = 1LL * tiles_m * tiles_n;
   if (tiles > 0x7fffffffLL) return fail(VT_ERR_INVALID, "sgemm tile count overflows int");
   VT_CUDA(cudaFuncSetAttribute(sgemm_small_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(SS_SMEM_BYTES)));
-  sgemm_small_kernel<<<unsigned(tiles), SS_THREADS, SS_SMEM_BYTES, s>>>(A, B, C, M, N, K, tiles_n);
+  VT_CUDA(launch_overlapped(sgemm_small_kernel, unsigned(tiles), unsigned(SS_THREADS), size_t(SS_SMEM_BYTES), s, A, B, C,
+                            M, N, K, tiles_n));
   count_launch();
   VT_CUDA(cudaGetLastError());
   return VT_OK;

@@ -292,3 +292,32 @@ def test_measure_controls_matches_reference_scoring(native, g, lowering):
     assert [c["name"] for c in result["controls"]] == ["baseline", "existing_batched_b_1", "existing_batched_b_2"]
     with pytest.raises(ValueError, match="candidate failed"):
         measure_controls(g.make_plan(16, 16, 16, "baseline"), [g.Fence()], a[:256], b[:256])
+
+
+def test_stream_order_holds_across_overlapped_launches(native):
+    """The int8 kernels may be placed on the GPU while the kernel before them on the stream is still running
+    and must not touch memory until it has completed.  A large fill of C runs right before each product with
+    no synchronisation in between: if the product's stores did not wait, the fill would overwrite them."""
+    import torch
+    rng = np.random.default_rng(31)
+    m, n, k = 4096, 4096, 64          # a short product behind a 64 MiB fill
+    a = rng.integers(-128, 128, (m, k), dtype=np.int8)
+    b = rng.integers(-128, 128, (k, n), dtype=np.int8)
+    want = go.matmul_exact(a.reshape(-1), b.reshape(-1), m, n, k).reshape(m, n).astype(np.int32)
+    dA, dB = torch.from_numpy(a).cuda(), torch.from_numpy(b).cuda()
+    dC = torch.empty((m, n), dtype=torch.int32, device="cuda")
+    st = native.torch_stream()
+    for variant in (0, 1):
+        for rep in range(8):
+            dC.fill_(-7 - rep)
+            native.i8gemm(dA, dB, dC, m, n, k, variant=variant, where=native.VT_DEVICE, stream=st)
+        native.sync(0, st)
+        assert np.array_equal(dC.cpu().numpy(), want), variant
+        # and a product whose input is the previous kernel's output: B2 is written by a copy kernel right before
+        dB2 = torch.empty_like(dB)
+        for rep in range(4):
+            dB2.fill_(0)
+            dB2.copy_(dB)
+            native.i8gemm(dA, dB2, dC, m, n, k, variant=variant, where=native.VT_DEVICE, stream=st)
+        native.sync(0, st)
+        assert np.array_equal(dC.cpu().numpy(), want), variant

@@ -255,3 +255,28 @@ def test_demos_run_end_to_end(native, capsys):
     for cand in report["candidates"]:
         assert cand["numeric_passed"] and len(cand["validation"]) == 6
     assert report["illustrative_repair"]["accepted"] is False and report["illustrative_repair"]["repair_accepted"]
+
+
+def test_stream_order_holds_across_overlapped_launches(native):
+    """Back-to-back calls where each product reads what the one before it wrote (X <- X . B through two
+    buffers, skinny and small kernels) must give the bits of the same chain run with a synchronisation after
+    every call: these kernels start their set-up before the previous kernel on the stream has finished and may
+    touch memory only after it has."""
+    import torch
+    st = native.torch_stream()
+    gen = torch.Generator(device="cuda").manual_seed(77)
+    for (m, n) in ((16, 2048), (8, 4096), (96, 2048), (256, 256)):
+        B = (torch.rand((n, n), device="cuda", generator=gen) * 2 - 1) / (n ** 0.5) * 1.7
+        X0 = torch.rand((m, n), device="cuda", generator=gen) * 2 - 1
+        results = []
+        for synced in (True, False):
+            bufs = [X0.clone(), torch.zeros_like(X0)]
+            for step in range(12):
+                src, dst = bufs[step & 1], bufs[1 - (step & 1)]
+                native.sgemm(src, B, dst, m, n, n, where=native.VT_DEVICE, stream=st)
+                if synced:
+                    native.sync(0, st)
+            native.sync(0, st)
+            results.append(bufs[0].clone())
+        assert torch.isfinite(results[0]).all() and float(results[0].abs().max()) > 0
+        assert torch.equal(results[0], results[1]), (m, n)

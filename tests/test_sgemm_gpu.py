@@ -259,13 +259,13 @@ def test_demos_run_end_to_end(native, capsys):
 
 def test_stream_order_holds_across_overlapped_launches(native):
     """Back-to-back calls where each product reads what the one before it wrote (X <- X . B through two
-    buffers, skinny and small kernels) must give the bits of the same chain run with a synchronisation after
+    buffers; skinny, panel, small and 3xTF32 kernels) must give the bits of the same chain run with a synchronisation after
     every call: these kernels start their set-up before the previous kernel on the stream has finished and may
     touch memory only after it has."""
     import torch
     st = native.torch_stream()
     gen = torch.Generator(device="cuda").manual_seed(77)
-    for (m, n) in ((16, 2048), (8, 4096), (96, 2048), (256, 256)):
+    for (m, n) in ((16, 2048), (8, 4096), (96, 2048), (256, 256), (1024, 1024)):
         B = (torch.rand((n, n), device="cuda", generator=gen) * 2 - 1) / (n ** 0.5) * 1.7
         X0 = torch.rand((m, n), device="cuda", generator=gen) * 2 - 1
         results = []

@@ -54,6 +54,10 @@ __device__ __forceinline__ float tf32_lo_part(float x) {
 }
 __global__ void __launch_bounds__(256) lo_parts_kernel(const float4* __restrict__ a, float4* __restrict__ a_lo, int64_t na4,
                                                       const float4* __restrict__ b, float4* __restrict__ b_lo, int64_t nb4) {
+  // Launched for overlap with the kernel before it (see launch_overlapped): the lo parts overwrite scratch that
+  // a product still running may be reading, so nothing is touched before that kernel has completed.
+  grid_dependency_wait();
+  grid_launch_dependents();
   const int64_t stride = int64_t(gridDim.x) * blockDim.x;
   for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < na4 + nb4; i += stride) {
     const bool in_a = i < na4;
@@ -109,6 +113,10 @@ sgemm_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_
   cluster_sync_all();
   tc_fence_after_sync();
   const uint32_t tmem_base = ps->tmem_base;
+  // The set-up above may overlap the end of the lo-part pass (or of whatever kernel precedes this one on the
+  // stream); operands, lo parts, C and the status word are not touched before it has completed.
+  grid_dependency_wait();
+  grid_launch_dependents();
 
   // Register budget by warpgroup: the epilogue keeps 128 fp32 partial sums per thread, the
   // producer and MMA threads need almost nothing.  (40 + 232 + 232) * 128 <= 65536.
@@ -318,9 +326,10 @@ int launch_sgemm_tf32x3(DeviceCtx* c, const float* A, const float* B, float* C, 
   float* Al = Bl + nb;
   if (parts & 3) {
     const int blocks = c->sm_count * 8;
-    lo_parts_kernel<<<blocks, 256, 0, s>>>(reinterpret_cast<const float4*>(A), reinterpret_cast<float4*>(Al),
-                                           (parts & 1) ? int64_t(na / 4) : 0, reinterpret_cast<const float4*>(B),
-                                           reinterpret_cast<float4*>(Bl), (parts & 2) ? int64_t(nb / 4) : 0);
+    VT_CUDA(launch_overlapped(lo_parts_kernel, unsigned(blocks), 256u, size_t(0), s, reinterpret_cast<const float4*>(A),
+                              reinterpret_cast<float4*>(Al), (parts & 1) ? int64_t(na / 4) : int64_t(0),
+                              reinterpret_cast<const float4*>(B), reinterpret_cast<float4*>(Bl),
+                              (parts & 2) ? int64_t(nb / 4) : int64_t(0)));
     count_launch();
   }
   if (M == 0) return VT_OK;   // B lo only
@@ -348,8 +357,8 @@ int launch_sgemm_tf32x3(DeviceCtx* c, const float* A, const float* B, float* C, 
   }
   const int max_pairs = c->sm_count / 2;
   const int pairs = int(tiles < max_pairs ? tiles : max_pairs);
-  sgemm_tf32x3_pair_kernel<<<2 * pairs, T_THREADS, T_SMEM_BYTES, s>>>(tmAh, tmAl, tmBh, tmBl, tmC, int(M), int(N),
-                                                                        int(K), rs, c->status);
+  VT_CUDA(launch_overlapped(sgemm_tf32x3_pair_kernel, unsigned(2 * pairs), unsigned(T_THREADS), size_t(T_SMEM_BYTES), s,
+                            tmAh, tmAl, tmBh, tmBl, tmC, int(M), int(N), int(K), rs, c->status));
   count_launch();
   VT_CUDA(cudaGetLastError());
   return VT_OK;

@@ -280,3 +280,26 @@ def test_stream_order_holds_across_overlapped_launches(native):
             results.append(bufs[0].clone())
         assert torch.isfinite(results[0]).all() and float(results[0].abs().max()) > 0
         assert torch.equal(results[0], results[1]), (m, n)
+
+
+@pytest.mark.parametrize("variant,shape", [(1, (512, 384, 640)), (2, (320, 448, 200)), (9, (16384, 32, 512)),
+                                           (8, (96, 1024, 1024)), (4, (512, 512, 512))])
+def test_inputs_written_by_the_kernel_before(native, variant, shape):
+    """B is rewritten and C poisoned by ordinary kernels right before each product, with no synchronisation:
+    a product that started reading or writing before those kernels had finished would see the other B or lose
+    its output to the poison."""
+    import torch
+    m, n, k = shape
+    st = native.torch_stream()
+    gen = torch.Generator(device="cuda").manual_seed(78)
+    A = torch.rand((m, k), device="cuda", generator=gen) * 2 - 1
+    Bs = [torch.rand((k, n), device="cuda", generator=gen) * 2 - 1 for _ in range(2)]
+    Bw = torch.empty_like(Bs[0])
+    C = torch.empty((m, n), device="cuda")
+    for rep in range(7):
+        Bw.copy_(Bs[rep & 1])
+        C.fill_(float("nan"))
+        native.sgemm(A, Bw, C, m, n, k, variant=variant, where=native.VT_DEVICE, stream=st)
+    native.sync(0, st)
+    ref = (A.double() @ Bs[0].double()).cpu().numpy()
+    assert relfro(C.cpu().numpy(), ref) <= TOL

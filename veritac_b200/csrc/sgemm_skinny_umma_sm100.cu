@@ -564,6 +564,10 @@ using KuTall128 = KuShape<128, 1, 2, true, 1, 4, true>;
 // (B has row pitch `ldb`; the N columns are a panel of it.)
 __global__ void __launch_bounds__(256) tall_b_and_lo_kernel(const float* __restrict__ B, float* __restrict__ out, int64_t K,
                                                             int N, int nt, int64_t ldb) {
+  // Launched for overlap with the kernel before it: `out` is scratch that the streaming kernel of the previous
+  // panel or call may still be reading, so nothing is touched before that kernel has completed.
+  grid_dependency_wait();
+  grid_launch_dependents();
   const int64_t total = K * 2 * nt;
   const int64_t stride = int64_t(gridDim.x) * blockDim.x;
   for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
@@ -591,7 +595,8 @@ int launch_tall_shape(DeviceCtx* c, uint32_t attr_bit, const float* A, const flo
     return fail(VT_ERR_UNSUPPORTED, "M = %lld has more slabs than the library keeps tickets for", (long long)M);
   const int64_t total = K * 2 * NT;
   const int blocks = int(total / 256 + 1 < int64_t(c->sm_count) * 8 ? total / 256 + 1 : int64_t(c->sm_count) * 8);
-  tall_b_and_lo_kernel<<<blocks, 256, 0, s>>>(B, b_and_lo, K, int(N), NT, ldb);
+  VT_CUDA(launch_overlapped(tall_b_and_lo_kernel, unsigned(blocks), 256u, size_t(0), s, B, b_and_lo, K, int(N), int(NT),
+                            ldb));
   count_launch();
   CUtensorMap tmBig, tmSmall;
   int rc = encode_tmap_2d(&tmBig, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, A, uint64_t(K), uint64_t(M), uint64_t(K) * 4, 32, 128);

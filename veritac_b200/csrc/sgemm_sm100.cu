@@ -144,6 +144,10 @@ sgemm_tile_kernel(const float* __restrict__ A, const float* __restrict__ B, floa
 #pragma unroll
     for (int j = 0; j < 4 * RN; ++j) acc[p][j] = make_float2(0.f, 0.f);
 
+  // Launched for overlap with the kernel before it on the stream (launch_overlapped): its blocks may be placed
+  // while that kernel's last blocks run; nothing is read or written before it has completed.
+  grid_dependency_wait();
+  grid_launch_dependents();
   const int ktiles = (K + SG_BK - 1) / SG_BK;
   load_tile(0, 0);
   store_tile(0);
@@ -512,9 +516,11 @@ int launch_tile(const float* A, const float* B, float* C, int M, int N, int K, c
       ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(C)) & 15) == 0;
   const bool full = aligned && M % BM == 0 && N % BN == 0 && K % SG_BK == 0;
   if (full)
-    sgemm_tile_kernel<RM, RN, false><<<unsigned(tiles), SG_THREADS, 0, s>>>(A, B, C, M, N, K, tiles_m, tiles_n, group);
+    VT_CUDA(launch_overlapped(sgemm_tile_kernel<RM, RN, false>, unsigned(tiles), unsigned(SG_THREADS), size_t(0), s, A, B,
+                              C, M, N, K, tiles_m, tiles_n, group));
   else
-    sgemm_tile_kernel<RM, RN, true><<<unsigned(tiles), SG_THREADS, 0, s>>>(A, B, C, M, N, K, tiles_m, tiles_n, group);
+    VT_CUDA(launch_overlapped(sgemm_tile_kernel<RM, RN, true>, unsigned(tiles), unsigned(SG_THREADS), size_t(0), s, A, B,
+                              C, M, N, K, tiles_m, tiles_n, group));
   count_launch();
   VT_CUDA(cudaGetLastError());
   return VT_OK;

@@ -395,8 +395,11 @@ i8gemm_umma_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
       if (!__all_sync(0xffffffffu, ready)) break;
       tc_fence_after_sync();
       const uint32_t t_row = tmem_base + (uint32_t(q * 32) << 16) + uint32_t(acc * BN);
+      // The last tile's epilogue overlaps nothing, and by now every MMA of this pair has read its operands and
+      // no load is in flight: the operand ring serves as one store buffer per column chunk (4 x 32 KiB).
+      uint8_t* wide = (kTmaStore && t + num_pairs >= num_tiles) ? tiles + size_t(q) * 8 * EPI_BUF_BYTES : nullptr;
       epilogue_warp_tile<kTmaStore, kBufs>(t_row, &tmC, staging + q * kBufs * EPI_BUF_BYTES, C, M, N, m0 + q * 32, n0, lane,
-                                           store_policy);
+                                           store_policy, wide);
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive_remote(&ps->tmem_empty[acc], 0);

@@ -44,11 +44,14 @@ __device__ __forceinline__ void tile_coords(const TileRaster& rs, int t, int& mi
 //   kTmaStore: TMEM -> registers -> swizzled shared memory -> cp.async.bulk.tensor store, so C is
 //              written in whole 128-byte lines and rows/columns outside C are clipped by the TMA unit;
 //   otherwise: TMEM -> registers -> predicated 16-byte global stores.
+// `wide`, when given, is 8 further buffers (32 KiB, 1024-byte aligned) that nothing else uses any more: every
+// column chunk then gets a buffer of its own and no store waits for the one before it (the last tile of a
+// CTA, whose epilogue nothing overlaps, takes them from the idle operand ring).
 // Returns once the accumulator has been read (the stores may still be in flight).
 template <bool kTmaStore, int kBufs = 2>
 __device__ __forceinline__ void epilogue_warp_tile(uint32_t t_row, const CUtensorMap* tmC, uint8_t* staging,
                                                    int32_t* __restrict__ C, int M, int N, int row0, int n0,
-                                                   int lane, uint64_t store_policy = 0) {
+                                                   int lane, uint64_t store_policy = 0, uint8_t* wide = nullptr) {
   const int row = row0 + lane;
 #pragma unroll 1
   for (int c = 0; c < BN / 32; ++c) {
@@ -56,9 +59,11 @@ __device__ __forceinline__ void epilogue_warp_tile(uint32_t t_row, const CUtenso
     tmem_ld_32x32b_x32(t_row + uint32_t(c * 32), r);
     tmem_ld_wait();
     if constexpr (kTmaStore) {
-      uint8_t* buf = staging + (c & (kBufs - 1)) * EPI_BUF_BYTES;
-      if (lane == 0) tma_store_wait_read<kBufs - 1>();   // the store that last read this buffer is done with it
-      __syncwarp();
+      uint8_t* buf = wide ? wide + c * EPI_BUF_BYTES : staging + (c & (kBufs - 1)) * EPI_BUF_BYTES;
+      if (!wide) {
+        if (lane == 0) tma_store_wait_read<kBufs - 1>();   // the store that last read this buffer is done with it
+        __syncwarp();
+      }
       const uint32_t base = smem_u32(buf) + uint32_t(lane) * 128u;
 #pragma unroll
       for (int v = 0; v < 8; ++v)

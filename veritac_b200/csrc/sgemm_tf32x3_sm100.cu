@@ -272,12 +272,18 @@ sgemm_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_
         if (acc == 0) acc_phase ^= 1;
       }
       if (!alive) break;
-      // registers -> swizzled shared memory -> TMA store, 32 columns at a time
+      // registers -> swizzled shared memory -> TMA store, 32 columns at a time.  After the pair's last tile every
+      // MMA has read its operands and no load is in flight: the idle operand ring then gives each chunk a buffer
+      // of its own (8 warps x 4 x 4 KiB) and no store waits for the one before it.
+      const bool last = t + num_pairs >= num_tiles;
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
-        if (lane == 0) tma_store_wait_read<0>();
-        __syncwarp();
-        const uint32_t base = smem_u32(stage_buf) + uint32_t(lane) * 128u;
+        uint8_t* buf = last ? tiles + size_t(e * 4 + c) * EPI_BUF_BYTES : stage_buf;
+        if (!last) {
+          if (lane == 0) tma_store_wait_read<0>();
+          __syncwarp();
+        }
+        const uint32_t base = smem_u32(buf) + uint32_t(lane) * 128u;
 #pragma unroll
         for (int v = 0; v < 8; ++v)
           st_shared_v4(base + (uint32_t(v ^ (lane & 7)) << 4), __float_as_uint(master[c * 32 + 4 * v]),
@@ -286,7 +292,7 @@ sgemm_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_
         fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) {
-          if (row0 < M && col0 + c * 32 < N) tma_store_2d(&tmC, stage_buf, col0 + c * 32, row0);
+          if (row0 < M && col0 + c * 32 < N) tma_store_2d(&tmC, buf, col0 + c * 32, row0);
           tma_store_commit();
         }
       }

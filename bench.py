@@ -573,7 +573,10 @@ def run_gpu_arm(args, kind, M, N, K, batch, metric, unit):
                    "sharding": "M rows per rank, B broadcast once from rank 0 (%.2f ms, outside the timed region), "
                                "no data-path collective" % bcast_ms if world > 1 else "single GPU",
                    "l2": "working set per launch %.0f MiB > 126 MB L2; no flush between steps"
-                         % ((rows * K * elem_in + K * N * elem_in + rows * N * elem_out) / 2**20)},
+                         % ((rows * K * elem_in + K * N * elem_in + rows * N * elem_out) / 2**20),
+                   "launch": "steps are enqueued back to back; the kernels are launched with programmatic stream "
+                             "serialization (a step's set-up may overlap the end of the step before it; it touches "
+                             "memory only after that step has completed)"},
         "clocks": clocks,
         "sustained": None if sustained is None else dict(
             sustained, value=ops_per_step_job / (sustained["ms_per_step"] * 1e-3) / 1e12, unit=unit,

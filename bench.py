@@ -203,7 +203,7 @@ def _oracle_lib():
     lib = ctypes.CDLL(str(build_oracle.build()))
     i64, vp = ctypes.c_long, ctypes.c_void_p
     lib.oracle_i8_tiled_ref.argtypes = [vp, vp, vp, i64, i64, i64, i64, i64]
-    for name in ("oracle_sgemm_tuned", "oracle_dgemm_tuned"):
+    for name in ("oracle_sgemm_tuned", "oracle_dgemm_tuned", "oracle_sgemm_naive"):
         getattr(lib, name).argtypes = [vp, vp, vp, i64, i64, i64]
     lib.oracle_threads.restype = ctypes.c_int
     return lib
@@ -227,6 +227,11 @@ class CpuArm:
             allowed = os.cpu_count() or 1
         self.lib.oracle_set_threads(ctypes.c_int(allowed))   # not whatever OMP_NUM_THREADS the launcher exported
         self.threads = int(self.lib.oracle_threads())
+        # The README schedule tiles i1 by 32, which the tile tactic refuses when 32 does not divide N; the untuned
+        # nest of make_matmul_stmt (one thread) is then what the reference has for the shape.
+        self.untuned = kind == "f32" and N % 32 != 0
+        if self.untuned:
+            self.threads = 1
         rng = np.random.default_rng(seed)
         self.block = 16 if kind != "f32" else 32
         self.unit = self.block * self.threads            # rows that keep every thread busy
@@ -245,8 +250,8 @@ class CpuArm:
         t0 = time.perf_counter()
         if self.kind == "f32":
             self.C[:rows] = 0
-            self.lib.oracle_sgemm_tuned(self.A.ctypes.data, self.B.ctypes.data, self.C.ctypes.data, rows, self.N,
-                                        self.K)
+            fn = self.lib.oracle_sgemm_naive if self.untuned else self.lib.oracle_sgemm_tuned
+            fn(self.A.ctypes.data, self.B.ctypes.data, self.C.ctypes.data, rows, self.N, self.K)
         else:
             self.lib.oracle_i8_tiled_ref(self.A.ctypes.data, self.B.ctypes.data, self.C.ctypes.data, rows, self.N,
                                          self.K, 0, rows)
@@ -262,7 +267,9 @@ class CpuArm:
         return 2.0 * rows * self.N * self.K
 
     def describe(self, rows: int) -> str:
-        what = ("OpenMP C restatement of the generated tile(32)x2/reorder/simd/parallel fp32 nest"
+        what = ("C restatement of the untuned generated fp32 nest (tile 32 does not divide N), one thread"
+                if self.untuned else
+                "OpenMP C restatement of the generated tile(32)x2/reorder/simd/parallel fp32 nest"
                 if self.kind == "f32" else
                 "OpenMP C restatement of the reference's int8 tile loop (baseline i,j,k order)")
         return "%s; rows [0,%d) of the %dx%dx%d product (all of B)" % (what, rows, self.M, self.N, self.K)

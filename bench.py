@@ -4,17 +4,23 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl reference]
 
 One JSON line on stdout (rank 0).  A *step* is one pass of the hot path over one batch of synthetic
-input: one GEMM of the named shape per GPU.  Default workload: exact int8 x int8 -> int32 GEMM,
-M = N = K = 8192 per GPU (BASELINE.json configs[2]); with N GPUs every rank owns 8192 rows of a
-(8192*N) x 8192 A and C (M-row sharding, weak scaling) and B is broadcast once from rank 0 over NCCL
-before timing.  There is no data-path collective.
+input: one GEMM of the named shape.  Default workload: exact int8 x int8 -> int32 GEMM with
+M = N = K = 8192; with N GPUs the 8192 rows of A and C are split over the ranks (rank r owns rows
+[r*M/N, (r+1)*M/N), strong scaling) and B is broadcast from rank 0 over NCCL before timing.  There is
+no data-path collective.  `--scaling weak` gives every rank the whole shape instead.
 
   value      whole-job throughput, operands resident in HBM, CUDA-event time on the launching
              stream, max over ranks
   e2e        same metric through the C ABI with pinned HOST buffers: host->device copies of A and B
-             and the device->host copy of C are inside the timed region of every step
+             and the device->host copy of C are inside the timed region of every step (with N > 1, B
+             crosses the host link on rank 0 only and reaches the other GPUs by the broadcast, also
+             inside the timed region); link_floor_ms = plain copies of the same bytes, no compute
+  parity     after the timed regions every rank checks sampled rows of its C, from the device-resident
+             run and from the host-buffer run, against the exact product; ok = all ranks passed
   roofline   achieved = algorithmic ops (or bytes) per launch / average launch duration of the
              timed region; peak from MEASURED_PEAKS.json (fallback stated if absent)
+  also       the other named workloads, each timed like the headline (fp32 8192^3 by the automatic
+             choice and by the FFMA kernel, fp32 16 x 8192 x 8192, the batched B-reuse int8 workload)
   cpu_baseline  the oracle's OpenMP C restatement of the reference's CPU arithmetic, timed on this
              host's cores on a bounded sample of the same workload (N = 1 only)
 
@@ -41,16 +47,19 @@ NOMINAL_INT8_TOPS = 4500.0     # dense int8, NVIDIA's B200 figure
 NOMINAL_FP32_TFLOPS = 74.45    # 148 SMs x 128 FMA lanes x 2 x 1.965 GHz
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
-# DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the ncu captures
-# summarised under profiles/; None until a capture exists for the workload.
+# DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) of the dominant kernel, constants typed in
+# from ncu captures of these workloads on one GPU (a run of this script cannot measure them); None where no
+# capture was taken.
 NCU_TRAFFIC_BYTES = {"sgemm_skinny": 273.9e6, "sgemm_panel_128": 282.9e6, "sgemm_tall_16": 275.8e6, "i8_8192": 590.1e6, "i8_batched_32": 654.4e6, "i8_batched": 8 * 654.4e6}
 
 WORKLOADS = {
     # name: (kind, M, N, K, batch)
     "i8_8192": ("i8", 8192, 8192, 8192, 1),
     "i8_64": ("i8", 64, 64, 64, 1),
+    "i8_shard_2048": ("i8", 2048, 8192, 8192, 1),         # one GPU's rows of the 8192^3 product on 4 GPUs
+    "i8_shard_1024": ("i8", 1024, 8192, 8192, 1),         # ... on 8 GPUs
     "i8_batched": ("i8b", 1024, 4096, 4096, 256),
-    "i8_batched_32": ("i8b", 1024, 4096, 4096, 32),      # one GPU's share of config 4 on 8 GPUs
+    "i8_batched_32": ("i8b", 1024, 4096, 4096, 32),      # one GPU's share of the batched workload on 8 GPUs
     "sgemm_8192": ("f32", 8192, 8192, 8192, 1),
     "sgemm_256": ("f32", 256, 256, 256, 1),
     "sgemm_skinny": ("f32", 16, 8192, 8192, 1),
@@ -348,9 +357,9 @@ def run_reference_arm(args, kind, M, N, K, metric, unit):
     value = arm.ops(rows) * steps / total / 1e12
     line = {
         "impl": "reference", "metric": metric, "value": value, "unit": unit, "n_gpus": args.gpus, "steps": steps,
-        "warmup": warm, "ms_per_step": total / steps * 1e3, "higher_is_better": True, "scaling": "weak",
+        "warmup": warm, "ms_per_step": total / steps * 1e3, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "f32" if kind == "f32" else "s8->s32", "data": "synthetic",
-        "config": {"workload": args.workload, "M": M, "N": N, "K": K,
+        "config": {"workload": args.workload, "M_per_gpu": M, "N": N, "K": K, "global_M": M,
                    "note": "CPU arm: each step is a bounded row sample of the workload on the host cores"},
         "cpu_baseline": {"value": value, "unit": unit, "cores": arm.threads, "kind": arm.kind_label,
                          "sample": arm.describe(rows)},
@@ -364,176 +373,15 @@ def run_reference_arm(args, kind, M, N, K, metric, unit):
 # ---------------------------------------------------------------------------------------------
 # GPU arm
 # ---------------------------------------------------------------------------------------------
-def run_gpu_arm(args, kind, M, N, K, batch, metric, unit):
-    import numpy as np
-    import torch
-    import torch.distributed as dist
+PANEL_WORKLOADS = ("sgemm_skinny", "sgemm_panel_64", "sgemm_panel_128", "sgemm_tall_16")
 
-    from veritac_b200 import _native as nv
-    from veritac_b200 import build, sharding
 
-    build.build()
-    rank, world, local = sharding.init_process_group()
-    if world != args.gpus:
-        if rank == 0:
-            sys.stderr.write("bench: --gpus %d but WORLD_SIZE is %d (launch with torchrun)\n" % (args.gpus, world))
-        if args.gpus != 1:
-            return 2
-    if not torch.cuda.is_available():
-        sys.stderr.write("bench: no CUDA device; the GPU arm has no CPU fallback\n")
-        return 2
-    torch.cuda.set_device(local)
-    dev = local
-    peaks, peaks_src = load_peaks()
-    steps, warm = max(1, args.steps), max(3, args.warmup)
-    rows = M * batch                     # rows this rank owns (weak scaling: per-GPU work is fixed)
-    if args.scaling == "strong":
-        r0, r1 = sharding.row_shard(M * batch, world, rank, align=M if kind == "i8b" else 16)
-        rows = r1 - r0
-    gen = torch.Generator(device="cuda").manual_seed(20260917 + rank)
-    st = nv.torch_stream()
-
-    # Operands: A differs per rank (its own row block); B comes from rank 0 by one broadcast.
-    if kind == "f32":
-        A = torch.rand((rows, K), device="cuda", generator=gen) * 2 - 1
-        B = torch.rand((K, N), device="cuda", generator=gen) * 2 - 1
-        C = torch.zeros((rows, N), device="cuda")
-        elem_in, elem_out = 4, 4
-    else:
-        A = torch.randint(-128, 128, (rows, K), dtype=torch.int8, device="cuda", generator=gen)
-        B = torch.randint(-128, 128, (K, N), dtype=torch.int8, device="cuda", generator=gen)
-        C = torch.empty((rows, N), dtype=torch.int32, device="cuda")
-        elem_in, elem_out = 1, 4
-    t_b0 = time.perf_counter()
-    sharding.replicate_from_rank0(B)
-    torch.cuda.synchronize()
-    bcast_ms = (time.perf_counter() - t_b0) * 1e3
-
-    def step():
-        if kind == "f32":
-            nv.sgemm(A, B, C, rows, N, K, dev=dev, variant=args.sgemm_variant, where=nv.VT_DEVICE, stream=st)
-        elif kind == "i8b":
-            nv.i8gemm_shared_b(A, B, C, rows // M, M, N, K, dev=dev, acc_rows=16, where=nv.VT_DEVICE, stream=st)
-        else:
-            nv.i8gemm(A, B, C, rows, N, K, dev=dev, variant=args.i8_variant, where=nv.VT_DEVICE, stream=st)
-
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    for _ in range(warm):
-        step()
-    nv.sync(dev, st)
-    barrier()
-    try:
-        gpu_uuid = str(torch.cuda.get_device_properties(dev).uuid)
-    except Exception:
-        gpu_uuid = None
-    sampler = ClockSampler(local, gpu_uuid)
-    if rank == 0:
-        sampler.start()
-        time.sleep(0.05)
-    launches0 = nv.launch_count()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
-    sampler.mark_begin()
-    e0.record()
-    for _ in range(steps):
-        step()
-    e1.record()
-    barrier()
-    sampler.mark_end()
-    elapsed_ms = e0.elapsed_time(e1)
-    launches = nv.launch_count() - launches0
-    nv.sync(dev, st)
-    if world > 1:
-        t = torch.tensor([elapsed_ms], device="cuda", dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        elapsed_ms = float(t.item())
-        tot = torch.tensor([float(rows)], device="cuda", dtype=torch.float64)
-        dist.all_reduce(tot, op=dist.ReduceOp.SUM)
-        total_rows = float(tot.item())
-    else:
-        total_rows = float(rows)
-    ms_per_step = elapsed_ms / steps
-
-    # ---- the same step back to back for about a second: NVML's clock and power readings lag a region of a
-    # few milliseconds, so this is where the power cap shows; reported beside the timed region, not as it ----
-    sustained = None
-    if args.sustain_seconds > 0:
-        reps = max(steps, min(200000, int(args.sustain_seconds * 1e3 / max(ms_per_step, 1e-3))))
-        s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        barrier()
-        t_s0 = time.perf_counter()
-        s0.record()
-        for _ in range(reps):
-            step()
-        s1.record()
-        barrier()
-        t_s1 = time.perf_counter()
-        sus_ms = s0.elapsed_time(s1) / reps
-        nv.sync(dev, st)
-        if world > 1:
-            t = torch.tensor([sus_ms], device="cuda", dtype=torch.float64)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            sus_ms = float(t.item())
-        if rank == 0:
-            # the second half of the window: the readings have caught up with the load by then
-            sustained = sampler.window(0.5 * (t_s0 + t_s1), t_s1) or {}
-            sustained.update({"steps": reps, "ms_per_step": sus_ms, "seconds": t_s1 - t_s0})
-    clocks = sampler.stop() if rank == 0 else None
-    ops_per_step_job = 2.0 * total_rows * N * K
-    value = ops_per_step_job / (ms_per_step * 1e-3) / 1e12
-
-    # ---- end to end through the C ABI with pinned host buffers (every rank, its own block) ----
-    e2e_steps = max(2, min(steps, 5))
-    hA = torch.empty((rows, K), dtype=A.dtype).pin_memory()
-    hB = torch.empty((K, N), dtype=B.dtype).pin_memory()
-    hC = torch.empty((rows, N), dtype=C.dtype).pin_memory()
-    hA.copy_(A)
-    hB.copy_(B)
-
-    def e2e_step():
-        if kind == "f32":
-            nv.sgemm(hA, hB, hC, rows, N, K, dev=dev, where=nv.VT_HOST)
-        elif kind == "i8b":
-            nv.i8gemm_shared_b(hA, hB, hC, rows // M, M, N, K, dev=dev, acc_rows=16, where=nv.VT_HOST)
-        else:
-            nv.i8gemm(hA, hB, hC, rows, N, K, dev=dev, where=nv.VT_HOST)
-
-    if args.no_e2e:
-        e2e_steps = 0
-        e2e_s = None
-    else:
-        e2e_step()
-        barrier()
-        t0 = time.perf_counter()
-        for _ in range(e2e_steps):
-            e2e_step()
-        barrier()
-        e2e_s = (time.perf_counter() - t0) / e2e_steps
-    if world > 1 and e2e_s:
-        t = torch.tensor([e2e_s], device="cuda", dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_s = float(t.item())
-    e2e_value = ops_per_step_job / e2e_s / 1e12 if e2e_s else None
-    e2e_ok = bool(torch.equal(hC[:64].cuda(), C[:64])) if kind != "f32" and not args.no_e2e else None
-    h2d = (rows * K + K * N) * elem_in
-    d2h = rows * N * elem_out
-
-    if rank != 0:
-        if world > 1:
-            dist.barrier()
-            dist.destroy_process_group()
-        return 0
-
-    # ---- roofline of the dominant kernel (this rank's launch) ----
-    launch_ms = ms_per_step
+def roofline_for(workload, kind, rows, N, K, launch_ms, peaks, peaks_src, sgemm_variant, nv):
+    """Roofline object of the dominant kernel of one rank's launch (see the module docstring)."""
     ops_per_launch = 2.0 * rows * N * K
     algo_bytes = (K * N + rows * K + rows * N) * 4.0
     tf32x3_peak = peaks["bf16_tflops"] / 2.0 / 3.0       # three TF32 MMAs per fp32 product; TF32 at half the bf16 rate
-    panel = args.workload in ("sgemm_skinny", "sgemm_panel_64", "sgemm_panel_128", "sgemm_tall_16")
+    panel = workload in PANEL_WORKLOADS
     if panel and algo_bytes / (peaks["hbm_gbs"] * 1e9) >= ops_per_launch / (tf32x3_peak * 1e12):
         achieved = algo_bytes / (launch_ms * 1e-3) / 1e9
         roof = {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
@@ -548,13 +396,12 @@ def run_gpu_arm(args, kind, M, N, K, batch, metric, unit):
                 "hbm_gbs_achieved": algo_bytes / (launch_ms * 1e-3) / 1e9}
     elif kind == "f32":
         achieved = ops_per_launch / (launch_ms * 1e-3) / 1e12
-        tensor_path = args.sgemm_variant == nv.VT_SGEMM_TF32X3 or (
-            args.sgemm_variant == nv.VT_SGEMM_AUTO and rows >= 256 and N >= 256 and K >= 256
+        tensor_path = sgemm_variant == nv.VT_SGEMM_TF32X3 or (
+            sgemm_variant == nv.VT_SGEMM_AUTO and rows >= 256 and N >= 256 and K >= 256
             and float(rows) * N * K >= 5.0e8 and N % 4 == 0 and K % 4 == 0)
         if tensor_path:
-            # three TF32 MMAs per fp32 product; TF32 issues at half the bf16 rate
-            peak = peaks["bf16_tflops"] / 2.0 / 3.0
-            roof = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+            roof = {"bound": "tensor", "achieved": achieved, "peak": tf32x3_peak, "unit": "TFLOP/s",
+                    "frac": achieved / tf32x3_peak,
                     "peak_source": "%s bf16_tflops / 2 (TF32 rate) / 3 (MMAs per fp32 product); the step also holds the "
                                    "pass that writes the lo parts" % peaks_src,
                     "vs_ffma_pipe_74.45": achieved / NOMINAL_FP32_TFLOPS}
@@ -566,34 +413,354 @@ def run_gpu_arm(args, kind, M, N, K, batch, metric, unit):
     else:
         achieved = ops_per_launch / (launch_ms * 1e-3) / 1e12
         peak = 2.0 * peaks["bf16_tflops"]
-        roof = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+        roof = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TOP/s", "frac": achieved / peak,
                 "peak_source": "2 x %s bf16_tflops (kind::i8 issues at twice the bf16 rate)" % peaks_src,
                 "frac_of_nominal_4500": achieved / NOMINAL_INT8_TOPS}
-    roof["traffic"] = NCU_TRAFFIC_BYTES.get(args.workload)
+    roof["traffic"] = NCU_TRAFFIC_BYTES.get(workload)
+    roof["traffic_source"] = ("constant from an ncu capture of this workload on one GPU, not measured by this run"
+                              if roof["traffic"] is not None else None)
     roof["launch_ms"] = launch_ms
+    return roof
 
+
+class Job:
+    """One workload on this rank: operands in HBM, the device-resident step, timing, the parity check."""
+
+    def __init__(self, ctx, workload, scaling, i8_variant=0, sgemm_variant=0):
+        torch, nv, sharding = ctx["torch"], ctx["nv"], ctx["sharding"]
+        self.ctx, self.workload = ctx, workload
+        self.kind, self.M, self.N, self.K, self.batch = WORKLOADS[workload]
+        self.i8_variant, self.sgemm_variant = i8_variant, sgemm_variant
+        rank, world = ctx["rank"], ctx["world"]
+        total = self.M * self.batch
+        self.replicas = world > 1 and total < 16 * world        # too few rows to split: every rank runs the whole shape
+        if scaling == "weak" or world == 1 or self.replicas:
+            self.rows = total
+        else:
+            r0, r1 = sharding.row_shard(total, world, rank, align=self.M if self.kind == "i8b" else 16)
+            self.rows = r1 - r0
+        gen = torch.Generator(device="cuda").manual_seed(20260917 + rank + 1000 * (sorted(WORKLOADS).index(workload) + 1))
+        self.gen = gen
+        N, K, rows = self.N, self.K, self.rows
+        if self.kind == "f32":
+            self.A = torch.rand((rows, K), device="cuda", generator=gen) * 2 - 1
+            self.B = torch.rand((K, N), device="cuda", generator=gen) * 2 - 1
+            self.C = torch.zeros((rows, N), device="cuda")
+            self.elem_in, self.elem_out = 4, 4
+        else:
+            self.A = torch.randint(-128, 128, (rows, K), dtype=torch.int8, device="cuda", generator=gen)
+            self.B = torch.randint(-128, 128, (K, N), dtype=torch.int8, device="cuda", generator=gen)
+            self.C = torch.empty((rows, N), dtype=torch.int32, device="cuda")
+            self.elem_in, self.elem_out = 1, 4
+        # Operands: A differs per rank (its own row block); B is rank 0's, delivered by broadcast.
+        sharding.replicate_from_rank0(self.B)
+        self.total_rows = ctx["sum"](float(rows)) if not self.replicas else float(rows)
+
+    def step(self):
+        nv, dev, st = self.ctx["nv"], self.ctx["dev"], self.ctx["st"]
+        if self.rows == 0:
+            return
+        if self.kind == "f32":
+            nv.sgemm(self.A, self.B, self.C, self.rows, self.N, self.K, dev=dev, variant=self.sgemm_variant,
+                     where=nv.VT_DEVICE, stream=st)
+        elif self.kind == "i8b":
+            nv.i8gemm_shared_b(self.A, self.B, self.C, self.rows // self.M, self.M, self.N, self.K, dev=dev, acc_rows=16,
+                               where=nv.VT_DEVICE, stream=st)
+        else:
+            nv.i8gemm(self.A, self.B, self.C, self.rows, self.N, self.K, dev=dev, variant=self.i8_variant,
+                      where=nv.VT_DEVICE, stream=st)
+
+    def timed(self, steps, warm, sampler=None):
+        """(ms per step: CUDA events on the launching stream, max over ranks; kernel launches of this rank)."""
+        torch, nv, ctx = self.ctx["torch"], self.ctx["nv"], self.ctx
+        for _ in range(warm):
+            self.step()
+        nv.sync(ctx["dev"], ctx["st"])
+        ctx["barrier"]()
+        launches0 = nv.launch_count()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ctx["barrier"]()
+        if sampler:
+            sampler.mark_begin()
+        e0.record()
+        for _ in range(steps):
+            self.step()
+        e1.record()
+        ctx["barrier"]()
+        if sampler:
+            sampler.mark_end()
+        ms = ctx["max"](e0.elapsed_time(e1)) / steps
+        launches = nv.launch_count() - launches0
+        nv.sync(ctx["dev"], ctx["st"])
+        return ms, launches
+
+    def value(self, ms_per_step):
+        """Whole-job throughput in T(FL)OPS; replicas count once (every rank does the same whole product)."""
+        return 2.0 * self.total_rows * self.N * self.K / (ms_per_step * 1e-3) / 1e12
+
+    def check(self, C, samples=32):
+        """Sampled rows of this rank's C against the exact product.  int8: float64 matmul of the sampled rows is exact
+        (|sum| < 2^53) and every bit must agree; fp32: relative Frobenius error of the sampled rows against float64,
+        bound 1e-5."""
+        torch = self.ctx["torch"]
+        if self.rows == 0:
+            return {"ok": True, "rows_checked": 0}
+        idx = torch.randint(0, self.rows, (min(samples, self.rows),), device="cuda", generator=self.gen)
+        got = C[idx.cpu()] if C.device.type == "cpu" else C[idx]
+        got = got.cuda()
+        exact = self.A[idx].double() @ self.B.double()
+        if self.kind == "f32":
+            err = float(torch.linalg.norm(got.double() - exact) / torch.linalg.norm(exact))
+            return {"ok": bool(err <= 1e-5), "rows_checked": int(idx.numel()), "rel_frobenius": err, "bound": 1e-5}
+        bad = int((got.to(torch.int64) != exact.to(torch.int64)).sum().item())
+        return {"ok": bad == 0, "rows_checked": int(idx.numel()), "cells_differing": bad}
+
+    def release(self):
+        self.A = self.B = self.C = None
+        self.ctx["torch"].cuda.empty_cache()
+
+
+def run_gpu_arm(args, kind, M, N, K, batch, metric, unit):
+    import torch
+    import torch.distributed as dist
+
+    from veritac_b200 import _native as nv
+    from veritac_b200 import build, sharding
+
+    build.build()
+    t_init0 = time.perf_counter()
+    rank, world, local = sharding.init_process_group()
+    if world != args.gpus:
+        if rank == 0:
+            sys.stderr.write("bench: --gpus %d but WORLD_SIZE is %d (launch with torchrun)\n" % (args.gpus, world))
+        if args.gpus != 1:
+            return 2
+    if not torch.cuda.is_available():
+        sys.stderr.write("bench: no CUDA device; the GPU arm has no CPU fallback\n")
+        return 2
+    torch.cuda.set_device(local)
+    dev = local
+    peaks, peaks_src = load_peaks()
+    steps, warm = max(1, args.steps), max(3, args.warmup)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def reduce_scalar(x, op):
+        if world == 1:
+            return float(x)
+        t = torch.tensor([float(x)], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=op)
+        return float(t.item())
+
+    ctx = {"torch": torch, "nv": nv, "sharding": sharding, "rank": rank, "world": world, "dev": dev,
+           "st": nv.torch_stream(), "barrier": barrier,
+           "max": lambda x: reduce_scalar(x, dist.ReduceOp.MAX), "sum": lambda x: reduce_scalar(x, dist.ReduceOp.SUM),
+           "min": lambda x: reduce_scalar(x, dist.ReduceOp.MIN)}
+
+    # ---- communicator: created by the first collective; timed apart from the broadcast of B ----
+    comm_init_ms = bcast_ms_warm = None
+    if world > 1:
+        tiny = torch.zeros(1, device="cuda")
+        dist.broadcast(tiny, src=0)
+        torch.cuda.synchronize()
+        comm_init_ms = (time.perf_counter() - t_init0) * 1e3
+
+    job = Job(ctx, args.workload, args.scaling, args.i8_variant, args.sgemm_variant)
+    rows, global_rows = job.rows, int(job.total_rows)
+    if world > 1:
+        b0, b1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        b0.record()
+        sharding.replicate_from_rank0(job.B)
+        b1.record()
+        torch.cuda.synchronize()
+        bcast_ms_warm = ctx["max"](b0.elapsed_time(b1))
+
+    try:
+        gpu_uuid = str(torch.cuda.get_device_properties(dev).uuid)
+    except Exception:
+        gpu_uuid = None
+    sampler = ClockSampler(local, gpu_uuid)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.05)
+    ms_per_step, launches = job.timed(steps, warm, sampler)
+    value = job.value(ms_per_step)
+
+    # ---- the same step back to back for about a second: NVML's clock and power readings lag a region of a
+    # few milliseconds, so this is where the power cap shows; reported beside the timed region, not as it ----
+    sustained = None
+    if args.sustain_seconds > 0:
+        reps = max(steps, min(200000, int(args.sustain_seconds * 1e3 / max(ms_per_step, 1e-3))))
+        s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        t_s0 = time.perf_counter()
+        s0.record()
+        for _ in range(reps):
+            job.step()
+        s1.record()
+        barrier()
+        t_s1 = time.perf_counter()
+        sus_ms = ctx["max"](s0.elapsed_time(s1) / reps)
+        nv.sync(dev, ctx["st"])
+        if rank == 0:
+            # the second half of the window: the readings have caught up with the load by then
+            sustained = sampler.window(0.5 * (t_s0 + t_s1), t_s1) or {}
+            sustained.update({"steps": reps, "ms_per_step": sus_ms, "seconds": t_s1 - t_s0})
+    clocks = sampler.stop() if rank == 0 else None
+
+    # ---- parity of the device-resident run: this rank's C as the timed steps left it ----
+    parity_device = job.check(job.C)
+
+    # ---- end to end through the C ABI with pinned host buffers ----
+    # One GPU: A, B and C are host buffers of one vt_* call.  Several GPUs, int8: B exists in rank 0's host memory
+    # only; rank 0 copies it in, the broadcast carries it to the other GPUs, and every rank's call takes its rows
+    # of A from and returns its rows of C to host memory (VT_HOST_AC_DEVICE_B).  All of that is inside the timed
+    # region of every step.
+    e2e = {"value": None, "unit": unit, "h2d_bytes_per_step": None, "d2h_bytes_per_step": None}
+    parity_host = None
+    if not args.no_e2e:
+        e2e_steps = max(2, min(steps, 5))
+        hA = torch.empty((rows, K), dtype=job.A.dtype).pin_memory()
+        hC = torch.empty((rows, N), dtype=job.C.dtype).pin_memory()
+        hA.copy_(job.A)
+        shared_b = world > 1 and kind != "f32" and not job.replicas
+        hB = torch.empty((K, N), dtype=job.B.dtype).pin_memory() if (rank == 0 or not shared_b) else None
+        if hB is not None:
+            hB.copy_(job.B)
+        dB = torch.empty_like(job.B) if shared_b else None
+
+        def host_call(a, b, c, where):
+            if rows == 0:
+                return
+            if kind == "f32":
+                nv.sgemm(a, b, c, rows, N, K, dev=dev, where=where)
+            elif kind == "i8b":
+                nv.i8gemm_shared_b(a, b, c, rows // M, M, N, K, dev=dev, acc_rows=16, where=where, stream=ctx["st"])
+            else:
+                nv.i8gemm(a, b, c, rows, N, K, dev=dev, where=where, stream=ctx["st"])
+
+        def e2e_step():
+            if shared_b:
+                sharding.run_row_sharded(lambda a, b, c: host_call(a, b, c, nv.VT_HOST_AC_DEVICE_B), hA, dB, hC,
+                                         B_source=hB)
+            else:
+                host_call(hA, hB, hC, nv.VT_HOST)
+
+        def floor_step():
+            # the same bytes over the same link as plain copies, both directions at once, no compute
+            with torch.cuda.stream(copy_in):
+                if hB is not None:
+                    job.B.copy_(hB, non_blocking=True)
+                job.A.copy_(hA, non_blocking=True)
+            with torch.cuda.stream(copy_out):
+                hC.copy_(job.C, non_blocking=True)
+
+        def wall(fn, n):
+            fn()
+            barrier()
+            t0 = time.perf_counter()
+            for _ in range(n):
+                fn()
+            barrier()
+            return ctx["max"]((time.perf_counter() - t0) / n)
+
+        e2e_s = wall(e2e_step, e2e_steps)
+        parity_host = job.check(hC)
+        copy_in, copy_out = torch.cuda.Stream(), torch.cuda.Stream()
+        floor_s = wall(floor_step, e2e_steps)
+        h2d = ctx["sum"](float((rows * K + (K * N if hB is not None else 0)) * job.elem_in))
+        d2h = ctx["sum"](float(rows * N * job.elem_out))
+        e2e = {"value": 2.0 * job.total_rows * N * K / e2e_s / 1e12, "unit": unit, "h2d_bytes_per_step": int(h2d),
+               "d2h_bytes_per_step": int(d2h), "steps": e2e_steps, "ms_per_step": e2e_s * 1e3,
+               "link_floor_ms": floor_s * 1e3, "over_link_floor": e2e_s / floor_s,
+               "bytes": "whole job, all ranks; " + ("B crosses the host link on rank 0 only and reaches the other "
+                                                     "GPUs by the NCCL broadcast inside the timed region"
+                                                     if shared_b else "every rank copies the operands it uses"),
+               "link_floor": "plain cudaMemcpyAsync of the same bytes on every rank at once, host->device and "
+                             "device->host on two streams, no compute, wall clock, max over ranks"}
+
+    parity = {"device_run": parity_device, "host_buffer_run": parity_host,
+              "ok": bool(ctx["min"](1.0 if parity_device["ok"] and (parity_host is None or parity_host["ok"]) else 0.0) > 0.5),
+              "ranks": world, "against": "exact product of the sampled rows in float64 on the GPU (int8: every bit; "
+                                         "fp32: relative Frobenius error <= 1e-5)"}
+
+    # ---- the weak-scaling figure beside the strong one: every rank the whole shape ----
+    weak = None
+    if world > 1 and args.scaling == "strong" and not job.replicas and not args.no_also:
+        job.release()
+        wjob = Job(ctx, args.workload, "weak", args.i8_variant, args.sgemm_variant)
+        w_ms, _ = wjob.timed(steps, warm)
+        weak = {"ms_per_step": w_ms, "value": wjob.value(w_ms), "unit": unit, "rows_per_gpu": wjob.rows,
+                "parity_ok": bool(ctx["min"](1.0 if wjob.check(wjob.C)["ok"] else 0.0) > 0.5)}
+        wjob.release()
+        job = None
+
+    # ---- the other named workloads, each timed like the headline ----
+    also = None
+    if not args.no_also:
+        if job is not None:
+            job.release()
+            job = None
+        also = {}
+        for name, wl, variant in (("sgemm_8192", "sgemm_8192", nv.VT_SGEMM_AUTO),
+                                  ("sgemm_8192_ffma", "sgemm_8192", nv.VT_SGEMM_TILE128),
+                                  ("sgemm_skinny", "sgemm_skinny", nv.VT_SGEMM_AUTO),
+                                  ("i8_batched", "i8_batched", 0)):
+            if wl == args.workload and variant == args.sgemm_variant:
+                continue
+            j = Job(ctx, wl, "strong", 0, variant)
+            a_ms, a_launches = j.timed(steps, warm)
+            ok = bool(ctx["min"](1.0 if j.check(j.C)["ok"] else 0.0) > 0.5)
+            roof = roofline_for(wl, j.kind, j.rows, j.N, j.K, a_ms, peaks, peaks_src, variant, nv)
+            also[name] = {"metric": metric_of(wl)[0], "ms_per_step": a_ms, "value": j.value(a_ms), "unit": metric_of(wl)[1],
+                          "rows_per_gpu": j.rows, "global_rows": int(j.total_rows), "launches": int(a_launches),
+                          "steps": steps, "parity_ok": ok,
+                          "sharding": "replicas (16 rows do not shard); value is one replica's" if j.replicas else
+                                      ("batch dealt over the ranks" if j.kind == "i8b" else "M rows per rank") if world > 1 else "single GPU",
+                          "roofline": {k: roof[k] for k in ("bound", "achieved", "peak", "unit", "frac")}}
+            j.release()
+
+    if rank != 0:
+        if world > 1:
+            dist.barrier()
+            dist.destroy_process_group()
+        return 0
+
+    roof = roofline_for(args.workload, kind, rows, N, K, ms_per_step, peaks, peaks_src, args.sgemm_variant, nv)
     line = {
         "metric": metric, "value": value, "unit": unit, "n_gpus": world, "steps": steps, "warmup": warm,
-        "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None,
-        "dtype": "f32" if kind == "f32" else "s8->s32", "data": "synthetic",
-        "config": {"workload": args.workload, "M_per_gpu": rows, "N": N, "K": K, "global_M": int(total_rows),
-                   "sharding": "M rows per rank, B broadcast once from rank 0 (%.2f ms, outside the timed region), "
-                               "no data-path collective" % bcast_ms if world > 1 else "single GPU",
+        "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": args.scaling if world > 1 else "strong",
+        "vs_baseline": None, "dtype": "f32" if kind == "f32" else "s8->s32", "data": "synthetic",
+        "config": {"workload": args.workload, "M_per_gpu": rows, "N": N, "K": K, "global_M": global_rows,
+                   "sharding": ("rows [r*M/g, (r+1)*M/g) of A and C per rank, B replicated: broadcast from rank 0 before "
+                                "the timed region; no data-path collective") if world > 1 else "single GPU",
+                   "comm_init_ms": comm_init_ms, "bcast_ms_warm": bcast_ms_warm,
+                   "bcast": "comm_init_ms: process group + first 4-byte broadcast (communicator creation), wall clock; "
+                            "bcast_ms_warm: one more broadcast of B on the warm communicator, CUDA events, max over ranks"
+                            if world > 1 else None,
                    "l2": "working set per launch %.0f MiB > 126 MB L2; no flush between steps"
-                         % ((rows * K * elem_in + K * N * elem_in + rows * N * elem_out) / 2**20),
+                         % ((rows * K * (1 if kind != "f32" else 4) + K * N * (1 if kind != "f32" else 4) + rows * N * 4) / 2**20),
                    "launch": "steps are enqueued back to back; the kernels are launched with programmatic stream "
                              "serialization (a step's set-up may overlap the end of the step before it; it touches "
                              "memory only after that step has completed)"},
         "clocks": clocks,
         "sustained": None if sustained is None else dict(
-            sustained, value=ops_per_step_job / (sustained["ms_per_step"] * 1e-3) / 1e12, unit=unit,
+            sustained, value=value * ms_per_step / sustained["ms_per_step"], unit=unit,
             note="the same step repeated back to back after the timed region; clocks are NVML samples of the second "
                  "half of that window"),
-        "e2e": {"value": e2e_value, "unit": unit, "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
-                "steps": e2e_steps, "ms_per_step": e2e_s * 1e3 if e2e_s else None, "matches_device_run": e2e_ok},
+        "e2e": e2e,
+        "parity": parity,
         "gpu_launches": int(launches),
         "roofline": roof,
     }
+    if weak is not None:
+        line["weak"] = weak
+    if also is not None:
+        line["also"] = also
     if world == 1 and not args.no_cpu_baseline:
         arm = make_cpu_arm(args, kind if kind != "i8b" else "i8", M * batch if kind == "i8b" else M, N, K)
         rows_cpu = arm.size_sample(12.0)
@@ -607,6 +774,16 @@ def run_gpu_arm(args, kind, M, N, K, batch, metric, unit):
     return 0
 
 
+def metric_of(workload):
+    kind, M, N, K, batch = WORKLOADS[workload]
+    if kind == "f32":
+        return "fp32 GEMM TFLOPS at %dx%dx%d" % (M, N, K), "TFLOPS"
+    if kind == "i8b":
+        return "exact int8->int32 batched B-reuse GEMM TOPS (%d x %dx%dx%d)" % (batch, M, N, K), "TOPS"
+    return ("exact int8->int32 GEMM TOPS at %d^3" % M if M == N == K else
+            "exact int8->int32 GEMM TOPS at %dx%dx%d" % (M, N, K)), "TOPS"
+
+
 def main() -> int:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--gpus", type=int, default=1)
@@ -614,8 +791,8 @@ def main() -> int:
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=("b200", "reference"), default="b200")
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default="i8_8192")
-    ap.add_argument("--scaling", choices=("weak", "strong"), default="weak",
-                    help="weak: every GPU gets the full shape; strong: the shape's rows are split over the GPUs")
+    ap.add_argument("--scaling", choices=("weak", "strong"), default="strong",
+                    help="strong: the shape's rows are split over the GPUs; weak: every GPU gets the full shape")
     ap.add_argument("--i8-variant", type=int, default=0, help="VT_I8_* kernel variant (0 = the library's choice)")
     ap.add_argument("--sgemm-variant", type=int, default=0, help="VT_SGEMM_* kernel variant (0 = the library's choice)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -623,15 +800,10 @@ def main() -> int:
                     help="after the timed region, repeat the step for about this long and report its rate and the "
                          "clocks NVML shows under that load (0 = skip)")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
+    ap.add_argument("--no-also", action="store_true", help="skip the other workloads and the weak figure")
     args = ap.parse_args()
     kind, M, N, K, batch = WORKLOADS[args.workload]
-    if kind == "f32":
-        metric, unit = "fp32 GEMM TFLOPS at %dx%dx%d" % (M, N, K), "TFLOPS"
-    elif kind == "i8b":
-        metric, unit = "exact int8->int32 batched B-reuse GEMM TOPS (%d x %dx%dx%d)" % (batch, M, N, K), "TOPS"
-    else:
-        metric, unit = "exact int8->int32 GEMM TOPS at %d^3" % M if M == N == K else \
-            "exact int8->int32 GEMM TOPS at %dx%dx%d" % (M, N, K), "TOPS"
+    metric, unit = metric_of(args.workload)
     if args.impl == "reference":
         return run_reference_arm(args, "i8" if kind == "i8b" else kind, M * batch if kind == "i8b" else M, N, K,
                                  metric, unit)

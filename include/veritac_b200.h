@@ -19,6 +19,11 @@
  *                         `stream` (a cudaStream_t, or NULL for the library's own stream; the
  *                         legacy default stream is cudaStreamLegacy, (void*)1) and returns;
  *                         vt_sync() waits and reports kernel status.
+ *              VT_HOST_AC_DEVICE_B (vt_i8gemm only) = one rank of a row-sharded job: A and C are this
+ *                         rank's row blocks in host memory, B is the replicated operand, already in
+ *                         this GPU's memory once the work queued on `stream` has run (the broadcast
+ *                         that delivered it).  Copies A in, computes, copies C out and returns when C
+ *                         is complete, like VT_HOST.
  *   - One host thread per device at a time; different devices may be driven concurrently.
  */
 #ifndef VERITAC_B200_H
@@ -41,7 +46,7 @@ enum {
   VT_ERR_PROGRAM = -6      /* malformed tile program */
 };
 
-enum { VT_HOST = 0, VT_DEVICE = 1 };
+enum { VT_HOST = 0, VT_DEVICE = 1, VT_HOST_AC_DEVICE_B = 2 };
 
 /* Tile visiting order of the int8 GEMM = the loop order of the Gemmini schedule it stands for.
  * The order affects cache reuse only; results are identical for all of them. */
@@ -53,23 +58,19 @@ enum {
   VT_RASTER_AUTO = 3      /* grouped order tuned for L2 reuse on B200                               */
 };
 
-/* int8 kernel variants.  VT_I8_AUTO picks the fastest verified one; the others exist so that each
- * design choice can be measured against its alternative:
- *   B_AS_STORED            one CTA per 128x256 tile, B read as stored, C written by TMA stores
- *   B_RELAYOUT             same, after re-laying B out as N x K on the device
- *   CTA_PAIR               two CTAs per 256x256 tile (tcgen05 cta_group::2), C written by TMA stores
- *   DIRECT_STORE           B_AS_STORED with plain 16-byte global stores for C
- *   CTA_PAIR_DIRECT_STORE  CTA_PAIR with plain 16-byte global stores for C
- *   CTA_PAIR_TWO_EPI_BUFFERS  CTA_PAIR with 5 operand stages and two store buffers per epilogue warp
- *                          (CTA_PAIR itself runs 6 stages and one buffer) */
+/* int8 kernel variants.  VT_I8_AUTO picks the fastest verified one (CTA_PAIR above 128 rows); the others
+ * exist so that a design choice can be measured against its alternative:
+ *   B_AS_STORED            one CTA per 128x256 tile
+ *   CTA_PAIR               two CTAs per 256x256 tile (tcgen05 cta_group::2); when the tiles do not fill a whole
+ *                          number of waves of CTA pairs, the K blocks of the last wave are shared by all pairs
+ *                          and the partial int32 sums are added by the pair that owns the tile (exact)
+ *   CTA_PAIR_WHOLE_TILES   the same kernel with every tile computed whole by one pair
+ * All read B as stored and write C by TMA stores. */
 enum {
   VT_I8_AUTO = 0,
   VT_I8_B_AS_STORED = 1,
-  VT_I8_B_RELAYOUT = 2,
-  VT_I8_CTA_PAIR = 3,
-  VT_I8_DIRECT_STORE = 4,
-  VT_I8_CTA_PAIR_DIRECT_STORE = 5,
-  VT_I8_CTA_PAIR_TWO_EPI_BUFFERS = 6
+  VT_I8_CTA_PAIR_WHOLE_TILES = 2,
+  VT_I8_CTA_PAIR = 3
 };
 
 /* fp32 kernel variants.
@@ -169,6 +170,17 @@ int vt_sgemm_skinny_static_scratch(int dev, const float* A, const float* B, floa
 /* Waits for `stream` (NULL = the library's stream) on `dev` and returns VT_ERR_DEVICE_WAIT if any
  * kernel since the last check gave up on a bounded wait, VT_ERR_CUDA on an asynchronous CUDA error. */
 int vt_sync(int dev, void* stream);
+
+/* TEST HOOK, not for production callers (it has no counterpart in the reference).  Every device-side wait of
+ * the kernels is bounded; this sets the bound for later launches on `dev` (`wait_limit_cycles` of the SM
+ * clock, <= 0 restores the default of about two seconds) and, with `i8_stop_fill` >= 0, makes the odd CTA of
+ * every int8 CTA pair stop feeding its operands at that ring fill, so that the waits for them run out, the
+ * kernel tears its pipeline down and returns, and vt_sync() reports VT_ERR_DEVICE_WAIT.  -1 turns it off. */
+int vt_test_set_wait_hooks(int dev, int64_t wait_limit_cycles, int i8_stop_fill);
+
+/* TEST HOOK.  Launches one small CTA on `stream` that waits, with the bound set above, for a barrier that
+ * nothing ever completes; the wait runs out and the kernel records its status and returns. */
+int vt_test_expire_wait(int dev, void* stream);
 
 /* Pinned host memory for VT_HOST calls. */
 void* vt_host_alloc(size_t bytes);

@@ -39,14 +39,14 @@ M, N, K = 80, 48, 64
 rng = np.random.default_rng(123)
 A = rng.integers(-128, 128, (M, K), dtype=np.int8)             # every rank can regenerate A ...
 B_true = rng.integers(-128, 128, (K, N), dtype=np.int8)
-B = torch.from_numpy(B_true.copy()) if rank == 0 else torch.zeros((K, N), dtype=torch.int8)
-sharding.replicate_from_rank0(B)                                 # ... but B only arrives by broadcast
-assert np.array_equal(B.numpy(), B_true)
+B_source = torch.from_numpy(B_true.copy()) if rank == 0 else None   # ... but B exists on rank 0 only
+B = torch.zeros((K, N), dtype=torch.int8)
 r0, r1 = sharding.row_shard(M, world, rank)
 C_rows = np.full((r1 - r0, N), -2**31, dtype=np.int32)
 def compute(a, b, c):
-    c[:] = go.matmul_exact(a, b, a.shape[0], N, K).astype(np.int32)
-sharding.sharded_gemm(compute, A[r0:r1], B.numpy(), C_rows)
+    c[:] = go.matmul_exact(a, b.numpy(), a.shape[0], N, K).astype(np.int32)
+sharding.run_row_sharded(compute, A[r0:r1], B, C_rows, B_source=B_source)
+assert np.array_equal(B.numpy(), B_true)                         # it arrived by the broadcast
 parts = [None] * world
 dist.all_gather_object(parts, (r0, r1, C_rows))
 C = np.concatenate([p[2] for p in sorted(parts, key=lambda p: p[0])])

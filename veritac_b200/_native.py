@@ -21,6 +21,7 @@ VT_ERR_PROGRAM = -6
 
 VT_HOST = 0
 VT_DEVICE = 1
+VT_HOST_AC_DEVICE_B = 2
 
 VT_RASTER_BASELINE = 0
 VT_RASTER_REUSE_B = 1
@@ -29,11 +30,8 @@ VT_RASTER_AUTO = 3
 
 VT_I8_AUTO = 0
 VT_I8_B_AS_STORED = 1
-VT_I8_B_RELAYOUT = 2
+VT_I8_CTA_PAIR_WHOLE_TILES = 2
 VT_I8_CTA_PAIR = 3
-VT_I8_DIRECT_STORE = 4
-VT_I8_CTA_PAIR_DIRECT_STORE = 5
-VT_I8_CTA_PAIR_TWO_EPI_BUFFERS = 6
 
 VT_SGEMM_AUTO = 0
 VT_SGEMM_TILE128 = 1
@@ -59,6 +57,8 @@ SIGNATURES = {
     "vt_sgemm": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_int, c_void_p]),
     "vt_sgemm_skinny_static_scratch": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,
                                                c_void_p]),
+    "vt_test_set_wait_hooks": (c_int, [c_int, c_int64, c_int]),
+    "vt_test_expire_wait": (c_int, [c_int, c_void_p]),
     "vt_sync": (c_int, [c_int, c_void_p]),
     "vt_host_alloc": (c_void_p, [c_size_t]),
     "vt_host_free": (c_int, [c_void_p]),
@@ -162,6 +162,16 @@ SKINNY_STATIC_SCRATCH_BYTES = 8 << 20
 def sgemm_skinny_static_scratch(A, B, C, M: int, N: int, K: int, *, dev: int = 0, stream: int = 0) -> None:
     """Skinny fp32 GEMM on device pointers that allocates nothing (see the header for the limits)."""
     check(lib().vt_sgemm_skinny_static_scratch(dev, _ptr(A), _ptr(B), _ptr(C), M, N, K, stream))
+
+
+def test_set_wait_hooks(dev: int = 0, wait_limit_cycles: int = 0, i8_stop_fill: int = -1) -> None:
+    """Test hook: bound of the device-side waits (0 = default) and the int8 pair kernel's induced stop."""
+    check(lib().vt_test_set_wait_hooks(dev, wait_limit_cycles, i8_stop_fill))
+
+
+def test_expire_wait(dev: int = 0, stream: int = 0) -> None:
+    """Test hook: enqueue one CTA whose bounded wait runs out."""
+    check(lib().vt_test_expire_wait(dev, stream))
 
 
 def sync(dev: int = 0, stream: int = 0) -> None:

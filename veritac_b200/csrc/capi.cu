@@ -49,15 +49,20 @@ cudaStream_t pick_stream(DeviceCtx* c, void* stream) { return stream ? static_ca
 
 // Host-pointer int8 GEMM, row blocks only: B and the first row block of A go in, then row blocks
 // are computed while the next block of A streams in and the previous block of C streams out.
-int i8gemm_from_host_rows(DeviceCtx* c, const int8_t* A, const int8_t* B, int32_t* C, int8_t* dA, int8_t* dB,
-                          int32_t* dC, int64_t M, int64_t N, int64_t K, int mode, int group, int variant) {
+// With `b_ready` given, B is `dB` itself, already on the device once the work queued on that stream is done.
+int i8gemm_from_host_rows(DeviceCtx* c, const int8_t* A, const int8_t* B, int32_t* C, int8_t* dA, const int8_t* dB,
+                          int32_t* dC, int64_t M, int64_t N, int64_t K, int mode, int group, int variant,
+                          const cudaStream_t* b_ready = nullptr) {
   // Row blocks: a multiple of 128 rows, at least 1024, about 8 blocks for large M.
   int64_t rows = ((M / 8 + 127) / 128) * 128;
   if (rows < 1024) rows = 1024;
-  if (variant == VT_I8_B_RELAYOUT) rows = M;  // the re-layout pass runs once per launch; keep one launch
   cudaEvent_t ev_b = c->ev[0], ev_in = c->ev[1], ev_k = c->ev[2];
-  VT_CUDA(cudaMemcpyAsync(dB, B, size_t(K) * N, cudaMemcpyHostToDevice, c->copy_in));
-  VT_CUDA(cudaEventRecord(ev_b, c->copy_in));
+  if (b_ready) {
+    VT_CUDA(cudaEventRecord(ev_b, *b_ready));
+  } else {
+    VT_CUDA(cudaMemcpyAsync(const_cast<int8_t*>(dB), B, size_t(K) * N, cudaMemcpyHostToDevice, c->copy_in));
+    VT_CUDA(cudaEventRecord(ev_b, c->copy_in));
+  }
   VT_CUDA(cudaStreamWaitEvent(c->stream, ev_b, 0));
   for (int64_t r0 = 0; r0 < M; r0 += rows) {
     const int64_t r = (M - r0 < rows) ? (M - r0) : rows;
@@ -139,16 +144,18 @@ int i8gemm_from_host_corner(DeviceCtx* c, const int8_t* A, const int8_t* B, int3
   return VT_OK;
 }
 
+// `b_ready`: B is a device pointer, valid once the work queued on that stream is done (the replicated operand of
+// a row-sharded job); A and C are host pointers either way.
 int i8gemm_from_host(DeviceCtx* c, const int8_t* A, const int8_t* B, int32_t* C, int64_t M, int64_t N, int64_t K,
-                     int mode, int group, int variant) {
+                     int mode, int group, int variant, const cudaStream_t* b_ready = nullptr) {
   int8_t* dA = static_cast<int8_t*>(ctx_workspace(c, 0, size_t(M) * K));
-  int8_t* dB = static_cast<int8_t*>(ctx_workspace(c, 1, size_t(K) * N));
+  int8_t* dB = b_ready ? nullptr : static_cast<int8_t*>(ctx_workspace(c, 1, size_t(K) * N));
   int32_t* dC = static_cast<int32_t*>(ctx_workspace(c, 2, size_t(M) * N * sizeof(int32_t)));
-  if (!dA || !dB || !dC) return VT_ERR_CUDA;
-  const bool pitched = variant == VT_I8_B_AS_STORED || variant == VT_I8_CTA_PAIR ||
-                       variant == VT_I8_CTA_PAIR_TWO_EPI_BUFFERS;
+  if (!dA || (!dB && !b_ready) || !dC) return VT_ERR_CUDA;
   int rc;
-  if (pitched && M >= 2048 && N >= 2048)
+  if (b_ready)
+    rc = i8gemm_from_host_rows(c, A, nullptr, C, dA, B, dC, M, N, K, mode, group, variant, b_ready);
+  else if (M >= 2048 && N >= 2048)
     rc = i8gemm_from_host_corner(c, A, B, C, dA, dB, dC, M, N, K, mode, group, variant);
   else
     rc = i8gemm_from_host_rows(c, A, B, C, dA, dB, dC, M, N, K, mode, group, variant);
@@ -209,7 +216,8 @@ int vt_i8gemm(int dev, const int8_t* A, const int8_t* B, int32_t* C, int64_t M, 
               int batch_rows, int variant, int where, void* stream) {
   clear_error_text();
   if (!A || !B || !C) return fail(VT_ERR_INVALID, "null operand");
-  if (where != VT_HOST && where != VT_DEVICE) return fail(VT_ERR_INVALID, "where must be VT_HOST or VT_DEVICE");
+  if (where != VT_HOST && where != VT_DEVICE && where != VT_HOST_AC_DEVICE_B)
+    return fail(VT_ERR_INVALID, "where must be VT_HOST, VT_DEVICE or VT_HOST_AC_DEVICE_B");
   if (raster < VT_RASTER_BASELINE || raster > VT_RASTER_AUTO) return fail(VT_ERR_INVALID, "unknown raster %d", raster);
   if (raster == VT_RASTER_BATCHED && (batch_rows < 1 || batch_rows > 64))
     return fail(VT_ERR_INVALID, "batch_rows must be in 1..64 (accumulator rows 16..1024)");
@@ -221,6 +229,10 @@ int vt_i8gemm(int dev, const int8_t* A, const int8_t* B, int32_t* C, int64_t M, 
   raster_for(raster, batch_rows, M, &mode, &group);
   variant = resolve_i8_variant(variant, M);
   if (where == VT_HOST) return i8gemm_from_host(c, A, B, C, M, N, K, mode, group, variant);
+  if (where == VT_HOST_AC_DEVICE_B) {
+    const cudaStream_t b_ready = pick_stream(c, stream);
+    return i8gemm_from_host(c, A, B, C, M, N, K, mode, group, variant, &b_ready);
+  }
   return launch_i8gemm(c, A, B, C, M, N, K, mode, group, variant, pick_stream(c, stream));
 }
 
@@ -453,6 +465,22 @@ int vt_sgemm(int dev, const float* A, const float* B, float* C, int64_t M, int64
     return ctx_check_status(c, s);
   }
   return VT_OK;
+}
+
+int vt_test_set_wait_hooks(int dev, int64_t wait_limit_cycles, int i8_stop_fill) {
+  clear_error_text();
+  DeviceCtx* c = ctx_for(dev);
+  if (!c) return VT_ERR_CUDA;
+  c->wait_limit_cycles = wait_limit_cycles > 0 ? (long long)wait_limit_cycles : 4000000000LL;
+  c->i8_stop_fill = i8_stop_fill < 0 ? -1 : i8_stop_fill;
+  return VT_OK;
+}
+
+int vt_test_expire_wait(int dev, void* stream) {
+  clear_error_text();
+  DeviceCtx* c = ctx_for(dev);
+  if (!c) return VT_ERR_CUDA;
+  return launch_expire_wait(c, pick_stream(c, stream));
 }
 
 int vt_sync(int dev, void* stream) {

@@ -9,16 +9,18 @@
 // Structure (one persistent CTA per SM, 192 threads):
 //   warp 0      TMA producer: 128x128 int8 tile of A (K-major, 128-byte swizzle) and a 128(K)x256(N)
 //               slab of B exactly as stored (N contiguous => "MN-major" operand, two 128-column boxes),
-//               into a 4-stage shared-memory ring guarded by full/empty mbarriers.
-//   warp 1      MMA issuer: one thread issues tcgen05.mma.kind::i8 (M=128, N=256, K=32) four times per
-//               stage into one of two 256-column TMEM accumulators; tcgen05.commit releases the stage
-//               and, after the last K block, publishes the accumulator.
-//   warps 2..5  epilogue: tcgen05.ld the accumulator quarter owned by (warp % 4), 16-byte stores of
-//               int32 rows to HBM, then hand the accumulator back so the next tile's MMAs overlap.
+//               into a shared-memory ring guarded by full/empty mbarriers.
+//   warp 1      MMA issuer: one thread issues tcgen05.mma.kind::i8 (K=32) four times per stage into one
+//               of two 256-column TMEM accumulators; tcgen05.commit releases the stage and, after the
+//               last K block, publishes the accumulator.
+//   warps 2..5  epilogue: tcgen05.ld the accumulator quarter owned by (warp % 4), stage it in swizzled
+//               shared memory, TMA-store int32 rows to HBM, then hand the accumulator back so the next
+//               tile's MMAs overlap.
 // Tiles are visited in the order the Gemmini schedule implies (row-major for baseline i,j,k,
 // column-major for reuse_b j,k,i, grouped for the batched B-reuse lowering); the order changes L2
 // reuse only, never results.
 #include "ptx_sm100.cuh"
+#include "i8_pair_sched.cuh"
 #include "runtime.h"
 #include "umma_tile.cuh"
 
@@ -45,13 +47,11 @@ struct PipeState {
 
 constexpr size_t SMEM_BYTES = 1024 + size_t(STAGES) * STAGE_BYTES + EPI_STAGING_BYTES + sizeof(PipeState);
 
-// kBT == false: tmB describes B as stored (inner = N, outer = K).
-// kBT == true : tmB describes B re-laid out as N x K (inner = K, outer = N).
-template <bool kBT, bool kTmaStore>
+// One CTA per 128 x 256 tile; tmB describes B as stored (inner = N, outer = K).
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 i8gemm_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                   const __grid_constant__ CUtensorMap tmC, int32_t* __restrict__ C, int M, int N, int K,
-                   TileRaster rs, int* __restrict__ status) {
+                   const __grid_constant__ CUtensorMap tmC, int M, int N, int K, TileRaster rs,
+                   int* __restrict__ status) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* staging = tiles + size_t(STAGES) * STAGE_BYTES;
@@ -77,7 +77,7 @@ i8gemm_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
     fence_proxy_async_smem();
     tma_prefetch_desc(&tmA);
     tma_prefetch_desc(&tmB);
-    if (kTmaStore) tma_prefetch_desc(&tmC);
+    tma_prefetch_desc(&tmC);
   }
   if (warp == 1) {
     tmem_alloc<1>(&ps->tmem_base, TMEM_COLS);
@@ -111,12 +111,8 @@ i8gemm_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
           uint8_t* b_s = a_s + A_STAGE_BYTES;
           mbar_arrive_expect_tx(full, STAGE_BYTES);
           tma_load_2d(a_s, &tmA, full, kb * BK, m0);
-          if constexpr (kBT) {
-            tma_load_2d(b_s, &tmB, full, kb * BK, n0);
-          } else {
-            tma_load_2d(b_s, &tmB, full, n0, kb * BK);
-            tma_load_2d(b_s + B_BOX_BYTES, &tmB, full, n0 + 128, kb * BK);
-          }
+          tma_load_2d(b_s, &tmB, full, n0, kb * BK);
+          tma_load_2d(b_s + B_BOX_BYTES, &tmB, full, n0 + 128, kb * BK);
           filled |= 1u << stage;
           fill_parity = (fill_parity & ~(1u << stage)) | (phase << stage);
           if (++stage == STAGES) {
@@ -146,7 +142,7 @@ i8gemm_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
   } else if (warp == 1) {
     // ------------------------------ MMA issuer ------------------------------
     if (lane == 0) {
-      constexpr uint32_t idesc = umma_instr_desc(UMMA_D_S32, UMMA_AB_S8, false, !kBT, BM, BN);
+      constexpr uint32_t idesc = umma_instr_desc(UMMA_D_S32, UMMA_AB_S8, false, true, BM, BN);
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
@@ -166,13 +162,12 @@ i8gemm_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
           const uint32_t b_addr = a_addr + A_STAGE_BYTES;
 #pragma unroll
           for (int kk = 0; kk < BK / UMMA_K; ++kk) {
-            // A (and re-laid-out B): K-major, rows of 128 bytes, 8-row groups 1024 bytes apart;
-            // a K step of 32 moves 32 bytes inside the swizzle row.
+            // A: K-major, rows of 128 bytes, 8-row groups 1024 bytes apart; a K step of 32 moves 32 bytes
+            // inside the swizzle row.
             const uint64_t a_desc = umma_smem_desc_sw128(a_addr + kk * UMMA_K, 16, 1024);
             // B as stored: N contiguous.  128-column blocks are one TMA box (16 KiB) apart,
             // 8-row K groups 1024 bytes apart; a K step of 32 rows moves 4096 bytes.
-            const uint64_t b_desc = kBT ? umma_smem_desc_sw128(b_addr + kk * UMMA_K, 16, 1024)
-                                        : umma_smem_desc_sw128(b_addr + kk * UMMA_K * 128, B_BOX_BYTES, 1024);
+            const uint64_t b_desc = umma_smem_desc_sw128(b_addr + kk * UMMA_K * 128, B_BOX_BYTES, 1024);
             umma_i8<1>(d_tmem, a_desc, b_desc, idesc, uint32_t((kb | kk) != 0));
           }
           umma_commit(&ps->empty[stage]);
@@ -201,14 +196,14 @@ i8gemm_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
       if (!__all_sync(0xffffffffu, ready)) break;
       tc_fence_after_sync();
       const uint32_t t_row = tmem_base + (uint32_t(q * 32) << 16) + uint32_t(acc * BN);
-      epilogue_warp_tile<kTmaStore>(t_row, &tmC, staging + q * 2 * EPI_BUF_BYTES, C, M, N, m0 + q * 32, n0, lane);
+      epilogue_warp_tile<2>(t_row, &tmC, staging + q * 2 * EPI_BUF_BYTES, M, N, m0 + q * 32, n0, lane);
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&ps->tmem_empty[acc]);
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1;
     }
-    if (kTmaStore && lane == 0) tma_store_wait_all<0>();   // C fully written before shared memory goes away
+    if (lane == 0) tma_store_wait_all<0>();   // C fully written before shared memory goes away
     __syncwarp();
   }
 
@@ -228,12 +223,16 @@ i8gemm_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
 //   * both producers signal the even CTA's "full" barrier (it expects both CTAs' bytes);
 //   * tcgen05.commit multicasts the "empty" and "accumulator full" arrivals to both CTAs;
 //   * both CTAs' epilogue warps arrive on the even CTA's "accumulator empty" barrier (8 arrivals).
+// The work list (i8_pair_sched.cuh) shares the K blocks of the last, partial wave of tiles between all
+// pairs: a pair may leave a partial accumulator of a tile in scratch memory (`partials`, one
+// 128 x 256 int32 slot per CTA) and set a flag per epilogue warp; the pair that owns the tile adds it.
 // ---------------------------------------------------------------------------------------------
 constexpr int P_A_BYTES = 128 * BK;                 // this CTA's 128 rows of A
 constexpr int P_B_BYTES = 128 * BK;                 // this CTA's 128 columns of B (one TMA box)
 constexpr int P_STAGE_BYTES = P_A_BYTES + P_B_BYTES;
+constexpr int P_STAGES = 6;
+constexpr size_t P_SLOT_UINT4 = size_t(128) * 256 * 4 / 16;   // one CTA's partial accumulator
 
-template <int P_STAGES>
 struct PairPipeState {
   uint64_t full[P_STAGES];
   uint64_t empty[P_STAGES];
@@ -241,34 +240,35 @@ struct PairPipeState {
   uint64_t tmem_empty[2];
   uint32_t tmem_base;
   int abort_word;
+  uint32_t peer_abort;     // the peer CTA's abort word, written by the peer before the closing cluster barrier
+  uint32_t fills_own;      // ring fills this CTA's producer issued
+  uint32_t fills_peer;     // even CTA only: ring fills the odd CTA's producer issued
 };
 
-constexpr size_t pair_smem_bytes(int stages, int bufs) {
-  return 1024 + size_t(stages) * P_STAGE_BYTES + size_t(4 * bufs) * EPI_BUF_BYTES + 256;
-}
+constexpr size_t PAIR_SMEM_BYTES = 1024 + size_t(P_STAGES) * P_STAGE_BYTES + size_t(4) * EPI_BUF_BYTES + 256;
+static_assert(sizeof(PairPipeState) <= 256, "pipeline state outgrew its shared-memory reserve");
 
-// P_STAGES operand stages and kBufs epilogue buffers per warp: (6, 1) and (5, 2) both fit in 227 KiB.
-template <bool kTmaStore, int P_STAGES, int kBufs>
+// `wait_limit`: cycles a device-side wait may take before the pair gives up (kWaitLimitCycles in production).
+// `stop_fill`: test hook, -1 in production; the odd CTA's producer stops before this ring fill as if its wait for the
+// stage had run out, so the fill never completes, the even CTA's wait for it runs out and the teardown runs.
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
 i8gemm_umma_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                        const __grid_constant__ CUtensorMap tmC, int32_t* __restrict__ C, int M, int N, int K,
-                        TileRaster rs, int* __restrict__ status) {
+                        const __grid_constant__ CUtensorMap tmC, int M, int N, int K, TileRaster rs, PairSched sched,
+                        uint4* __restrict__ partials, int* __restrict__ flags, int* __restrict__ status,
+                        long long wait_limit, int stop_fill) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* staging = tiles + size_t(P_STAGES) * P_STAGE_BYTES;
   // C is written once and never read here: its lines should be the first to leave L2, so that A and B
   // (128 MiB at 8192^3, about the size of L2) stay (measured +0.5 %).
   const uint64_t store_policy = l2_policy_evict_first();
-  PairPipeState<P_STAGES>* ps = reinterpret_cast<PairPipeState<P_STAGES>*>(staging + 4 * kBufs * EPI_BUF_BYTES);
+  PairPipeState* ps = reinterpret_cast<PairPipeState*>(staging + 4 * EPI_BUF_BYTES);
   volatile int* abort_word = &ps->abort_word;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const uint32_t rank = cluster_cta_rank();          // 0 = even CTA (issues the MMAs), 1 = its peer
   const int pair = blockIdx.x >> 1;
-  const int num_pairs = gridDim.x >> 1;
-  const int num_tiles = rs.mt * rs.nt;               // 256 x 256 tiles
-  const int kblocks = (K + BK - 1) / BK;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < P_STAGES; ++s) {
@@ -280,11 +280,14 @@ i8gemm_umma_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
       mbar_init(&ps->tmem_empty[b], 8);              // 4 epilogue warps of each CTA
     }
     ps->abort_word = 0;
+    ps->peer_abort = 0;
+    ps->fills_own = 0;
+    ps->fills_peer = 0;
     fence_mbar_init();
     fence_proxy_async_smem();
     tma_prefetch_desc(&tmA);
     tma_prefetch_desc(&tmB);
-    if (kTmaStore) tma_prefetch_desc(&tmC);
+    tma_prefetch_desc(&tmC);
   }
   if (warp == 1) {
     tmem_alloc<2>(&ps->tmem_base, TMEM_COLS);
@@ -294,8 +297,8 @@ i8gemm_umma_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
   cluster_sync_all();                                // peer barriers exist before anything signals them
   tc_fence_after_sync();
   const uint32_t tmem_base = ps->tmem_base;
-  // The set-up above may overlap the end of the kernel before this one on the stream; operands, C and the
-  // status word are not touched before that kernel has completed.
+  // The set-up above may overlap the end of the kernel before this one on the stream; operands, C, scratch,
+  // flags and the status word are not touched before that kernel has completed.
   grid_dependency_wait();
   grid_launch_dependents();
 
@@ -304,14 +307,20 @@ i8gemm_umma_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
     if (lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
-      uint32_t filled = 0, fill_parity = 0;
+      uint32_t fills = 0;
       bool ok = true;
-      for (int t = pair; t < num_tiles && ok; t += num_pairs) {
+      PairItem it;
+      for (int i = 0; ok && pair_item(sched, pair, i, it); ++i) {
         int mi, ni;
-        tile_coords(rs, t, mi, ni);
+        tile_coords(rs, it.tile, mi, ni);
         const int m0 = mi * 256 + int(rank) * 128, n0 = ni * 256 + int(rank) * 128;
-        for (int kb = 0; kb < kblocks; ++kb) {
-          if (!mbar_wait(&ps->empty[stage], phase ^ 1, abort_word, KSTAT_WAIT_EXPIRED_PRODUCER)) {
+        for (int kb = it.kb0; kb < it.kb1; ++kb) {
+          if (!mbar_wait(&ps->empty[stage], phase ^ 1, abort_word, KSTAT_WAIT_EXPIRED_PRODUCER, wait_limit)) {
+            ok = false;
+            break;
+          }
+          if (rank == 1 && int(fills) == stop_fill) {
+            atomicCAS(const_cast<int*>(abort_word), 0, KSTAT_WAIT_EXPIRED_PRODUCER);
             ok = false;
             break;
           }
@@ -321,8 +330,7 @@ i8gemm_umma_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
           const uint32_t full_even = mapa_shared(smem_u32(&ps->full[stage]), 0);
           tma_load_2d_pair(a_s, &tmA, full_even, kb * BK, m0);
           tma_load_2d_pair(b_s, &tmB, full_even, n0, kb * BK);
-          filled |= 1u << stage;
-          fill_parity = (fill_parity & ~(1u << stage)) | (phase << stage);
+          ++fills;
           if (++stage == P_STAGES) {
             stage = 0;
             phase ^= 1;
@@ -330,16 +338,19 @@ i8gemm_umma_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
         }
       }
       if (ok) {
+        // Every stage released => every MMA that reads shared memory has retired before the ring is reused by
+        // the last epilogue or given back.
         for (int s = 0; s < P_STAGES; ++s) {
-          if (!mbar_wait(&ps->empty[stage], phase ^ 1, abort_word, KSTAT_WAIT_EXPIRED_PRODUCER)) break;
+          if (!mbar_wait(&ps->empty[stage], phase ^ 1, abort_word, KSTAT_WAIT_EXPIRED_PRODUCER, wait_limit)) break;
           if (++stage == P_STAGES) {
             stage = 0;
             phase ^= 1;
           }
         }
       }
-      (void)filled;
-      (void)fill_parity;
+      // How far this producer got, for the teardown of a pair that gave up (see the end of the kernel).
+      if (rank == 0) ps->fills_own = fills;
+      else st_shared_cluster_u32(mapa_shared(smem_u32(&ps->fills_peer), 0), fills);
     }
     __syncwarp();
   } else if (warp == 1) {
@@ -351,12 +362,13 @@ i8gemm_umma_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
-      for (int t = pair; t < num_tiles && ok; t += num_pairs) {
-        if (!mbar_wait<true>(&ps->tmem_empty[acc], acc_phase ^ 1, abort_word, KSTAT_WAIT_EXPIRED_MMA)) break;
+      PairItem it;
+      for (int i = 0; ok && pair_item(sched, pair, i, it); ++i) {
+        if (!mbar_wait<true>(&ps->tmem_empty[acc], acc_phase ^ 1, abort_word, KSTAT_WAIT_EXPIRED_MMA, wait_limit)) break;
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + uint32_t(acc * BN);
-        for (int kb = 0; kb < kblocks; ++kb) {
-          if (!mbar_wait<true>(&ps->full[stage], phase, abort_word, KSTAT_WAIT_EXPIRED_MMA)) {
+        for (int kb = it.kb0; kb < it.kb1; ++kb) {
+          if (!mbar_wait<true>(&ps->full[stage], phase, abort_word, KSTAT_WAIT_EXPIRED_MMA, wait_limit)) {
             ok = false;
             break;
           }
@@ -367,7 +379,7 @@ i8gemm_umma_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
           for (int kk = 0; kk < BK / UMMA_K; ++kk) {
             const uint64_t a_desc = umma_smem_desc_sw128(a_addr + kk * UMMA_K, 16, 1024);
             const uint64_t b_desc = umma_smem_desc_sw128(b_addr + kk * UMMA_K * 128, P_B_BYTES, 1024);
-            umma_i8<2>(d_tmem, a_desc, b_desc, idesc, uint32_t((kb | kk) != 0));
+            umma_i8<2>(d_tmem, a_desc, b_desc, idesc, uint32_t(kb != it.kb0 || kk != 0));
           }
           umma_commit_pair(&ps->empty[stage], 3);
           if (++stage == P_STAGES) {
@@ -387,68 +399,76 @@ i8gemm_umma_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
     const int q = warp & 3;
     int acc = 0;
     uint32_t acc_phase = 0;
-    for (int t = pair; t < num_tiles; t += num_pairs) {
+    // This warp's part of a CTA's scratch slot and its flag: pair p, CTA rank r -> slot 2p + r.
+    const size_t warp_off = size_t(q) * (P_SLOT_UINT4 / 4) + size_t(lane);
+    uint4* my_slot = partials + (size_t(pair) * 2 + rank) * P_SLOT_UINT4 + warp_off;
+    int* my_flag = flags + (pair * 2 + int(rank)) * 4 + q;
+    PairItem it, next;
+    bool have = pair_item(sched, pair, 0, it);
+    for (int i = 0; have; ++i) {
+      const bool more = pair_item(sched, pair, i + 1, next);
       int mi, ni;
-      tile_coords(rs, t, mi, ni);
+      tile_coords(rs, it.tile, mi, ni);
       const int m0 = mi * 256 + int(rank) * 128, n0 = ni * 256;
-      const bool ready = mbar_wait<true>(&ps->tmem_full[acc], acc_phase, abort_word, KSTAT_WAIT_EXPIRED_EPILOGUE);
+      const bool ready = mbar_wait<true>(&ps->tmem_full[acc], acc_phase, abort_word, KSTAT_WAIT_EXPIRED_EPILOGUE, wait_limit);
       if (!__all_sync(0xffffffffu, ready)) break;
       tc_fence_after_sync();
       const uint32_t t_row = tmem_base + (uint32_t(q * 32) << 16) + uint32_t(acc * BN);
-      // The last tile's epilogue overlaps nothing, and by now every MMA of this pair has read its operands and
-      // no load is in flight: the operand ring serves as one store buffer per column chunk (4 x 32 KiB).
-      uint8_t* wide = (kTmaStore && t + num_pairs >= num_tiles) ? tiles + size_t(q) * 8 * EPI_BUF_BYTES : nullptr;
-      epilogue_warp_tile<kTmaStore, kBufs>(t_row, &tmC, staging + q * kBufs * EPI_BUF_BYTES, C, M, N, m0 + q * 32, n0, lane,
-                                           store_policy, wide);
+      if (it.kind == PAIR_ITEM_PARTIAL) {
+        epilogue_warp_partial(t_row, my_slot);
+        __threadfence();
+        __syncwarp();
+        if (lane == 0) st_release_gpu(my_flag, 1);
+      } else {
+        const uint4* merge = nullptr;
+        if (it.ncontrib > 0) {
+          // Same warp, same lane of the contributors' CTAs of this rank: their flags first, then their sums.
+          bool there = true;
+          for (int x = 0; x < it.ncontrib && there; ++x)
+            there = flag_wait(flags + ((it.contrib0 + x) * 2 + int(rank)) * 4 + q, abort_word, KSTAT_WAIT_EXPIRED_PEER,
+                              wait_limit);
+          if (!__all_sync(0xffffffffu, there)) break;
+          merge = partials + (size_t(it.contrib0) * 2 + rank) * P_SLOT_UINT4 + warp_off;
+        }
+        // The last item's epilogue overlaps nothing, and by now every MMA of this pair has read its operands and
+        // no load is in flight: the operand ring serves as one store buffer per column chunk (4 x 32 KiB).
+        uint8_t* wide = more ? nullptr : tiles + size_t(q) * 8 * EPI_BUF_BYTES;
+        epilogue_warp_tile<1>(t_row, &tmC, staging + q * EPI_BUF_BYTES, M, N, m0 + q * 32, n0, lane, store_policy, wide,
+                              merge, it.ncontrib, 2 * P_SLOT_UINT4);
+        if (it.ncontrib > 0) {
+          __syncwarp();
+          if (lane == 0)
+            for (int x = 0; x < it.ncontrib; ++x) flags[((it.contrib0 + x) * 2 + int(rank)) * 4 + q] = 0;   // for the next launch
+        }
+      }
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive_remote(&ps->tmem_empty[acc], 0);
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1;
+      it = next;
+      have = more;
     }
-    if (kTmaStore && lane == 0) tma_store_wait_all<0>();
+    if (lane == 0) tma_store_wait_all<0>();
     __syncwarp();
   }
 
-  // Neither CTA may free TMEM or leave while its peer's MMAs, commits or remote arrivals can still
-  // touch it.
+  // Neither CTA may free TMEM or leave while its peer's MMAs, commits or remote arrivals can still touch it.
+  // The two CTAs also tell each other whether they gave up: a pair that did has to make sure that no copy is
+  // still on its way into either CTA's shared memory before the CTAs go.
   tc_fence_before_sync();
+  __syncthreads();                                   // every role of this CTA is done: the abort word is final
+  if (threadIdx.x == 0)
+    st_shared_cluster_u32(mapa_shared(smem_u32(&ps->peer_abort), rank ^ 1u), uint32_t(ps->abort_word));
   cluster_sync_all();
+  if (ps->abort_word != 0 || ps->peer_abort != 0) {  // the same verdict in both CTAs
+    if (rank == 0 && threadIdx.x == 0 &&
+        !pair_drain_loads<P_STAGES>(ps->full, ps->fills_own, ps->fills_peer, P_STAGE_BYTES))
+      atomicCAS(&ps->abort_word, 0, KSTAT_WAIT_EXPIRED_DRAIN);
+    cluster_sync_all();
+  }
   if (warp == 1) tmem_dealloc<2>(tmem_base, TMEM_COLS);
   if (threadIdx.x == 0 && ps->abort_word != 0) atomicCAS(status, 0, ps->abort_word);
-}
-
-// B[K,N] -> Bt[N,K], 64x64 byte tiles through shared memory (only the K-major-B variant uses it).
-__global__ void __launch_bounds__(256) i8_transpose_kernel(const int8_t* __restrict__ B, int8_t* __restrict__ Bt,
-                                                           int K, int N) {
-  __shared__ int8_t tile[64][65];
-  const int n0 = blockIdx.x * 64, k0 = blockIdx.y * 64;
-  for (int i = threadIdx.x; i < 64 * 64; i += 256) {
-    const int r = i >> 6, c = i & 63;
-    const int k = k0 + r, n = n0 + c;
-    tile[r][c] = (k < K && n < N) ? B[size_t(k) * N + n] : int8_t(0);
-  }
-  __syncthreads();
-  for (int i = threadIdx.x; i < 64 * 64; i += 256) {
-    const int r = i >> 6, c = i & 63;  // r: n within tile, c: k within tile
-    const int n = n0 + r, k = k0 + c;
-    if (n < N && k < K) Bt[size_t(n) * K + k] = tile[c][r];
-  }
-}
-
-template <typename KernelT>
-int launch_with_smem(DeviceCtx* c, uint32_t attr_bit, KernelT kernel, size_t smem, int grid, cudaStream_t s,
-                     const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC, int32_t* C, int M,
-                     int N, int K, const TileRaster& rs) {
-  if (!(c->func_attr_mask & attr_bit)) {
-    VT_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
-    c->func_attr_mask |= attr_bit;
-  }
-  VT_CUDA(launch_overlapped(kernel, unsigned(grid), unsigned(NUM_THREADS), smem, s, tmA, tmB, tmC, C, M, N, K, rs,
-                            c->status));
-  count_launch();
-  VT_CUDA(cudaGetLastError());
-  return VT_OK;
 }
 
 }  // namespace
@@ -458,16 +478,12 @@ int launch_i8gemm(DeviceCtx* c, const int8_t* A, const int8_t* B, int32_t* C, in
   if (ldb == 0) ldb = N;
   if (ldc == 0) ldc = N;
   if (ldb < N || ldc < N || (ldb & 15) || (ldc & 3)) return fail(VT_ERR_INVALID, "bad row pitch for B or C");
-  if ((ldb != N || ldc != N) && variant != VT_I8_B_AS_STORED && variant != VT_I8_CTA_PAIR &&
-      variant != VT_I8_CTA_PAIR_TWO_EPI_BUFFERS)
-    return fail(VT_ERR_UNSUPPORTED, "i8gemm variant %d takes no row pitch", variant);
-  if (variant < VT_I8_B_AS_STORED || variant > VT_I8_CTA_PAIR_TWO_EPI_BUFFERS)
+  if (variant < VT_I8_B_AS_STORED || variant > VT_I8_CTA_PAIR)
     return fail(VT_ERR_UNSUPPORTED, "i8gemm variant %d is not built", variant);
   if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(C)) & 15)
     return fail(VT_ERR_INVALID, "i8gemm operands must be 16-byte aligned");
   if (raster_mode < 0 || raster_mode > 2) return fail(VT_ERR_INVALID, "raster mode %d out of range", raster_mode);
-  const bool pair = variant == VT_I8_CTA_PAIR || variant == VT_I8_CTA_PAIR_DIRECT_STORE ||
-                    variant == VT_I8_CTA_PAIR_TWO_EPI_BUFFERS;
+  const bool pair = variant != VT_I8_B_AS_STORED;
   const int tile_m = pair ? 256 : BM;
 
   TileRaster rs;
@@ -484,39 +500,38 @@ int launch_i8gemm(DeviceCtx* c, const int8_t* A, const int8_t* B, int32_t* C, in
   if (rc) return rc;
   rc = encode_tmap_2d(&tmC, CU_TENSOR_MAP_DATA_TYPE_INT32, 4, C, uint64_t(N), uint64_t(M), uint64_t(ldc) * 4, 32, 32);
   if (rc) return rc;
-  const int iM = int(M), iN = int(N), iK = int(K);
-
-  if (variant == VT_I8_B_RELAYOUT) {
-    int8_t* Bt = static_cast<int8_t*>(ctx_workspace(c, 3, size_t(N) * size_t(K)));
-    if (!Bt) return VT_ERR_CUDA;
-    dim3 tg(unsigned((N + 63) / 64), unsigned((K + 63) / 64));
-    i8_transpose_kernel<<<tg, 256, 0, s>>>(B, Bt, iK, iN);
-    count_launch();
-    rc = encode_tmap_2d(&tmB, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, Bt, uint64_t(K), uint64_t(N), uint64_t(K), BK, BN);
-    if (rc) return rc;
-    const int grid = int(tiles < c->sm_count ? tiles : c->sm_count);
-    return launch_with_smem(c, 2u, i8gemm_umma_kernel<true, true>, SMEM_BYTES, grid, s, tmA, tmB, tmC, C, iM, iN, iK, rs);
-  }
   rc = encode_tmap_2d(&tmB, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, B, uint64_t(N), uint64_t(K), uint64_t(ldb), 128, BK);
   if (rc) return rc;
+  const int iM = int(M), iN = int(N), iK = int(K);
+
   if (!pair) {
     const int grid = int(tiles < c->sm_count ? tiles : c->sm_count);
-    if (variant == VT_I8_B_AS_STORED)
-      return launch_with_smem(c, 1u, i8gemm_umma_kernel<false, true>, SMEM_BYTES, grid, s, tmA, tmB, tmC, C, iM, iN,
-                              iK, rs);
-    return launch_with_smem(c, 8u, i8gemm_umma_kernel<false, false>, SMEM_BYTES, grid, s, tmA, tmB, tmC, C, iM, iN,
-                            iK, rs);
+    if (!(c->func_attr_mask & 1u)) {
+      VT_CUDA(cudaFuncSetAttribute(i8gemm_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(SMEM_BYTES)));
+      c->func_attr_mask |= 1u;
+    }
+    VT_CUDA(launch_overlapped(i8gemm_umma_kernel, unsigned(grid), unsigned(NUM_THREADS), SMEM_BYTES, s, tmA, tmB, tmC, iM,
+                              iN, iK, rs, c->status));
+    count_launch();
+    VT_CUDA(cudaGetLastError());
+    return VT_OK;
   }
+  // The tail is shared only when all pairs of the device take part; otherwise one pair per tile, whole tiles.
   const int max_pairs = c->sm_count / 2;
-  const int grid = 2 * int(tiles < max_pairs ? tiles : max_pairs);
-  if (variant == VT_I8_CTA_PAIR)
-    return launch_with_smem(c, 4u, i8gemm_umma_pair_kernel<true, 6, 1>, pair_smem_bytes(6, 1), grid, s, tmA, tmB, tmC,
-                            C, iM, iN, iK, rs);
-  if (variant == VT_I8_CTA_PAIR_TWO_EPI_BUFFERS)
-    return launch_with_smem(c, 64u, i8gemm_umma_pair_kernel<true, 5, 2>, pair_smem_bytes(5, 2), grid, s, tmA, tmB, tmC,
-                            C, iM, iN, iK, rs);
-  return launch_with_smem(c, 16u, i8gemm_umma_pair_kernel<false, 6, 1>, pair_smem_bytes(6, 1), grid, s, tmA, tmB, tmC,
-                          C, iM, iN, iK, rs);
+  const int kblocks = int((K + BK - 1) / BK);
+  PairSched sched = make_pair_sched(max_pairs, int(tiles), kblocks, variant == VT_I8_CTA_PAIR);
+  if (sched.tail == 0) sched = make_pair_sched(int(tiles < max_pairs ? tiles : max_pairs), int(tiles), kblocks, false);
+  if (!(c->func_attr_mask & 4u)) {
+    VT_CUDA(cudaFuncSetAttribute(i8gemm_umma_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 int(PAIR_SMEM_BYTES)));
+    c->func_attr_mask |= 4u;
+  }
+  VT_CUDA(launch_overlapped(i8gemm_umma_pair_kernel, unsigned(2 * sched.pairs), unsigned(NUM_THREADS), PAIR_SMEM_BYTES, s,
+                            tmA, tmB, tmC, iM, iN, iK, rs, sched, static_cast<uint4*>(c->i8_partials), c->i8_flags,
+                            c->status, c->wait_limit_cycles, c->i8_stop_fill));
+  count_launch();
+  VT_CUDA(cudaGetLastError());
+  return VT_OK;
 }
 
 }  // namespace vt

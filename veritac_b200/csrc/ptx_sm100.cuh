@@ -18,6 +18,7 @@ enum : int {
   KSTAT_WAIT_EXPIRED_MMA = 102,       // MMA issuer gave up on a "full"/"tmem empty" barrier
   KSTAT_WAIT_EXPIRED_EPILOGUE = 103,  // epilogue gave up on a "tmem full" barrier
   KSTAT_WAIT_EXPIRED_DRAIN = 104,     // teardown gave up waiting for copies in flight
+  KSTAT_WAIT_EXPIRED_PEER = 105,      // gave up on a flag in global memory that another CTA sets
 };
 
 // ~2 s at 2 GHz; a healthy pipeline waits microseconds.
@@ -94,7 +95,8 @@ __device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t pa
 // Bounded wait.  Returns false when the CTA is aborting (this wait expired, or another role's
 // did).  `abort_word` lives in shared memory; `code` is what gets recorded on expiry.
 template <bool kCluster = false>
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_word, int code) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_word, int code,
+                                          long long limit_cycles = kWaitLimitCycles) {
   long long t0 = 0;
 #pragma unroll 1
   for (uint32_t spin = 0;; ++spin) {
@@ -105,7 +107,46 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
       const long long now = clock64();
       if (t0 == 0) {
         t0 = now;
-      } else if (now - t0 > kWaitLimitCycles) {
+      } else if (now - t0 > limit_cycles) {
+        atomicCAS(const_cast<int*>(abort_word), 0, code);
+        return false;
+      }
+    }
+  }
+}
+
+// Accounts for `bytes` of transactions on `bar` that no copy will ever deliver (teardown bookkeeping).
+__device__ __forceinline__ void mbar_complete_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.complete_tx.relaxed.cta.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+               : "memory");
+}
+// 32-bit store into the shared memory of a CTA of this cluster (address from mapa_shared).
+__device__ __forceinline__ void st_shared_cluster_u32(uint32_t cluster_addr, uint32_t v) {
+  asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
+}
+
+// Flags in global memory that one CTA sets and another waits for.
+__device__ __forceinline__ void st_release_gpu(int* p, int v) {
+  asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ int ld_acquire_gpu(const int* p) {
+  int v;
+  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+// Bounded wait for a non-zero flag; same abort protocol as mbar_wait.
+__device__ __forceinline__ bool flag_wait(const int* flag, volatile int* abort_word, int code,
+                                          long long limit_cycles = kWaitLimitCycles) {
+  long long t0 = 0;
+#pragma unroll 1
+  for (uint32_t spin = 0;; ++spin) {
+    if (ld_acquire_gpu(flag) != 0) return true;
+    if ((spin & 0x3f) == 0x3f) {
+      if (*abort_word != 0) return false;
+      const long long now = clock64();
+      if (t0 == 0) {
+        t0 = now;
+      } else if (now - t0 > limit_cycles) {
         atomicCAS(const_cast<int*>(abort_word), 0, code);
         return false;
       }
@@ -371,6 +412,13 @@ __device__ __forceinline__ uint32_t cluster_cta_rank() {
 }
 __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+// 16-byte load that bypasses L1 (data another SM wrote during this kernel).
+__device__ __forceinline__ uint4 ld_global_cg_v4(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.cg.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
 }
 
 // Streaming 16-byte store (C is written once and never re-read by the kernel).

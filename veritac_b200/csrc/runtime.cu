@@ -6,6 +6,7 @@
 #include <cstdio>
 #include <cstring>
 #include <mutex>
+#include <new>
 
 #include "ptx_sm100.cuh"
 
@@ -52,9 +53,9 @@ DeviceCtx* ctx_for(int dev) {
     return nullptr;
   }
   DeviceCtx* c = &g_ctx[dev];
-  if (c->ready) return c;
+  if (c->ready.load(std::memory_order_acquire)) return c;
   std::lock_guard<std::mutex> lock(g_mu);
-  if (c->ready) return c;
+  if (c->ready.load(std::memory_order_acquire)) return c;
   cudaDeviceProp prop;
   e = cudaGetDeviceProperties(&prop, dev);
   if (e != cudaSuccess) {
@@ -85,6 +86,10 @@ DeviceCtx* ctx_for(int dev) {
   CTX_TRY(cudaMallocHost(&c->status_host, sizeof(int)));
   CTX_TRY(cudaMalloc(&c->tickets, kTicketCount * sizeof(int)));
   CTX_TRY(cudaMemset(c->tickets, 0, kTicketCount * sizeof(int)));
+  c->i8_flag_count = c->sm_count * 4;
+  CTX_TRY(cudaMalloc(&c->i8_flags, size_t(c->i8_flag_count) * sizeof(int)));
+  CTX_TRY(cudaMemset(c->i8_flags, 0, size_t(c->i8_flag_count) * sizeof(int)));
+  CTX_TRY(cudaMalloc(&c->i8_partials, size_t(c->sm_count) * 128 * 256 * sizeof(int32_t)));
   for (auto& ev : c->ev) CTX_TRY(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
 #undef CTX_TRY
   if (!g_encode) {
@@ -97,7 +102,7 @@ DeviceCtx* ctx_for(int dev) {
     }
     g_encode = reinterpret_cast<EncodeTiledFn>(fn);
   }
-  c->ready = true;
+  c->ready.store(true, std::memory_order_release);
   return c;
 }
 
@@ -125,6 +130,7 @@ int ctx_check_status(DeviceCtx* c, cudaStream_t s) {
   if (st != KSTAT_OK) {
     VT_CUDA(cudaMemsetAsync(c->status, 0, sizeof(int), s));
     VT_CUDA(cudaMemsetAsync(c->tickets, 0, kTicketCount * sizeof(int), s));   // an aborted kernel may have left counts behind
+    VT_CUDA(cudaMemsetAsync(c->i8_flags, 0, size_t(c->i8_flag_count) * sizeof(int), s));
     VT_CUDA(cudaStreamSynchronize(s));
     return fail(VT_ERR_DEVICE_WAIT, "a kernel gave up on a bounded device-side wait (status %d)", st);
   }
@@ -143,13 +149,43 @@ void ctx_destroy_all() {
     if (c->status) cudaFree(c->status);
     if (c->status_host) cudaFreeHost(c->status_host);
     if (c->tickets) cudaFree(c->tickets);
+    if (c->i8_flags) cudaFree(c->i8_flags);
+    if (c->i8_partials) cudaFree(c->i8_partials);
     for (auto& ev : c->ev)
       if (ev) cudaEventDestroy(ev);
     if (c->stream) cudaStreamDestroy(c->stream);
     if (c->copy_in) cudaStreamDestroy(c->copy_in);
     if (c->copy_out) cudaStreamDestroy(c->copy_out);
-    *c = DeviceCtx();
+    c->ready.store(false, std::memory_order_release);
+    c->~DeviceCtx();
+    new (c) DeviceCtx();
   }
+}
+
+namespace {
+// One warp waits for a barrier that expects an arrival nobody makes.  The wait is the production one
+// (mbar_wait): it gives up after `limit` cycles, records its code in the abort word, and the kernel passes
+// that on to the device status word exactly as the GEMM kernels do.
+__global__ void __launch_bounds__(32) expire_wait_kernel(int* __restrict__ status, long long limit) {
+  __shared__ uint64_t bar;
+  __shared__ int abort_word;
+  if (threadIdx.x == 0) {
+    mbar_init(&bar, 1);
+    abort_word = 0;
+    fence_mbar_init();
+  }
+  __syncwarp();
+  const bool done = mbar_wait(&bar, 0, &abort_word, KSTAT_WAIT_EXPIRED_MMA, limit);
+  __syncwarp();
+  if (threadIdx.x == 0 && !done && abort_word != 0) atomicCAS(status, 0, abort_word);
+}
+}  // namespace
+
+int launch_expire_wait(DeviceCtx* c, cudaStream_t s) {
+  expire_wait_kernel<<<1, 32, 0, s>>>(c->status, c->wait_limit_cycles);
+  count_launch();
+  VT_CUDA(cudaGetLastError());
+  return VT_OK;
 }
 
 int encode_tmap_2d(CUtensorMap* out, CUtensorMapDataType dtype, int elem_bytes, const void* base, uint64_t inner,

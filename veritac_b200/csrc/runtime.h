@@ -8,6 +8,8 @@
 #include <stddef.h>
 #include <stdint.h>
 
+#include <atomic>
+
 #include "../../include/veritac_b200.h"
 
 namespace vt {
@@ -16,7 +18,7 @@ constexpr int kTicketCount = 4096;
 
 struct DeviceCtx {
   int dev = -1;
-  bool ready = false;
+  std::atomic<bool> ready{false};
   int sm_count = 0;
   size_t smem_optin = 0;
   cudaStream_t stream = nullptr;       // library-owned stream used when the caller passes none
@@ -25,6 +27,15 @@ struct DeviceCtx {
   int* status = nullptr;               // device word kernels write a KSTAT_* code into
   int* status_host = nullptr;          // pinned mirror
   int* tickets = nullptr;              // kTicketCount zeroed counters (per-slab arrival counts of the skinny kernel)
+  // int8 CTA-pair kernel: one 128 x 256 int32 partial accumulator per CTA and one flag per epilogue warp (zero
+  // between launches), sized for one CTA per SM at context creation so that no launch ever allocates
+  void* i8_partials = nullptr;
+  int* i8_flags = nullptr;
+  int i8_flag_count = 0;
+  // Test hooks (vt_test_set_wait_hooks): how long a device-side wait may take, and the ring fill at which the odd
+  // CTA of every int8 pair stops (-1: never).
+  long long wait_limit_cycles = 4000000000LL;
+  int i8_stop_fill = -1;
   // grow-only device workspace for host-pointer calls and operand re-layouts
   void* ws[4] = {nullptr, nullptr, nullptr, nullptr};
   size_t ws_bytes[4] = {0, 0, 0, 0};
@@ -81,12 +92,13 @@ cudaError_t launch_overlapped(void (*kernel)(KArgs...), unsigned grid, unsigned 
 
 // ---- kernel launchers (device pointers only) ------------------------------------------------
 // raster_mode: 0 row-major tiles, 1 column-major tiles, 2 grouped (group = tile-rows per sweep).
-// variant: VT_I8_B_AS_STORED (B consumed as K x N row-major, an MN-major operand),
-// VT_I8_B_RELAYOUT (B re-laid out to N x K first, a K-major operand), VT_I8_CTA_PAIR.
-// ldb / ldc: row pitch of B and C in elements when they are sub-blocks of wider matrices (0 = N);
-// only the variants that write C through TMA stores and read B as stored take a pitch.
+// variant: VT_I8_B_AS_STORED (one CTA per 128 x 256 tile), VT_I8_CTA_PAIR (two CTAs per 256 x 256 tile, the last
+// partial wave of tiles shared along K), VT_I8_CTA_PAIR_WHOLE_TILES (the same without the sharing).
+// ldb / ldc: row pitch of B and C in elements when they are sub-blocks of wider matrices (0 = N).
 int launch_i8gemm(DeviceCtx* c, const int8_t* A, const int8_t* B, int32_t* C, int64_t M, int64_t N, int64_t K,
                   int raster_mode, int group, int variant, cudaStream_t s, int64_t ldb = 0, int64_t ldc = 0);
+// Test hook: one CTA whose bounded wait runs out (see vt_test_expire_wait).
+int launch_expire_wait(DeviceCtx* c, cudaStream_t s);
 int launch_sgemm(DeviceCtx* c, const float* A, const float* B, float* C, int64_t M, int64_t N, int64_t K,
                  int variant, cudaStream_t s);
 double sgemm_tile_choice(const float* A, const float* B, const float* C, int64_t M, int64_t N, int64_t K, int sm_count,

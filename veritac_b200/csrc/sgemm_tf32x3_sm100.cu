@@ -41,6 +41,9 @@ struct TfPipeState {
   uint64_t tmem_empty[2];
   uint32_t tmem_base;
   int abort_word;
+  uint32_t peer_abort;     // the peer CTA's abort word, written by the peer before the closing cluster barrier
+  uint32_t fills_own;      // ring fills this CTA's producer issued
+  uint32_t fills_peer;     // even CTA only: ring fills the odd CTA's producer issued
 };
 
 constexpr size_t T_SMEM_BYTES = 1024 + size_t(T_STAGES) * T_STAGE_BYTES + EPI_STAGING_BYTES + sizeof(TfPipeState);
@@ -97,6 +100,9 @@ sgemm_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_
       mbar_init(&ps->tmem_empty[b], 16);   // 8 epilogue warps of each CTA
     }
     ps->abort_word = 0;
+    ps->peer_abort = 0;
+    ps->fills_own = 0;
+    ps->fills_peer = 0;
     fence_mbar_init();
     fence_proxy_async_smem();
     tma_prefetch_desc(&tmAh);
@@ -127,6 +133,7 @@ sgemm_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_
     if (lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
+      uint32_t fills = 0;
       bool ok = true;
       for (int t = pair; t < num_tiles && ok; t += num_pairs) {
         int mi, ni;
@@ -151,6 +158,7 @@ sgemm_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_
             tma_load_2d_pair(b_hi + b * T_B_BOX_BYTES, &tmBh, full_even, n0 + 32 * b, k0);
             tma_load_2d_pair(b_lo + b * T_B_BOX_BYTES, &tmBl, full_even, n0 + 32 * b, k0);
           }
+          ++fills;
           if (++stage == T_STAGES) {
             stage = 0;
             phase ^= 1;
@@ -166,6 +174,9 @@ sgemm_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_
           }
         }
       }
+      // How far this producer got, for the teardown of a pair that gave up (see the end of the kernel).
+      if (rank == 0) ps->fills_own = fills;
+      else st_shared_cluster_u32(mapa_shared(smem_u32(&ps->fills_peer), 0), fills);
     }
     __syncwarp();
   } else if (warp == 1) {
@@ -301,8 +312,20 @@ sgemm_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_
     __syncwarp();
   }
 
+  // Neither CTA may free TMEM or leave while its peer's MMAs, commits or remote arrivals can still touch it.
+  // The two CTAs also tell each other whether they gave up: a pair that did makes sure that no copy is still on
+  // its way into either CTA's shared memory before the CTAs go (pair_drain_loads, umma_tile.cuh).
   tc_fence_before_sync();
+  __syncthreads();                                   // every role of this CTA is done: the abort word is final
+  if (threadIdx.x == 0)
+    st_shared_cluster_u32(mapa_shared(smem_u32(&ps->peer_abort), rank ^ 1u), uint32_t(ps->abort_word));
   cluster_sync_all();
+  if (ps->abort_word != 0 || ps->peer_abort != 0) {  // the same verdict in both CTAs
+    if (rank == 0 && threadIdx.x == 0 &&
+        !pair_drain_loads<T_STAGES>(ps->full, ps->fills_own, ps->fills_peer, T_STAGE_BYTES))
+      atomicCAS(&ps->abort_word, 0, KSTAT_WAIT_EXPIRED_DRAIN);
+    cluster_sync_all();
+  }
   if (warp == 1) tmem_dealloc<2>(tmem_base, TMEM_COLS);
   if (threadIdx.x == 0 && ps->abort_word != 0) atomicCAS(status, 0, ps->abort_word);
 }

@@ -12,7 +12,7 @@ constexpr int BN = 256;                             // accumulator columns per t
 constexpr int NUM_THREADS = 192;                    // 1 TMA warp, 1 MMA warp, 4 epilogue warps
 constexpr int TMEM_COLS = 512;                      // two 256-column 32-bit accumulators
 
-// Epilogue staging: each epilogue warp owns two 32-row x 32-column int32 buffers (4 KiB each,
+// Epilogue staging: each epilogue warp owns one or two 32-row x 32-column int32 buffers (4 KiB each,
 // 128-byte rows in the 128-byte swizzle the C tensor map expects).
 constexpr int EPI_BUF_BYTES = 32 * 32 * 4;
 constexpr int EPI_STAGING_BYTES = 4 * 2 * EPI_BUF_BYTES;   // 32 KiB
@@ -40,54 +40,108 @@ __device__ __forceinline__ void tile_coords(const TileRaster& rs, int t, int& mi
   }
 }
 
-// Moves one warp's 32 rows x 256 columns of an accumulator from TMEM to C.
-//   kTmaStore: TMEM -> registers -> swizzled shared memory -> cp.async.bulk.tensor store, so C is
-//              written in whole 128-byte lines and rows/columns outside C are clipped by the TMA unit;
-//   otherwise: TMEM -> registers -> predicated 16-byte global stores.
+// Moves one warp's 32 rows x 256 columns of an accumulator from TMEM to C: TMEM -> registers ->
+// swizzled shared memory -> cp.async.bulk.tensor store, so C is written in whole 128-byte lines and
+// rows/columns outside C are clipped by the TMA unit.
 // `wide`, when given, is 8 further buffers (32 KiB, 1024-byte aligned) that nothing else uses any more: every
 // column chunk then gets a buffer of its own and no store waits for the one before it (the last tile of a
 // CTA, whose epilogue nothing overlaps, takes them from the idle operand ring).
+// `merge`, when given, points at this lane's first 16 bytes of `ncontrib` partial accumulators of the same
+// tile (the layout epilogue_warp_partial writes, `merge_stride` uint4 apart); they are added before the
+// store.  The loads of one chunk are issued while the chunk before it is added and stored.
 // Returns once the accumulator has been read (the stores may still be in flight).
-template <bool kTmaStore, int kBufs = 2>
-__device__ __forceinline__ void epilogue_warp_tile(uint32_t t_row, const CUtensorMap* tmC, uint8_t* staging,
-                                                   int32_t* __restrict__ C, int M, int N, int row0, int n0,
-                                                   int lane, uint64_t store_policy = 0, uint8_t* wide = nullptr) {
-  const int row = row0 + lane;
+template <int kBufs = 2>
+__device__ __forceinline__ void epilogue_warp_tile(uint32_t t_row, const CUtensorMap* tmC, uint8_t* staging, int M,
+                                                   int N, int row0, int n0, int lane, uint64_t store_policy = 0,
+                                                   uint8_t* wide = nullptr, const uint4* merge = nullptr,
+                                                   int ncontrib = 0, size_t merge_stride = 0) {
+  uint4 nxt[8];
+  if (ncontrib > 0) {
+#pragma unroll
+    for (int v = 0; v < 8; ++v) nxt[v] = ld_global_cg_v4(merge + v * 32);
+  }
 #pragma unroll 1
   for (int c = 0; c < BN / 32; ++c) {
     uint32_t r[32];
     tmem_ld_32x32b_x32(t_row + uint32_t(c * 32), r);
     tmem_ld_wait();
-    if constexpr (kTmaStore) {
-      uint8_t* buf = wide ? wide + c * EPI_BUF_BYTES : staging + (c & (kBufs - 1)) * EPI_BUF_BYTES;
-      if (!wide) {
-        if (lane == 0) tma_store_wait_read<kBufs - 1>();   // the store that last read this buffer is done with it
-        __syncwarp();
-      }
-      const uint32_t base = smem_u32(buf) + uint32_t(lane) * 128u;
+#pragma unroll 1
+    for (int x = 0; x < ncontrib; ++x) {
+      uint4 cur[8];
 #pragma unroll
-      for (int v = 0; v < 8; ++v)
-        st_shared_v4(base + (uint32_t(v ^ (lane & 7)) << 4), r[4 * v], r[4 * v + 1], r[4 * v + 2], r[4 * v + 3]);
-      fence_proxy_async_smem();
-      __syncwarp();
-      if (lane == 0) {
-        if (row0 < M && n0 + c * 32 < N) {
-          if (store_policy) tma_store_2d_hint(tmC, buf, n0 + c * 32, row0, store_policy);
-          else tma_store_2d(tmC, buf, n0 + c * 32, row0);
-        }
-        tma_store_commit();
-      }
-    } else {
-      if (row < M) {
-        int32_t* crow = C + size_t(row) * size_t(N) + n0;
+      for (int v = 0; v < 8; ++v) cur[v] = nxt[v];
+      const int nx = x + 1 == ncontrib ? 0 : x + 1;
+      const int nc = x + 1 == ncontrib ? c + 1 : c;
+      if (nc < BN / 32) {
+        const uint4* src = merge + size_t(nx) * merge_stride + size_t(nc) * 256;
 #pragma unroll
-        for (int v = 0; v < 8; ++v) {
-          const int col = n0 + c * 32 + v * 4;
-          if (col < N) st_global_v4(crow + c * 32 + v * 4, r[4 * v], r[4 * v + 1], r[4 * v + 2], r[4 * v + 3]);
-        }
+        for (int v = 0; v < 8; ++v) nxt[v] = ld_global_cg_v4(src + v * 32);
+      }
+#pragma unroll
+      for (int v = 0; v < 8; ++v) {
+        r[4 * v] += cur[v].x;
+        r[4 * v + 1] += cur[v].y;
+        r[4 * v + 2] += cur[v].z;
+        r[4 * v + 3] += cur[v].w;
       }
     }
+    uint8_t* buf = wide ? wide + c * EPI_BUF_BYTES : staging + (c & (kBufs - 1)) * EPI_BUF_BYTES;
+    if (!wide) {
+      if (lane == 0) tma_store_wait_read<kBufs - 1>();   // the store that last read this buffer is done with it
+      __syncwarp();
+    }
+    const uint32_t base = smem_u32(buf) + uint32_t(lane) * 128u;
+#pragma unroll
+    for (int v = 0; v < 8; ++v)
+      st_shared_v4(base + (uint32_t(v ^ (lane & 7)) << 4), r[4 * v], r[4 * v + 1], r[4 * v + 2], r[4 * v + 3]);
+    fence_proxy_async_smem();
+    __syncwarp();
+    if (lane == 0) {
+      if (row0 < M && n0 + c * 32 < N) {
+        if (store_policy) tma_store_2d_hint(tmC, buf, n0 + c * 32, row0, store_policy);
+        else tma_store_2d(tmC, buf, n0 + c * 32, row0);
+      }
+      tma_store_commit();
+    }
   }
+}
+
+// Leaves one warp's 32 rows x 256 columns of an accumulator in scratch memory as a partial sum that another
+// CTA will add (epilogue_warp_tile's `merge`).  `slot` is this lane's first 16 bytes of the warp's 32 KiB:
+// uint4 index ((chunk * 8 + v) * 32 + lane) holds columns [32 chunk + 4 v, +4) of the lane's row, so every
+// store instruction of the warp writes 512 contiguous bytes.
+__device__ __forceinline__ void epilogue_warp_partial(uint32_t t_row, uint4* slot) {
+#pragma unroll 1
+  for (int c = 0; c < BN / 32; ++c) {
+    uint32_t r[32];
+    tmem_ld_32x32b_x32(t_row + uint32_t(c * 32), r);
+    tmem_ld_wait();
+#pragma unroll
+    for (int v = 0; v < 8; ++v) st_global_v4(slot + (c * 8 + v) * 32, r[4 * v], r[4 * v + 1], r[4 * v + 2], r[4 * v + 3]);
+  }
+}
+
+// Teardown of a CTA pair whose pipeline gave up, run by one thread of the even CTA after both CTAs have stopped
+// issuing copies.  Both CTAs' operand copies are counted on the even CTA's `full` barriers, which its producer
+// arms for the two of them; `fills_even` / `fills_odd` say how many ring fills each producer got to.  A fill
+// that only one of them reached can never complete by itself, so the books are balanced first (bytes that will
+// never come are written off; a copy of the peer that was never armed is armed now), and then the last fill of
+// every stage is waited for, with a limit.  After this no copy is in flight into either CTA's shared memory.
+template <int kStages>
+__device__ __forceinline__ bool pair_drain_loads(uint64_t* full, uint32_t fills_even, uint32_t fills_odd,
+                                                 uint32_t bytes_per_cta) {
+  const uint32_t hi = fills_even > fills_odd ? fills_even : fills_odd;
+  uint32_t lo = fills_even > fills_odd ? fills_odd : fills_even;
+  if (hi - lo > uint32_t(kStages)) lo = hi - uint32_t(kStages);
+  for (uint32_t f = lo; f < hi; ++f) {
+    uint64_t* bar = &full[f % uint32_t(kStages)];
+    if (fills_even > fills_odd) mbar_complete_tx(bar, bytes_per_cta);
+    else mbar_arrive_expect_tx(bar, bytes_per_cta);
+  }
+  bool ok = true;
+  for (uint32_t f = hi > uint32_t(kStages) ? hi - uint32_t(kStages) : 0; f < hi; ++f)
+    ok = mbar_wait_drain(&full[f % uint32_t(kStages)], (f / uint32_t(kStages)) & 1u) && ok;
+  return ok;
 }
 
 }  // namespace

@@ -76,14 +76,22 @@ def replicate_from_rank0(tensor):
     return tensor
 
 
-def sharded_gemm(compute, A_rows, B, C_rows):
-    """Runs `compute(A_rows, B, C_rows)` on this rank's block; a no-op for an empty block.
+def run_row_sharded(compute, A_rows, B_local, C_rows, B_source=None):
+    """One end-to-end step of the row-sharded product on this rank.
 
-    `compute` is the device call (for int8: a closure over `_native.i8gemm` with VT_DEVICE).  The
-    function exists so that the host-side sharding logic is one code path whether the call below it
-    is the CUDA kernel or, in CPU tests, a checker.
+    `B_source` is the job's B where it originates, on rank 0 only (a pinned host tensor in the GPU job): rank 0
+    copies it into its `B_local`, the broadcast then delivers it into every other rank's `B_local` over the
+    GPU interconnect, so B crosses the host link once per job step instead of once per rank.  After that
+    `compute(A_rows, B_local, C_rows)` runs on this rank's block (for int8: `_native.i8gemm` with
+    VT_HOST_AC_DEVICE_B, which copies the block of A in and the block of C out); a rank with an empty block
+    still takes part in the broadcast.  The same function drives the CPU test, where `compute` is a checker.
     """
-    if A_rows.shape[0] == 0:
-        return C_rows
-    compute(A_rows, B, C_rows)
+    import torch.distributed as dist
+
+    rank = dist.get_rank() if dist.is_available() and dist.is_initialized() else 0
+    if B_source is not None and rank == 0:
+        B_local.copy_(B_source, non_blocking=True)
+    replicate_from_rank0(B_local)
+    if A_rows.shape[0] > 0:
+        compute(A_rows, B_local, C_rows)
     return C_rows

@@ -61,15 +61,17 @@ enum {
 /* int8 kernel variants.  VT_I8_AUTO picks the fastest verified one (CTA_PAIR above 128 rows); the others
  * exist so that a design choice can be measured against its alternative:
  *   B_AS_STORED            one CTA per 128x256 tile
- *   CTA_PAIR               two CTAs per 256x256 tile (tcgen05 cta_group::2); when the tiles do not fill a whole
- *                          number of waves of CTA pairs, the K blocks of the last wave are shared by all pairs
- *                          and the partial int32 sums are added by the pair that owns the tile (exact)
- *   CTA_PAIR_WHOLE_TILES   the same kernel with every tile computed whole by one pair
+ *   CTA_PAIR               two CTAs per 256x256 tile (tcgen05 cta_group::2), every tile computed by one pair
+ *   CTA_PAIR_SHARED_TAIL   the same kernel; when the tiles do not fill a whole number of waves of CTA pairs,
+ *                          the K blocks of the last wave are shared by all pairs and the partial int32 sums
+ *                          are added by the pair that owns the tile (exact).  Measured level with CTA_PAIR
+ *                          (the pairs then no longer walk K in step and the L2 serves them more slowly),
+ *                          so VT_I8_AUTO does not choose it.
  * All read B as stored and write C by TMA stores. */
 enum {
   VT_I8_AUTO = 0,
   VT_I8_B_AS_STORED = 1,
-  VT_I8_CTA_PAIR_WHOLE_TILES = 2,
+  VT_I8_CTA_PAIR_SHARED_TAIL = 2,
   VT_I8_CTA_PAIR = 3
 };
 

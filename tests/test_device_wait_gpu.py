@@ -16,7 +16,7 @@ pytestmark = pytest.mark.gpu
 SHORT = 4_000_000        # cycles: about 2 ms
 
 
-def exact_call(native, m, n, k, seed, variant=0):
+def exact_call(native, m, n, k, seed, variant=2):
     import torch
     gen = torch.Generator(device="cuda").manual_seed(seed)
     A = torch.randint(-128, 128, (m, k), dtype=torch.int8, device="cuda", generator=gen)
@@ -59,7 +59,7 @@ def test_pair_kernel_tears_down_when_its_peer_stops(native, shape):
     C = torch.zeros((m, n), dtype=torch.int32, device="cuda")
     try:
         native.test_set_wait_hooks(0, SHORT, 5)
-        native.i8gemm(A, B, C, m, n, k, where=native.VT_DEVICE, stream=st)
+        native.i8gemm(A, B, C, m, n, k, variant=native.VT_I8_CTA_PAIR_SHARED_TAIL, where=native.VT_DEVICE, stream=st)
         with pytest.raises(native.NativeError) as err:
             native.sync(0, st)
         assert err.value.code == native.VT_ERR_DEVICE_WAIT

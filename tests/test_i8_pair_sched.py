@@ -3,7 +3,8 @@
 The header is compiled into a small program that prints every pair's items.  Every (tile, K-block) must be
 computed exactly once; every tile must be finished (written to C) by exactly one pair, which must name as
 contributors exactly the pairs that left a partial sum of that tile; a pair leaves at most one partial sum
-(it has one scratch slot), and leaves it before anything it could have to wait for."""
+(it has one scratch slot), and leaves it before anything it could have to wait for; an owned tile whose
+contributors' sums are written into the accumulator ahead of its MMAs comes right after a whole tile."""
 import shutil
 import subprocess
 from pathlib import Path
@@ -24,7 +25,7 @@ int main(int argc, char** argv) {
   for (int p = 0; p < s.pairs; ++p) {
     vt::PairItem it;
     for (int i = 0; vt::pair_item(s, p, i, it); ++i)
-      printf("I %d %d %d %d %d %d %d %d\n", p, i, it.tile, it.kb0, it.kb1, it.kind, it.contrib0, it.ncontrib);
+      printf("I %d %d %d %d %d %d %d %d %d\n", p, i, it.tile, it.kb0, it.kb1, it.kind, it.contrib0, it.ncontrib, it.preload);
   }
   return 0;
 }
@@ -59,8 +60,14 @@ def check(head, items, tiles, kb):
     covered = {}
     finished = {}
     partial_of = {}
-    for p, i, tile, kb0, kb1, kind, c0, nc in items:
+    for p, i, tile, kb0, kb1, kind, c0, nc, pre in items:
         assert 0 <= tile < tiles and 0 <= kb0 < kb1 <= kb
+        if pre:
+            # sums written into an accumulator ahead of the MMAs: the accumulator must have been used and drained
+            # before (two items earlier), and the item right before must be a whole tile that hides the work
+            assert kind == 0 and nc > 0 and i >= 2
+            before = [x for x in items if x[0] == p and x[1] == i - 1][0]
+            assert before[3] == 0 and before[4] == kb and before[5] == 0
         for k in range(kb0, kb1):
             assert (tile, k) not in covered, "K block computed twice"
             covered[(tile, k)] = p
@@ -82,7 +89,7 @@ def check(head, items, tiles, kb):
         assert all(q < p for q in contributors)
     # per-pair K blocks: nobody does more than a whole-tile schedule would give the busiest pair
     work = {}
-    for p, i, tile, kb0, kb1, kind, c0, nc in items:
+    for p, i, tile, kb0, kb1, kind, c0, nc, pre in items:
         work[p] = work.get(p, 0) + kb1 - kb0
     return max(work.values()), tail
 

@@ -343,7 +343,7 @@ def _device_case(native, m, n, k, seed, variant=0, reps=2):
         assert torch.equal(C, want), (m, n, k, variant, rep)
 
 
-@pytest.mark.parametrize("variant", [0, 3])
+@pytest.mark.parametrize("variant", [0, 2])
 def test_shared_tail_of_the_pair_kernel(native, variant):
     """Shapes whose 256 x 256 tiles do not fill whole waves of the 74 CTA pairs: the K blocks of the last wave
     are dealt to all pairs and partial int32 sums meet in scratch memory.  The 1024- and 2048-row shards of the
@@ -364,7 +364,7 @@ def test_shared_tail_equals_whole_tiles(native):
     B = torch.randint(-128, 128, (k, n), dtype=torch.int8, device="cuda", generator=gen)
     st = native.torch_stream()
     outs = []
-    for variant in (native.VT_I8_CTA_PAIR_WHOLE_TILES, native.VT_I8_CTA_PAIR):
+    for variant in (native.VT_I8_CTA_PAIR, native.VT_I8_CTA_PAIR_SHARED_TAIL):
         for raster, br in ((0, 1), (1, 1), (2, 3), (3, 1)):
             C = torch.full((m, n), -2**31, dtype=torch.int32, device="cuda")
             native.i8gemm(A, B, C, m, n, k, variant=variant, raster=raster, batch_rows=br, where=native.VT_DEVICE, stream=st)

@@ -7,9 +7,16 @@
 // tile's last K-block *owns* the tile, adds the partial accumulators of the pairs before it and writes
 // C.  int32 addition is associative, so the result does not depend on the cut.
 //
-// A pair runs its items in this order: its partial piece (at most one: the end of its range), the tail
-// tiles it owns, then its whole tiles.  Partial pieces wait for nothing, so every owner's wait for its
-// contributors ends; the owner's merge overlaps the MMAs of the whole tile after it.
+// A pair's partial piece (at most one: the end of its range) is always its first item; partial pieces wait
+// for nothing, so every owner's wait for its contributors ends.  The rest of the order keeps the adding of
+// partial sums off the critical path:
+//   * a pair with a partial piece and whole tiles runs  partial, whole tiles, owned tail tiles.  Its owned
+//     tile that has contributors is *preloaded*: while the whole tile before it is being multiplied, the
+//     epilogue warps add the contributors' sums and write them into the (idle) accumulator, and the MMAs of
+//     the owned piece then accumulate on top;
+//   * a pair without a partial piece runs  owned tail tiles, whole tiles,  and a pair without whole tiles
+//     partial, owned tail tiles: there the contributors' sums are added in the epilogue of the owned tile
+//     (overlapping the whole tile after it, where there is one).
 #pragma once
 
 #include <stdint.h>
@@ -34,6 +41,7 @@ struct PairItem {
   int kind;            // PAIR_ITEM_TO_C: finish the tile and write C; PAIR_ITEM_PARTIAL: leave sums in this pair's slot
   int contrib0;        // PAIR_ITEM_TO_C: pairs [contrib0, contrib0 + ncontrib) left partial sums of this tile
   int ncontrib;
+  int preload;         // the contributors' sums go into the accumulator before the MMAs (else: added in the epilogue)
 };
 
 // Whether sharing the tail pays: the idle part of the last wave must be worth more than the extra
@@ -50,80 +58,127 @@ __host__ __device__ inline PairSched make_pair_sched(int pairs, int tiles, int k
     const long long units = (long long)tail * kblocks;
     const long long per = units / pairs;
     const long long idle = (long long)(pairs - tail) * kblocks;   // pair-K-blocks the whole-tile order leaves unused
-    if (per >= 16 && per * 8 >= kblocks && idle >= 12LL * pairs) s.tail = tail;
+    // units * pairs < 2^31 keeps the device-side arithmetic in 32 bits
+    if (per >= 16 && per * 8 >= kblocks && idle >= 12LL * pairs && units * pairs < 0x7fffffffLL) s.tail = tail;
   }
   if (s.tail == 0) s.whole_waves = (tiles + pairs - 1) / pairs;   // upper bound; items past `tiles` do not exist
   return s;
 }
 
 // First unit of pair p's range (units: tail tile j, K-block kb -> j * KB + kb).
-__host__ __device__ inline long long pair_range_begin(const PairSched& s, int p) {
-  const long long units = (long long)s.tail * s.kblocks;
+__host__ __device__ inline int pair_range_begin(const PairSched& s, int p) {
+  const int units = s.tail * s.kblocks;
   if (p <= 0) return 0;
   if (p >= s.pairs) return units;
-  long long b = (long long)p * units / s.pairs;
-  const int r = int(b % s.kblocks);
+  int b = int(unsigned(p * units) / unsigned(s.pairs));
+  const int r = b % s.kblocks;
   if (r < PAIR_MIN_PIECE) b -= r;
   else if (s.kblocks - r < PAIR_MIN_PIECE) b += s.kblocks - r;
   return b;
 }
 
-// The idx-th item of pair `pair`; false when it has no more.
-__host__ __device__ inline bool pair_item(const PairSched& s, int pair, int idx, PairItem& out) {
+// Range begins as a function object, so that the kernel can read them from a table its warps fill in parallel
+// while the host-side check computes them directly.
+struct PairRangeDirect {
+  const PairSched& s;
+  __host__ __device__ int operator()(int p) const { return pair_range_begin(s, p); }
+};
+
+// Number of items of pair `pair` that lie in the shared tail (they come first): at most one partial piece and
+// the tail tiles whose last K-block is in the pair's range.
+template <class RangeBegin>
+__host__ __device__ inline int pair_tail_items(const PairSched& s, int pair, const RangeBegin& begin) {
+  if (s.tail == 0) return 0;
+  const int u0 = begin(pair), u1 = begin(pair + 1);
+  if (u1 <= u0) return 0;
+  const int j_end = u1 / s.kblocks;
+  return (u1 - j_end * s.kblocks != 0 ? 1 : 0) + j_end - u0 / s.kblocks;
+}
+__host__ __device__ inline int pair_tail_items(const PairSched& s, int pair) {
+  return pair_tail_items(s, pair, PairRangeDirect{s});
+}
+
+// The t-th item of pair `pair` inside the shared tail, in range order: the partial piece (if any), then the
+// owned tiles; t < pair_tail_items().
+template <class RangeBegin>
+__host__ __device__ inline void pair_tail_item(const PairSched& s, int pair, int t, PairItem& out, const RangeBegin& begin) {
+  const int KB = s.kblocks;
+  const int first_tail_tile = s.whole_waves * s.pairs;
+  const int u0 = begin(pair), u1 = begin(pair + 1);
+  const int j_first = u0 / KB, j_end = u1 / KB;                // tail tiles [j_first, j_end) end inside the range
+  const bool has_partial = u1 > u0 && u1 != j_end * KB;
   out.contrib0 = 0;
   out.ncontrib = 0;
+  out.preload = 0;
+  if (has_partial) {
+    if (t == 0) {
+      const int base = j_end * KB;
+      out.tile = first_tail_tile + j_end;
+      out.kb0 = (u0 > base ? u0 : base) - base;
+      out.kb1 = u1 - base;
+      out.kind = PAIR_ITEM_PARTIAL;
+      return;
+    }
+    --t;
+  }
+  const int j = j_first + t;
+  const int base = j * KB;
+  out.tile = first_tail_tile + j;
+  out.kb0 = (u0 > base ? u0 : base) - base;
+  out.kb1 = KB;
+  out.kind = PAIR_ITEM_TO_C;
+  if (out.kb0 > 0) {
+    // The pairs before this one whose ranges reach into tile j, nearest first.
+    int n = 0;
+    for (int q = pair - 1; q >= 0 && begin(q + 1) > base; --q) {
+      ++n;
+      if (begin(q) <= base) break;
+    }
+    out.ncontrib = n;
+    out.contrib0 = pair - n;
+    out.preload = (has_partial && s.whole_waves > 0) ? 1 : 0;
+  }
+}
+
+// Position of the whole tiles in a pair's order: after the partial piece when it has one, else after the tail.
+__host__ __device__ inline int pair_whole_first(int tail_items, bool first_is_partial) {
+  return first_is_partial ? 1 : tail_items;
+}
+
+// The idx-th item of pair `pair` in execution order; false when it has no more.
+template <class RangeBegin>
+__host__ __device__ inline bool pair_item(const PairSched& s, int pair, int idx, PairItem& out, const RangeBegin& begin) {
+  out.contrib0 = 0;
+  out.ncontrib = 0;
+  out.preload = 0;
+  out.kb0 = 0;
+  out.kb1 = s.kblocks;
+  out.kind = PAIR_ITEM_TO_C;
   if (s.tail == 0) {
     const long long t = (long long)pair + (long long)idx * s.pairs;
     if (t >= s.tiles) return false;
     out.tile = int(t);
-    out.kb0 = 0;
-    out.kb1 = s.kblocks;
-    out.kind = PAIR_ITEM_TO_C;
     return true;
   }
-  const int KB = s.kblocks;
-  const int first_tail_tile = s.whole_waves * s.pairs;
-  const long long u0 = pair_range_begin(s, pair), u1 = pair_range_begin(s, pair + 1);
-  const int j_first = int(u0 / KB), j_end = int(u1 / KB);      // tail tiles [j_first, j_end) end inside the range
-  const bool has_partial = u1 > u0 && (u1 % KB) != 0;
-  const int owned = u1 > u0 ? j_end - j_first : 0;
-  if (has_partial) {
-    if (idx == 0) {
-      const long long base = (long long)j_end * KB;
-      out.tile = first_tail_tile + j_end;
-      out.kb0 = int((u0 > base ? u0 : base) - base);
-      out.kb1 = int(u1 - base);
-      out.kind = PAIR_ITEM_PARTIAL;
-      return true;
-    }
-    --idx;
+  const int n_tail = pair_tail_items(s, pair, begin);
+  bool first_is_partial = false;
+  if (n_tail > 0) {
+    PairItem first;
+    pair_tail_item(s, pair, 0, first, begin);
+    first_is_partial = first.kind == PAIR_ITEM_PARTIAL;
   }
-  if (idx < owned) {
-    const int j = j_first + idx;
-    const long long base = (long long)j * KB;
-    out.tile = first_tail_tile + j;
-    out.kb0 = int((u0 > base ? u0 : base) - base);
-    out.kb1 = KB;
-    out.kind = PAIR_ITEM_TO_C;
-    if (out.kb0 > 0) {
-      // The pairs before this one whose ranges reach into tile j, nearest first.
-      int n = 0;
-      for (int q = pair - 1; q >= 0 && pair_range_begin(s, q + 1) > base; --q) {
-        ++n;
-        if (pair_range_begin(s, q) <= base) break;
-      }
-      out.ncontrib = n;
-      out.contrib0 = pair - n;
-    }
+  const int w0 = pair_whole_first(n_tail, first_is_partial);
+  if (idx >= w0 && idx < w0 + s.whole_waves) {
+    out.tile = pair + (idx - w0) * s.pairs;
     return true;
   }
-  idx -= owned;
-  if (idx >= s.whole_waves) return false;
-  out.tile = pair + idx * s.pairs;
-  out.kb0 = 0;
-  out.kb1 = KB;
-  out.kind = PAIR_ITEM_TO_C;
+  const int t = idx < w0 ? idx : idx - s.whole_waves;
+  if (t >= n_tail) return false;
+  pair_tail_item(s, pair, t, out, begin);
   return true;
+}
+__host__ __device__ inline bool pair_item(const PairSched& s, int pair, int idx, PairItem& out) {
+  return pair_item(s, pair, idx, out, PairRangeDirect{s});
 }
 
 }  // namespace vt

@@ -86,7 +86,7 @@ DeviceCtx* ctx_for(int dev) {
   CTX_TRY(cudaMallocHost(&c->status_host, sizeof(int)));
   CTX_TRY(cudaMalloc(&c->tickets, kTicketCount * sizeof(int)));
   CTX_TRY(cudaMemset(c->tickets, 0, kTicketCount * sizeof(int)));
-  c->i8_flag_count = c->sm_count * 4;
+  c->i8_flag_count = c->sm_count * 8;
   CTX_TRY(cudaMalloc(&c->i8_flags, size_t(c->i8_flag_count) * sizeof(int)));
   CTX_TRY(cudaMemset(c->i8_flags, 0, size_t(c->i8_flag_count) * sizeof(int)));
   CTX_TRY(cudaMalloc(&c->i8_partials, size_t(c->sm_count) * 128 * 256 * sizeof(int32_t)));

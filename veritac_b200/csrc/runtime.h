@@ -27,7 +27,7 @@ struct DeviceCtx {
   int* status = nullptr;               // device word kernels write a KSTAT_* code into
   int* status_host = nullptr;          // pinned mirror
   int* tickets = nullptr;              // kTicketCount zeroed counters (per-slab arrival counts of the skinny kernel)
-  // int8 CTA-pair kernel: one 128 x 256 int32 partial accumulator per CTA and one flag per epilogue warp (zero
+  // int8 CTA-pair kernel: one 128 x 256 int32 partial accumulator per CTA and eight flags, one per epilogue warp (zero
   // between launches), sized for one CTA per SM at context creation so that no launch ever allocates
   void* i8_partials = nullptr;
   int* i8_flags = nullptr;
@@ -92,8 +92,8 @@ cudaError_t launch_overlapped(void (*kernel)(KArgs...), unsigned grid, unsigned 
 
 // ---- kernel launchers (device pointers only) ------------------------------------------------
 // raster_mode: 0 row-major tiles, 1 column-major tiles, 2 grouped (group = tile-rows per sweep).
-// variant: VT_I8_B_AS_STORED (one CTA per 128 x 256 tile), VT_I8_CTA_PAIR (two CTAs per 256 x 256 tile, the last
-// partial wave of tiles shared along K), VT_I8_CTA_PAIR_WHOLE_TILES (the same without the sharing).
+// variant: VT_I8_B_AS_STORED (one CTA per 128 x 256 tile), VT_I8_CTA_PAIR (two CTAs per 256 x 256 tile),
+// VT_I8_CTA_PAIR_SHARED_TAIL (the same with the last partial wave of tiles shared along K).
 // ldb / ldc: row pitch of B and C in elements when they are sub-blocks of wider matrices (0 = N).
 int launch_i8gemm(DeviceCtx* c, const int8_t* A, const int8_t* B, int32_t* C, int64_t M, int64_t N, int64_t K,
                   int raster_mode, int group, int variant, cudaStream_t s, int64_t ldb = 0, int64_t ldc = 0);

@@ -40,10 +40,10 @@ __device__ __forceinline__ void tile_coords(const TileRaster& rs, int t, int& mi
   }
 }
 
-// Moves one warp's 32 rows x 256 columns of an accumulator from TMEM to C: TMEM -> registers ->
+// Moves one warp's 32 rows x 32 (c_end - c_begin) columns of an accumulator from TMEM to C: TMEM -> registers ->
 // swizzled shared memory -> cp.async.bulk.tensor store, so C is written in whole 128-byte lines and
 // rows/columns outside C are clipped by the TMA unit.
-// `wide`, when given, is 8 further buffers (32 KiB, 1024-byte aligned) that nothing else uses any more: every
+// `wide`, when given, is one further buffer per column chunk (4 KiB each, 1024-byte aligned) that nothing else uses any more: every
 // column chunk then gets a buffer of its own and no store waits for the one before it (the last tile of a
 // CTA, whose epilogue nothing overlaps, takes them from the idle operand ring).
 // `merge`, when given, points at this lane's first 16 bytes of `ncontrib` partial accumulators of the same
@@ -54,14 +54,15 @@ template <int kBufs = 2>
 __device__ __forceinline__ void epilogue_warp_tile(uint32_t t_row, const CUtensorMap* tmC, uint8_t* staging, int M,
                                                    int N, int row0, int n0, int lane, uint64_t store_policy = 0,
                                                    uint8_t* wide = nullptr, const uint4* merge = nullptr,
-                                                   int ncontrib = 0, size_t merge_stride = 0) {
+                                                   int ncontrib = 0, size_t merge_stride = 0, int c_begin = 0,
+                                                   int c_end = BN / 32) {
   uint4 nxt[8];
   if (ncontrib > 0) {
 #pragma unroll
-    for (int v = 0; v < 8; ++v) nxt[v] = ld_global_cg_v4(merge + v * 32);
+    for (int v = 0; v < 8; ++v) nxt[v] = ld_global_cg_v4(merge + size_t(c_begin) * 256 + v * 32);
   }
 #pragma unroll 1
-  for (int c = 0; c < BN / 32; ++c) {
+  for (int c = c_begin; c < c_end; ++c) {
     uint32_t r[32];
     tmem_ld_32x32b_x32(t_row + uint32_t(c * 32), r);
     tmem_ld_wait();
@@ -72,7 +73,7 @@ __device__ __forceinline__ void epilogue_warp_tile(uint32_t t_row, const CUtenso
       for (int v = 0; v < 8; ++v) cur[v] = nxt[v];
       const int nx = x + 1 == ncontrib ? 0 : x + 1;
       const int nc = x + 1 == ncontrib ? c + 1 : c;
-      if (nc < BN / 32) {
+      if (nc < c_end) {
         const uint4* src = merge + size_t(nx) * merge_stride + size_t(nc) * 256;
 #pragma unroll
         for (int v = 0; v < 8; ++v) nxt[v] = ld_global_cg_v4(src + v * 32);
@@ -85,7 +86,7 @@ __device__ __forceinline__ void epilogue_warp_tile(uint32_t t_row, const CUtenso
         r[4 * v + 3] += cur[v].w;
       }
     }
-    uint8_t* buf = wide ? wide + c * EPI_BUF_BYTES : staging + (c & (kBufs - 1)) * EPI_BUF_BYTES;
+    uint8_t* buf = wide ? wide + (c - c_begin) * EPI_BUF_BYTES : staging + (c & (kBufs - 1)) * EPI_BUF_BYTES;
     if (!wide) {
       if (lane == 0) tma_store_wait_read<kBufs - 1>();   // the store that last read this buffer is done with it
       __syncwarp();
@@ -106,19 +107,48 @@ __device__ __forceinline__ void epilogue_warp_tile(uint32_t t_row, const CUtenso
   }
 }
 
-// Leaves one warp's 32 rows x 256 columns of an accumulator in scratch memory as a partial sum that another
-// CTA will add (epilogue_warp_tile's `merge`).  `slot` is this lane's first 16 bytes of the warp's 32 KiB:
+// Leaves one warp's 32 rows x 32 (c_end - c_begin) columns of an accumulator in scratch memory as a partial sum that
+// another CTA will add (epilogue_warp_tile's `merge`).  `slot` is this lane's first 16 bytes of the quarter's 32 KiB:
 // uint4 index ((chunk * 8 + v) * 32 + lane) holds columns [32 chunk + 4 v, +4) of the lane's row, so every
 // store instruction of the warp writes 512 contiguous bytes.
-__device__ __forceinline__ void epilogue_warp_partial(uint32_t t_row, uint4* slot) {
+__device__ __forceinline__ void epilogue_warp_partial(uint32_t t_row, uint4* slot, int c_begin = 0, int c_end = BN / 32) {
 #pragma unroll 1
-  for (int c = 0; c < BN / 32; ++c) {
+  for (int c = c_begin; c < c_end; ++c) {
     uint32_t r[32];
     tmem_ld_32x32b_x32(t_row + uint32_t(c * 32), r);
     tmem_ld_wait();
 #pragma unroll
     for (int v = 0; v < 8; ++v) st_global_v4(slot + (c * 8 + v) * 32, r[4 * v], r[4 * v + 1], r[4 * v + 2], r[4 * v + 3]);
   }
+}
+
+// Writes the sum of `ncontrib` partial accumulators (the layout epilogue_warp_partial leaves, `merge_stride` uint4
+// apart, `merge` = this lane's first 16 bytes of the first one) into one warp's 32 rows x 32 (c_end - c_begin)
+// columns of an accumulator in TMEM, so that MMAs issued afterwards accumulate on top of them.
+__device__ __forceinline__ void preload_warp_tile(uint32_t t_row, const uint4* merge, int ncontrib, size_t merge_stride,
+                                                  int c_begin, int c_end) {
+#pragma unroll 1
+  for (int c = c_begin; c < c_end; ++c) {
+    uint32_t r[32];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) r[i] = 0u;
+#pragma unroll 1
+    for (int x = 0; x < ncontrib; ++x) {
+      const uint4* src = merge + size_t(x) * merge_stride + size_t(c) * 256;
+      uint4 cur[8];
+#pragma unroll
+      for (int v = 0; v < 8; ++v) cur[v] = ld_global_cg_v4(src + v * 32);
+#pragma unroll
+      for (int v = 0; v < 8; ++v) {
+        r[4 * v] += cur[v].x;
+        r[4 * v + 1] += cur[v].y;
+        r[4 * v + 2] += cur[v].z;
+        r[4 * v + 3] += cur[v].w;
+      }
+    }
+    tmem_st_32x32b_x32(t_row + uint32_t(c * 32), r);
+  }
+  tmem_st_wait();
 }
 
 // Teardown of a CTA pair whose pipeline gave up, run by one thread of the even CTA after both CTAs have stopped

@@ -25,6 +25,13 @@
  *                         that delivered it).  Copies A in, computes, copies C out and returns when C
  *                         is complete, like VT_HOST.
  *   - One host thread per device at a time; different devices may be driven concurrently.
+ *   - All calls on one device must be ordered with one another on the GPU (the same stream, or streams joined
+ *     by events): they share the device's status word, arrival counters and scratch memory (K-split partial
+ *     tiles, lo parts, the int8 kernel's partial accumulators), so two calls whose kernels could overlap
+ *     race on them.
+ *   - A VT_DEVICE call that needs more scratch memory than any call before it on that device grows the
+ *     workspace, which synchronises the device and allocates; issue the largest shape once before
+ *     latency-critical work or stream capture.
  */
 #ifndef VERITAC_B200_H
 #define VERITAC_B200_H
@@ -148,6 +155,12 @@ int vt_i8_tile_program(int dev, const int8_t* A, int64_t a_elems, const int8_t* 
 int vt_sgemm(int dev, const float* A, const float* B, float* C, int64_t M, int64_t N, int64_t K, int variant,
              int where, void* stream);
 
+/* The kernel VT_SGEMM_AUTO picks on `dev` for an M x N x K product of 16-byte-aligned device operands: a
+ * VT_SGEMM_* value other than AUTO, or a negative VT_ERR_* code.  Nothing is launched.  It lets a caller that
+ * carries a schedule of its own (tile sizes recovered from a loop nest, specializations/cpu_gemm/runner.py:111-190)
+ * see what the library would do before overriding it with an explicit variant. */
+int vt_sgemm_auto_variant(int dev, int64_t M, int64_t N, int64_t K);
+
 /* The skinny fp32 GEMM (M <= 16, N % 4 == 0, device pointers only) for hosts that must not let this
  * library allocate: it calls no cudaMalloc / cudaFree and no allocating library routine.  It has no
  * counterpart in the reference; it exists for embedders whose own pool (a framework's caching
@@ -158,7 +171,8 @@ int vt_sgemm(int dev, const float* A, const float* B, float* C, int64_t M, int64
  * library, until exit).  Shapes whose partial tiles need more are refused with VT_ERR_UNSUPPORTED and
  * a message giving both sizes; vt_sgemm serves those.
  *   - The first call on a device looks up the array's device address (with that device current);
- *     make that first call before starting any stream capture.
+ *     make that first call before starting any stream capture.  The calling thread's current device
+ *     is the same after the call as before it.
  *   - All calls share the one array: two calls whose kernels can overlap on the GPU (different
  *     streams, no ordering between them) race on it.  Calls on one stream are safe.  Nothing in
  *     the array has to be cleared between calls.

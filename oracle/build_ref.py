@@ -1,7 +1,8 @@
 """TEST INFRASTRUCTURE — builds artefacts of the *reference itself* into oracle/_ref/ (git-ignored).
 
 The reference's cpu_gemm path is a Python emitter whose product is generated OpenMP C.  Where the
-reference tree is present (the directory REFERENCE_ROOT names) this script imports its
+reference tree is present (the directory REFERENCE_ROOT names, else a directory `reference` beside this
+repository) this script imports its
 unmodified emitter (CodeGen/emit_c.py, CodeGen/lower.py), has it print `matmul()` for the 256^3 nest —
 untuned, and after the schedule its README quotes (tactics applied by oracle/loopnest_oracle.py,
 because the Lean CLI that applies them cannot be built here) — and compiles each text to a shared
@@ -18,7 +19,7 @@ from pathlib import Path
 
 HERE = Path(__file__).resolve().parent
 OUT = HERE / "_ref"
-REF = Path(os.environ.get("REFERENCE_ROOT", "/root/reference"))
+REF = Path(os.environ.get("REFERENCE_ROOT") or HERE.parents[1] / "reference")
 SHAPES = [(256, 256, 256), (512, 512, 512)]
 
 

@@ -1,7 +1,8 @@
 """Regenerates tests/golden/gemmini.json, cpu_gemm.json, learned_streams.json and schedule_ir.json from the
 reference tree.
 
-Needs the reference checkout (the directory REFERENCE_ROOT names) — it is imported and its
+Needs the reference checkout (the directory REFERENCE_ROOT names, else a directory `reference` beside this
+repository) — it is imported and its
 recorded evidence files are read — so it runs only where that tree exists; the fixtures it writes are
 committed and are what the tests read.  The reference's Lean plan checker cannot be built here; its
 documented override VERITAC_GEMMINI_CHECK_BIN (reference specializations/gemmini_gemm/backend.py:
@@ -21,7 +22,7 @@ from pathlib import Path
 
 HERE = Path(__file__).resolve().parent
 REPO = HERE.parents[1]
-REF = Path(os.environ.get("REFERENCE_ROOT", "/root/reference"))
+REF = Path(os.environ.get("REFERENCE_ROOT") or REPO.parent / "reference")
 
 os.environ["VERITAC_GEMMINI_CHECK_BIN"] = str(REPO / "oracle" / "gemmini_check_stub.py")
 sys.dont_write_bytecode = True

@@ -248,3 +248,57 @@ def test_batched_generator_argument_checks():
     bad_plan = dict(plan, k=33)
     with pytest.raises(ValueError):
         lowering.gen_batched_reuse_b(bad_plan, 1)
+
+
+def _strided_stream(stride_a, stride_b):
+    """The baseline stream of a 32 x 32 x 16 plan with the load strides of A and B replaced and every mvin
+    moved to the start of its buffer (or one tile along, for B's second column block), so that strides of 0, 1
+    and more than a row all stay inside the buffers.  Not a GEMM any more: it runs as a tile program."""
+    plan = g.make_plan(32, 32, 16, "baseline")
+    cmds = g.gen_commands(plan)
+    for c in cmds:
+        if c.kind == "config_ld" and c.slot == 0:
+            c.stride_bytes = stride_a
+        elif c.kind == "config_ld" and c.slot == 1:
+            c.stride_bytes = stride_b
+        elif c.kind == "mvin" and c.buf == "A":
+            c.offset = 0
+        elif c.kind == "mvin" and c.buf == "B":
+            c.offset = 16 if c.offset % 32 else 0
+    return plan, cmds
+
+
+def _numpy_tile_program(A, a_elems, B, b_elems, C, c_elems, lda, ldb, ldc, c_off, term_begin, a_off, b_off, **kw):
+    """What vt_i8_tile_program computes, stated in numpy: tile t = sum of A-tile x B-tile products, each tile
+    16 rows `stride` apart."""
+    import numpy as np
+    A, B = np.asarray(A, dtype=np.int64), np.asarray(B, dtype=np.int64)
+    rows = np.arange(16)[:, None]
+    cols = np.arange(16)[None, :]
+    for t, off in enumerate(c_off):
+        acc = np.zeros((16, 16), dtype=np.int64)
+        for j in range(term_begin[t], term_begin[t + 1]):
+            acc += A[a_off[j] + rows * lda + cols] @ B[b_off[j] + rows * ldb + cols]
+        C[off + rows * ldc + cols] = acc.astype(np.int32)
+
+
+@pytest.mark.parametrize("stride_a,stride_b", [(0, 32), (1, 32), (16, 0), (16, 1), (33, 32), (16, 31), (0, 0)])
+def test_load_strides_reach_the_tile_program_unchanged(stride_a, stride_b):
+    """config_ld strides of 0 (one row repeated), 1 (overlapping rows) and more than a row are legal in the
+    reference's interpreter (specializations/gemmini_gemm/backend.py:455-459, stride_bytes >= 0); the replay must
+    hand exactly those strides to the tile executor.  The executor is replaced by its numpy statement here."""
+    import numpy as np
+    import gemmini_oracle as go
+    plan, cmds = _strided_stream(stride_a, stride_b)
+    A, B = g.deterministic_inputs(32, 32, 16, 9)
+    want, want_stats = go.interpret(cmds, plan, A, B)
+    seen = {}
+
+    def fake(*args, **kw):
+        seen["lda"], seen["ldb"] = args[6], args[7]
+        return _numpy_tile_program(*args, **kw)
+
+    with mock.patch("veritac_b200._native.i8_tile_program", side_effect=fake):
+        got, stats = g.run_commands(cmds, plan, A, B)
+    assert (seen["lda"], seen["ldb"]) == (stride_a, stride_b)
+    assert got == want and stats == want_stats

@@ -408,3 +408,16 @@ def test_host_buffers_8192_cubed_through_the_corner_pipeline(native):
     assert torch.equal(C[rows].to(torch.int64), (A[rows].double() @ B.double()).to(torch.int64))
     ones = B.to(torch.int64).sum(dim=1)
     assert torch.equal(C.to(torch.int64).sum(dim=1), (A.to(torch.float64) @ ones.to(torch.float64)).to(torch.int64))
+
+
+@pytest.mark.parametrize("stride_a,stride_b", [(0, 32), (1, 32), (16, 0), (16, 1), (33, 32), (16, 31), (0, 0)])
+def test_load_strides_zero_one_and_beyond_a_row(native, g, stride_a, stride_b):
+    """config_ld strides the reference's interpreter accepts (any stride_bytes >= 0): 0 repeats one row, 1 makes
+    the rows of a tile overlap, more than a row skips rows.  The tile-program kernel must read exactly those rows;
+    checked against the sequential interpreter."""
+    from test_gemmini_host import _strided_stream
+    plan, cmds = _strided_stream(stride_a, stride_b)
+    A, B = g.deterministic_inputs(32, 32, 16, 9)
+    want, want_stats = go.interpret(cmds, plan, A, B)
+    got, stats = g.run_commands(cmds, plan, A, B)
+    assert got == want and stats == want_stats

@@ -25,15 +25,28 @@ def test_static_scratch_matches_workspace_path_two_calls_in_a_row(native):
 
     st = native.torch_stream()
     gen = torch.Generator(device="cuda").manual_seed(4242)
+    cases = []
     for (m, n, k) in ((16, 8192, 8192), (7, 1024, 4096)):
         A = torch.rand((m, k), device="cuda", generator=gen) * 2 - 1
         B = torch.rand((k, n), device="cuda", generator=gen) * 2 - 1
         want = torch.full((m, n), float("nan"), device="cuda")
         native.sgemm(A, B, want, m, n, k, variant=native.VT_SGEMM_SKINNY, where=native.VT_DEVICE, stream=st)
         native.sync(0, st)
-        got = torch.full((m, n), float("nan"), device="cuda")
+        cases.append((m, n, k, A, B, want, torch.full((m, n), float("nan"), device="cuda")))
+    # The point of the entry point: it takes no device memory.  After one warm-up call (the first call on a
+    # device looks up the array's address and loads the kernels), the free memory the driver reports must be
+    # the same before and after the two calls; every tensor they use exists already.
+    warm = torch.zeros((1, 64), device="cuda")
+    native.sgemm_skinny_static_scratch(torch.zeros((1, 64), device="cuda"), torch.zeros((64, 64), device="cuda"), warm,
+                                       1, 64, 64, stream=st)
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info()
+    for (m, n, k, A, B, want, got) in cases:
         native.sgemm_skinny_static_scratch(A, B, got, m, n, k, stream=st)
-        torch.cuda.synchronize()
+    torch.cuda.synchronize()
+    free_after, _ = torch.cuda.mem_get_info()
+    assert free_after == free_before, "the allocation-free entry point changed the device's free memory"
+    for (m, n, k, A, B, want, got) in cases:
         assert not torch.isnan(got).any()
         assert relfro(got, want) <= TOL
         assert torch.equal(got, want)

@@ -55,6 +55,7 @@ SIGNATURES = {
     "vt_i8_tile_program": (c_int, [c_int, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int64, c_int64,
                                    c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p]),
     "vt_sgemm": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_int, c_void_p]),
+    "vt_sgemm_auto_variant": (c_int, [c_int, c_int64, c_int64, c_int64]),
     "vt_sgemm_skinny_static_scratch": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,
                                                c_void_p]),
     "vt_test_set_wait_hooks": (c_int, [c_int, c_int64, c_int]),
@@ -154,6 +155,11 @@ def i8_tile_program(A, a_elems, B, b_elems, C, c_elems, lda, ldb, ldc, c_off, te
 def sgemm(A, B, C, M: int, N: int, K: int, *, dev: int = 0, variant: int = VT_SGEMM_AUTO, where: int = VT_HOST,
           stream: int = 0) -> None:
     check(lib().vt_sgemm(dev, _ptr(A), _ptr(B), _ptr(C), M, N, K, variant, where, stream))
+
+
+def sgemm_auto_variant(M: int, N: int, K: int, *, dev: int = 0) -> int:
+    """The VT_SGEMM_* kernel the automatic choice takes for this shape (aligned device operands)."""
+    return check(lib().vt_sgemm_auto_variant(dev, M, N, K))
 
 
 SKINNY_STATIC_SCRATCH_BYTES = 8 << 20

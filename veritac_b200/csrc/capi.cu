@@ -1,7 +1,6 @@
 // extern "C" entry points declared in include/veritac_b200.h: argument checking in the
 // reference's plan domain, host<->device staging for host-pointer calls, launch, status.
 #include <cstring>
-#include <vector>
 
 #include "runtime.h"
 
@@ -199,6 +198,49 @@ int sgemm_tf32x3_from_host(DeviceCtx* c, const float* A, const float* B, float* 
   return ctx_check_status(c, c->stream);
 }
 
+// The automatic choice of fp32 kernel for device operands dA, dB, dC (only their alignment is looked at).
+// Returns a VT_SGEMM_* value other than AUTO; VT_SGEMM_AUTO itself stands for "the FFMA tile kernels, whichever
+// sgemm_tile_choice picks".
+int choose_sgemm_variant(DeviceCtx* c, const float* dA, const float* dB, const float* dC, int64_t M, int64_t N, int64_t K) {
+  const bool skinny_ok = M <= 16 && N % 4 == 0 &&
+                         ((reinterpret_cast<uintptr_t>(dB) | reinterpret_cast<uintptr_t>(dC)) & 15) == 0;
+  // The streaming kernels count arrivals per 128-wide slab in kTicketCount counters: more slabs than that go to
+  // the tile kernels.
+  const int64_t max_streamed = int64_t(kTicketCount) * 128;
+  if (skinny_ok && N <= max_streamed && K >= 512 && (N >= 512 || (N >= 128 && double(N) * double(K) >= 1.0e6)))
+    return VT_SGEMM_SKINNY_TF32X3;
+  // Few rows against a large B: B is the traffic, and the row-panel kernel streams it once per 128 rows of A.
+  // (measured against the tile kernels and the 3xTF32 pair kernel: ahead from 1 Mi elements of B up to 32 rows,
+  // from 4 Mi up to 256 rows, from 16 Mi up to 384 rows).
+  if (M > 16 && M <= 3 * SKINNY_UMMA_MAX_ROWS && N >= 128 && K >= 512 &&
+      double(N) * double(K) >= (M <= 32 ? 1.0e6 : M <= 2 * SKINNY_UMMA_MAX_ROWS ? 4.0e6 : 1.6e7) &&
+      sgemm_skinny_umma_supported(dA, dB, dC, 1, N, K))
+    return VT_SGEMM_PANEL_TF32X3;
+  // Few columns against a large A: the mirror image (measured ahead of the tile kernels and the 3xTF32 pair kernel
+  // from 4 Mi elements of A up to 32 columns, from 12 Mi up to 64, from 16 Mi up to 128; two panels of 128 columns
+  // are level with the pair kernel and stay there).
+  if (N <= SKINNY_UMMA_MAX_ROWS && K >= 256 &&
+      double(M) * double(K) >= (N <= 32 ? 4.0e6 : N <= 64 ? 1.2e7 : 1.6e7) && sgemm_tall_umma_supported(dA, dB, dC, M, N, K))
+    return VT_SGEMM_TALL_TF32X3;
+  // Large products go to the tensor cores (3xTF32, measured ~1e-6 relative Frobenius error at any K) when that
+  // is clearly faster than the best FFMA tile kernel.  Its time is modelled as two launches (6 us), the pass that
+  // writes the lo parts and the write of C (8 bytes per element of A and B, 4 per element of C, at ~5.5 TB/s) and
+  // K x 34 ns for every wave of 256x256 tiles over the 74 CTA pairs (8192^3: 4.1 ms).  Below ~0.5 GFLOP the two
+  // passes cost more than they save.
+  if (M >= 128 && N >= 16 && K >= 64 && double(M) * double(N) * double(K) >= 5.0e8 &&
+      sgemm_tf32x3_supported(dA, dB, dC, M, N, K)) {
+    int tile_variant;
+    const double t_tile = sgemm_tile_choice(dA, dB, dC, M, N, K, c->sm_count, &tile_variant);
+    const double pair_tiles = double((M + 255) / 256) * double((N + 255) / 256);
+    const double pairs = c->sm_count / 2;
+    const double waves = pair_tiles <= pairs ? 1.0 : double(int64_t((pair_tiles + pairs - 1) / pairs));
+    const double t_tc = 6.0e-6 + ((double(M) * K + double(K) * N) * 8.0 + double(M) * N * 4.0) / 5.5e12 +
+                        waves * double(K) * 3.4e-8;
+    if (t_tc < 0.9 * t_tile) return VT_SGEMM_TF32X3;
+  }
+  return VT_SGEMM_AUTO;
+}
+
 }  // namespace
 
 extern "C" {
@@ -260,7 +302,10 @@ int vt_i8_tile_program(int dev, const int8_t* A, int64_t a_elems, const int8_t* 
   if (!A || !B || !C || !c_off || !term_begin) return fail(VT_ERR_INVALID, "null operand");
   if (where != VT_HOST && where != VT_DEVICE) return fail(VT_ERR_INVALID, "where must be VT_HOST or VT_DEVICE");
   if (n_tiles < 1 || n_tiles > 0x7fffffffLL) return fail(VT_ERR_PROGRAM, "tile count out of range");
-  if (lda < 16 || ldb < 16 || ldc < 16) return fail(VT_ERR_PROGRAM, "row strides must be >= 16");
+  // Operand strides are the stream's config_ld strides: 0 repeats one row, 1..15 makes rows overlap (the reference
+  // interpreter takes any stride >= 0); output tiles must not fold onto themselves.
+  if (lda < 0 || ldb < 0) return fail(VT_ERR_PROGRAM, "operand row strides must be >= 0");
+  if (ldc < 16) return fail(VT_ERR_PROGRAM, "output row stride must be >= 16");
   if (term_begin[0] != 0) return fail(VT_ERR_PROGRAM, "term_begin[0] must be 0");
   const int64_t n_terms = term_begin[n_tiles];
   if (n_terms > 0 && (!a_off || !b_off)) return fail(VT_ERR_INVALID, "null term arrays");
@@ -279,20 +324,23 @@ int vt_i8_tile_program(int dev, const int8_t* A, int64_t a_elems, const int8_t* 
   if (!c) return VT_ERR_CUDA;
   cudaStream_t s = where == VT_HOST ? c->stream : pick_stream(c, stream);
 
-  // Program tables: one packed upload into workspace slot 3.
+  // Program tables: packed into the context's pinned staging block (grow-only, reused once the previous upload
+  // from it has been consumed), then one asynchronous upload into workspace slot 3.  Nothing here waits for the
+  // caller's stream.
   const size_t n_c = size_t(n_tiles), n_tb = size_t(n_tiles) + 1, n_t = size_t(n_terms);
   const size_t table_elems = n_c + n_tb + 2 * n_t;
-  std::vector<int64_t> packed(table_elems);
-  std::memcpy(packed.data(), c_off, n_c * 8);
-  std::memcpy(packed.data() + n_c, term_begin, n_tb * 8);
+  int64_t* packed = static_cast<int64_t*>(ctx_pinned_staging(c, table_elems * 8));
+  if (!packed) return VT_ERR_CUDA;
+  std::memcpy(packed, c_off, n_c * 8);
+  std::memcpy(packed + n_c, term_begin, n_tb * 8);
   if (n_t) {
-    std::memcpy(packed.data() + n_c + n_tb, a_off, n_t * 8);
-    std::memcpy(packed.data() + n_c + n_tb + n_t, b_off, n_t * 8);
+    std::memcpy(packed + n_c + n_tb, a_off, n_t * 8);
+    std::memcpy(packed + n_c + n_tb + n_t, b_off, n_t * 8);
   }
   int64_t* d_tab = static_cast<int64_t*>(ctx_workspace(c, 3, table_elems * 8));
   if (!d_tab) return VT_ERR_CUDA;
-  VT_CUDA(cudaMemcpyAsync(d_tab, packed.data(), table_elems * 8, cudaMemcpyHostToDevice, s));
-  VT_CUDA(cudaStreamSynchronize(s));  // `packed` is pageable and dies with this frame
+  VT_CUDA(cudaMemcpyAsync(d_tab, packed, table_elems * 8, cudaMemcpyHostToDevice, s));
+  VT_CUDA(cudaEventRecord(c->staging_consumed, s));
 
   const int8_t* dA = A;
   const int8_t* dB = B;
@@ -349,37 +397,7 @@ int vt_sgemm(int dev, const float* A, const float* B, float* C, int64_t M, int64
   }
   const bool skinny_ok = M <= 16 && N % 4 == 0 &&
                          ((reinterpret_cast<uintptr_t>(dB) | reinterpret_cast<uintptr_t>(dC)) & 15) == 0;
-  if (variant == VT_SGEMM_AUTO && skinny_ok && K >= 512 && (N >= 512 || (N >= 128 && double(N) * double(K) >= 1.0e6)))
-    variant = VT_SGEMM_SKINNY_TF32X3;
-  // Few rows against a large B: B is the traffic, and the row-panel kernel streams it once per 128 rows of A.
-  // (measured against the tile kernels and the 3xTF32 pair kernel: ahead from 1 Mi elements of B up to 32 rows,
-  // from 4 Mi up to 256 rows, from 16 Mi up to 384 rows).
-  if (variant == VT_SGEMM_AUTO && M > 16 && M <= 3 * SKINNY_UMMA_MAX_ROWS && N >= 128 && K >= 512 &&
-      double(N) * double(K) >= (M <= 32 ? 1.0e6 : M <= 2 * SKINNY_UMMA_MAX_ROWS ? 4.0e6 : 1.6e7) &&
-      sgemm_skinny_umma_supported(dA, dB, dC, 1, N, K))
-    variant = VT_SGEMM_PANEL_TF32X3;
-  // Few columns against a large A: the mirror image (measured ahead of the tile kernels and the 3xTF32 pair kernel
-  // from 4 Mi elements of A up to 32 columns, from 12 Mi up to 64, from 16 Mi up to 128; two panels of 128 columns
-  // are level with the pair kernel and stay there).
-  if (variant == VT_SGEMM_AUTO && N <= SKINNY_UMMA_MAX_ROWS && K >= 256 &&
-      double(M) * double(K) >= (N <= 32 ? 4.0e6 : N <= 64 ? 1.2e7 : 1.6e7) && sgemm_tall_umma_supported(dA, dB, dC, M, N, K))
-    variant = VT_SGEMM_TALL_TF32X3;
-  // Large products go to the tensor cores (3xTF32, measured ~1e-6 relative Frobenius error at any K) when that
-  // is clearly faster than the best FFMA tile kernel.  Its time is modelled as two launches (6 us), the pass that
-  // writes the lo parts and the write of C (8 bytes per element of A and B, 4 per element of C, at ~5.5 TB/s) and
-  // K x 34 ns for every wave of 256x256 tiles over the 74 CTA pairs (8192^3: 4.1 ms).  Below ~0.5 GFLOP the two
-  // passes cost more than they save.
-  if (variant == VT_SGEMM_AUTO && M >= 128 && N >= 16 && K >= 64 && double(M) * double(N) * double(K) >= 5.0e8 &&
-      sgemm_tf32x3_supported(dA, dB, dC, M, N, K)) {
-    int tile_variant;
-    const double t_tile = sgemm_tile_choice(dA, dB, dC, M, N, K, c->sm_count, &tile_variant);
-    const double pair_tiles = double((M + 255) / 256) * double((N + 255) / 256);
-    const double pairs = c->sm_count / 2;
-    const double waves = pair_tiles <= pairs ? 1.0 : double(int64_t((pair_tiles + pairs - 1) / pairs));
-    const double t_tc = 6.0e-6 + ((double(M) * K + double(K) * N) * 8.0 + double(M) * N * 4.0) / 5.5e12 +
-                        waves * double(K) * 3.4e-8;
-    if (t_tc < 0.9 * t_tile) variant = VT_SGEMM_TF32X3;
-  }
+  if (variant == VT_SGEMM_AUTO) variant = choose_sgemm_variant(c, dA, dB, dC, M, N, K);
   int rc;
   if (variant == VT_SGEMM_TALL_TF32X3) {
     if (!sgemm_tall_umma_supported(dA, dB, dC, M, N, K))
@@ -465,6 +483,18 @@ int vt_sgemm(int dev, const float* A, const float* B, float* C, int64_t M, int64
     return ctx_check_status(c, s);
   }
   return VT_OK;
+}
+
+int vt_sgemm_auto_variant(int dev, int64_t M, int64_t N, int64_t K) {
+  clear_error_text();
+  if (M < 1 || N < 1 || K < 1) return fail(VT_ERR_INVALID, "dimensions must be positive");
+  if (M > 0x7fffffffLL || N > 0x7fffffffLL || K > 0x7fffffffLL) return fail(VT_ERR_INVALID, "dimension overflows int");
+  DeviceCtx* c = ctx_for(dev);
+  if (!c) return VT_ERR_CUDA;
+  const float* aligned = reinterpret_cast<const float*>(uintptr_t(256));   // never dereferenced
+  int variant = choose_sgemm_variant(c, aligned, aligned, aligned, M, N, K);
+  if (variant == VT_SGEMM_AUTO) sgemm_tile_choice(aligned, aligned, aligned, M, N, K, c->sm_count, &variant);
+  return variant;
 }
 
 int vt_test_set_wait_hooks(int dev, int64_t wait_limit_cycles, int i8_stop_fill) {

@@ -91,6 +91,7 @@ DeviceCtx* ctx_for(int dev) {
   CTX_TRY(cudaMemset(c->i8_flags, 0, size_t(c->i8_flag_count) * sizeof(int)));
   CTX_TRY(cudaMalloc(&c->i8_partials, size_t(c->sm_count) * 128 * 256 * sizeof(int32_t)));
   for (auto& ev : c->ev) CTX_TRY(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
+  CTX_TRY(cudaEventCreateWithFlags(&c->staging_consumed, cudaEventDisableTiming));
 #undef CTX_TRY
   if (!g_encode) {
     void* fn = nullptr;
@@ -123,6 +124,23 @@ void* ctx_workspace(DeviceCtx* c, int slot, size_t bytes) {
   return c->ws[slot];
 }
 
+void* ctx_pinned_staging(DeviceCtx* c, size_t bytes) {
+  if (bytes == 0) bytes = 256;
+  cudaError_t e = cudaEventSynchronize(c->staging_consumed);   // a never-recorded event is complete
+  if (e == cudaSuccess && c->staging_bytes < bytes) {
+    if (c->staging) e = cudaFreeHost(c->staging);
+    c->staging = nullptr;
+    c->staging_bytes = 0;
+    if (e == cudaSuccess) e = cudaMallocHost(&c->staging, bytes);
+    if (e == cudaSuccess) c->staging_bytes = bytes;
+  }
+  if (e != cudaSuccess) {
+    fail_cuda(e, "pinned staging block");
+    return nullptr;
+  }
+  return c->staging;
+}
+
 int ctx_check_status(DeviceCtx* c, cudaStream_t s) {
   VT_CUDA(cudaMemcpyAsync(c->status_host, c->status, sizeof(int), cudaMemcpyDeviceToHost, s));
   VT_CUDA(cudaStreamSynchronize(s));
@@ -148,6 +166,8 @@ void ctx_destroy_all() {
       if (c->ws[i]) cudaFree(c->ws[i]);
     if (c->status) cudaFree(c->status);
     if (c->status_host) cudaFreeHost(c->status_host);
+    if (c->staging) cudaFreeHost(c->staging);
+    if (c->staging_consumed) cudaEventDestroy(c->staging_consumed);
     if (c->tickets) cudaFree(c->tickets);
     if (c->i8_flags) cudaFree(c->i8_flags);
     if (c->i8_partials) cudaFree(c->i8_partials);

@@ -40,6 +40,10 @@ struct DeviceCtx {
   void* ws[4] = {nullptr, nullptr, nullptr, nullptr};
   size_t ws_bytes[4] = {0, 0, 0, 0};
   cudaEvent_t ev[8] = {};
+  // pinned host block for small tables that go to the device asynchronously (tile programs)
+  void* staging = nullptr;
+  size_t staging_bytes = 0;
+  cudaEvent_t staging_consumed = nullptr;   // recorded after the last upload from `staging`
   uint32_t func_attr_mask = 0;         // which kernels already had their shared-memory opt-in set here
 };
 
@@ -55,6 +59,9 @@ void ctx_destroy_all();
 DeviceCtx* ctx_for(int dev);
 // Grow-only workspace slot; returns nullptr (error set) on allocation failure.
 void* ctx_workspace(DeviceCtx* c, int slot, size_t bytes);
+// The context's pinned staging block, at least `bytes` long, free to overwrite (waits for the upload that last
+// read it); nullptr + error set on failure.
+void* ctx_pinned_staging(DeviceCtx* c, size_t bytes);
 // Reads and clears the device status word after the stream has drained.
 int ctx_check_status(DeviceCtx* c, cudaStream_t s);
 void count_launch(int n = 1);

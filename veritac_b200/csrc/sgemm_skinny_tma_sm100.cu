@@ -265,7 +265,7 @@ void sgemm_skinny_tma_plan(int64_t N, int64_t K, int sm_count, int* ctas, int* s
 }
 
 bool sgemm_skinny_tma_supported(const float* B, const float* C, int64_t M, int64_t N, int64_t K) {
-  return M >= 1 && M <= 16 && N % 4 == 0 && N >= 4 && K >= 1 && N < (1LL << 31) && K < (1LL << 31) &&
+  return M >= 1 && M <= 16 && N % 4 == 0 && N >= 4 && N <= int64_t(kTicketCount) * SKINNY_COLS && K >= 1 && K < (1LL << 31) &&
          ((reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(C)) & 15) == 0;
 }
 

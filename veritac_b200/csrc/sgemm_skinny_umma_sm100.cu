@@ -645,7 +645,9 @@ void sgemm_tall_umma_plan(int64_t M, int64_t N, int64_t K, int sm_count, int* ma
 
 bool sgemm_tall_umma_supported(const float* A, const float* B, const float* C, int64_t M, int64_t N, int64_t K) {
   (void)B;
-  return N >= 4 && N % 4 == 0 && M >= 1 && K % 4 == 0 && K >= 4 && M < (1LL << 31) && K < (1LL << 31) && N < (1LL << 31) &&
+  // one arrival counter per 128-row slab of A
+  return N >= 4 && N % 4 == 0 && M >= 1 && M <= int64_t(kTicketCount) * SKINNY_COLS && K % 4 == 0 && K >= 4 &&
+         K < (1LL << 31) && N < (1LL << 31) &&
          ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(C)) & 15) == 0;
 }
 
@@ -664,8 +666,9 @@ int launch_sgemm_tall_umma(DeviceCtx* c, const float* A, const float* B, float* 
 }
 
 bool sgemm_skinny_umma_supported(const float* A, const float* B, const float* C, int64_t M, int64_t N, int64_t K) {
-  return M >= 1 && M <= SKINNY_UMMA_MAX_ROWS && N % 4 == 0 && N >= 4 && K % 4 == 0 && K >= 4 && N < (1LL << 31) &&
-         K < (1LL << 31) &&
+  // one arrival counter per 128-column slab of B
+  return M >= 1 && M <= SKINNY_UMMA_MAX_ROWS && N % 4 == 0 && N >= 4 && N <= int64_t(kTicketCount) * SKINNY_COLS &&
+         K % 4 == 0 && K >= 4 && K < (1LL << 31) &&
          ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(C)) & 15) == 0;
 }
 

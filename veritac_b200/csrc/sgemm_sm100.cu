@@ -19,6 +19,7 @@
 //       8-row slices of each 32-row stage, keep 16x4 accumulators per thread, and fold through shared memory.  With a K split the
 //       per-split partial tiles go to scratch memory and a second kernel sums them in split order
 //       (deterministic, no atomics).
+#include <atomic>
 #include <mutex>
 
 #include "ptx_sm100.cuh"
@@ -638,7 +639,7 @@ constexpr size_t kStaticScratchFloats = VT_SKINNY_STATIC_SCRATCH_BYTES / sizeof(
 static __device__ __align__(256) float g_skinny_static_scratch[kStaticScratchFloats];
 
 struct StaticScratchSlot {
-  bool ready = false;
+  std::atomic<bool> ready{false};   // published with release once ptr and sm_count are in place
   float* ptr = nullptr;   // device address of g_skinny_static_scratch on this device
   int sm_count = 0;
 };
@@ -661,21 +662,35 @@ extern "C" int vt_sgemm_skinny_static_scratch(int dev, const float* A, const flo
   if (N > 0x7fffffffLL || K > 0x7fffffffLL) return fail(VT_ERR_INVALID, "dimension overflows int");
   if ((reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(C)) & 15)
     return fail(VT_ERR_INVALID, "B and C must be 16-byte aligned");
-  VT_CUDA(cudaSetDevice(dev));
+  // The launch below goes to `dev`; the caller's current device is put back before returning.
+  struct DeviceGuard {
+    int prev = -1;
+    ~DeviceGuard() { if (prev >= 0) cudaSetDevice(prev); }
+  } guard;
+  int current = -1;
+  VT_CUDA(cudaGetDevice(&current));
+  if (current != dev) {
+    VT_CUDA(cudaSetDevice(dev));
+    guard.prev = current;
+  }
   StaticScratchSlot* slot = &g_static_slot[dev];
-  if (!slot->ready) {
+  if (!slot->ready.load(std::memory_order_acquire)) {
     // Set-up, once per device, with that device current.  In host code the array's name is only
     // a stand-in for the symbol; the address kernels can use comes from the runtime.
     std::lock_guard<std::mutex> lock(g_static_mu);
-    if (!slot->ready) {
+    if (!slot->ready.load(std::memory_order_acquire)) {
+      int major = 0, sms = 0;
+      VT_CUDA(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev));
+      if (major != 10)
+        return fail(VT_ERR_UNSUPPORTED, "device %d is compute capability %d.x; this library is built for sm_100a only", dev,
+                    major);
       float* p = nullptr;
       VT_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_skinny_static_scratch));
-      int sms = 0;
       VT_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
       if (!p || sms < 1) return fail(VT_ERR_CUDA, "static scratch set-up returned no address");
       slot->ptr = p;
       slot->sm_count = sms;
-      slot->ready = true;
+      slot->ready.store(true, std::memory_order_release);
     }
   }
   int ksplit = 1;

@@ -15,6 +15,12 @@ generator in this module and in lowering.py does), tile by tile otherwise.  Unde
 k*16384 <= 2^31-1 no accumulator can leave int32 (VeriTac/GemminiExact.lean:62-75), so the GPU's
 summation order is unobservable and results are bit-identical to the interpreter's.
 
+Carried over as they stand in the reference, because callers and the Lean side compare against their
+exact verdicts and texts: `validate_plan`, `gemmini_check`, `optimize`, the command classes with their
+`to_dict` forms, and the refusal strings raised during the replay.  Everything that executes — the symbolic
+replay's provenance tracking, `_tile_terms`, `_plain_gemm_raster`, `_waves`, `_execute`, `run_plan` and the
+numpy paths — is this package's own.
+
 Not carried over: the Gemmini C / RV64 byte emission and the program-certificate plumbing of the
 reference (its backend.py:617-1055), which stay with the reference.
 """
@@ -576,7 +582,9 @@ def _execute(plan, A, B, tiles, raster_hint=None, batch_rows=1):
                 begin.append(len(a_off))
                 idx = off + np.arange(DIM)[:, None] * stride + np.arange(DIM)[None, :]
                 cover[idx.reshape(-1)] = True
-            nv.i8_tile_program(A, A.size, B, B.size, C, C.size, max(lda or DIM, DIM), max(ldb or DIM, DIM), ldc,
+            # Load strides are whatever config_ld set: 0 repeats one row, 1..15 gives overlapping rows (the
+            # reference accepts any stride_bytes >= 0, backend.py:455-459); DIM only stands in when no tile has terms.
+            nv.i8_tile_program(A, A.size, B, B.size, C, C.size, DIM if lda is None else lda, DIM if ldb is None else ldb, ldc,
                                np.array(c_off, dtype=np.int64), np.array(begin, dtype=np.int64),
                                np.array(a_off or [0], dtype=np.int64), np.array(b_off or [0], dtype=np.int64),
                                where=nv.VT_HOST)

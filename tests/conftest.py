@@ -25,6 +25,12 @@ for p in (str(REPO), str(REPO / "oracle")):
 if not os.access(STUB, os.X_OK):
     os.chmod(STUB, os.stat(STUB).st_mode | stat.S_IXUSR | stat.S_IXGRP | stat.S_IXOTH)
 os.environ["VERITAC_GEMMINI_CHECK_BIN"] = str(STUB)
+# Likewise the tactic verifier (`veritac --json`): the demo that drives it takes the executable's path from
+# VERITAC_BIN, which tests point at the oracle's restatement of the four tactics.
+CLI_STUB = REPO / "oracle" / "veritac_cli_stub.py"
+if not os.access(CLI_STUB, os.X_OK):
+    os.chmod(CLI_STUB, os.stat(CLI_STUB).st_mode | stat.S_IXUSR | stat.S_IXGRP | stat.S_IXOTH)
+os.environ["VERITAC_BIN"] = str(CLI_STUB)
 
 
 def pytest_configure(config):

@@ -166,3 +166,40 @@ def test_demo_scheduled_nest_is_what_the_tactics_produce():
         assert gemm_demo.readme_scheduled_stmt(M, K, N) == lo.apply_tactics(lo.matmul_stmt(M, K, N), lo.README_SCHEDULE)
     with pytest.raises(ValueError):
         gemm_demo.readme_scheduled_stmt(48, 32, 32)
+
+
+def test_agent_loop_applies_verified_tactics_and_skips_refused_ones(golden_cpu_gemm, tmp_path, monkeypatch):
+    """The verify-and-apply loop of the mock LLM demo (reference examples/llm_gemm_demo.py:260-333) against the
+    tactic verifier's command-line contract (`veritac --json`, Main.lean:697-745; the stub restates the tactics).
+    The fixed five-tactic proposal list turns the naive nest into the README-scheduled one; a proposal the verifier
+    refuses leaves the nest as it was and the walk goes on; without the executable the loop fails closed."""
+    from veritac_b200.examples import llm_gemm_demo as demo
+    from veritac_b200.examples.gemm_demo import naive_matmul_stmt, readme_scheduled_stmt
+    from veritac_b200.specializations.cpu_gemm.lower import parse_stmt
+    from veritac_b200.specializations.cpu_gemm.recognise import recognise_matmul
+    from veritac_b200.specializations.cpu_gemm.runner import schedule_hint
+
+    lines = []
+    schedule, final, refused = demo.run_agent(naive_matmul_stmt(64, 64, 64), demo.MockProposer(demo.mock_schedule()),
+                                              log=lines.append)
+    assert [t["kind"] for t in schedule] == ["tile", "tile", "reorder", "vectorize", "parallel"] and not refused
+    assert final == readme_scheduled_stmt(64, 64, 64)
+    assert any("proposer is done" in x for x in lines)
+    hint = schedule_hint(recognise_matmul(parse_stmt(final), 64, 64, 64))
+    assert (hint["tile_m"], hint["tile_n"], hint["parallel"], hint["vectorize"]) == (32, 32, ["i0_outer"], ["i1_inner"])
+    assert schedule_hint(recognise_matmul(parse_stmt(naive_matmul_stmt(64, 64, 64)), 64, 64, 64))["variant"] is None
+
+    # a tile size that does not divide the extent is refused; the remaining proposals still apply
+    bad = [demo._tactic("tile", "i0", size=48)] + demo.mock_schedule()
+    schedule, final, refused = demo.run_agent(naive_matmul_stmt(64, 64, 64), demo.MockProposer(bad), max_steps=10,
+                                              log=lines.append)
+    assert len(refused) == 1 and refused[0][0]["int_params"] == [48] and len(schedule) == 5
+    assert final == readme_scheduled_stmt(64, 64, 64)
+    # the step limit ends the walk early
+    schedule, final, _ = demo.run_agent(naive_matmul_stmt(64, 64, 64), demo.MockProposer(demo.mock_schedule()),
+                                        max_steps=2, log=lines.append)
+    assert len(schedule) == 2
+    # fail closed without the verifier
+    monkeypatch.setenv("VERITAC_BIN", str(tmp_path / "missing"))
+    with pytest.raises(FileNotFoundError, match="VeriTac binary not found"):
+        demo.call_lean(naive_matmul_stmt(16, 16, 16), [])

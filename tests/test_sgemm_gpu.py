@@ -261,6 +261,11 @@ def test_demos_run_end_to_end(native, capsys):
     assert report["rows"][-1]["modeled_input_bytes"] < report["rows"][0]["modeled_input_bytes"]
     assert gemmini_gemm_demo.main(["--m", "32", "--n", "16", "--k", "16", "--repeats", "2"]) == 0
     assert "winner by modeled objective" in capsys.readouterr().out
+    from veritac_b200.examples import llm_gemm_demo
+    assert llm_gemm_demo.main(["--mock", "--dim", "256", "--runs", "2"]) == 0
+    out = capsys.readouterr().out
+    assert out.count("verifier: applied") == 5 and "correct: True" in out
+    assert "kernel the library chose for 256x256x256: TILE32" in out and "tiles point at: TILE32" in out
 
 
 def test_stream_order_holds_across_overlapped_launches(native):

@@ -44,6 +44,9 @@ VT_SGEMM_TILE32 = 7
 VT_SGEMM_PANEL_TF32X3 = 8
 VT_SGEMM_TALL_TF32X3 = 9
 
+SGEMM_VARIANT_NAMES = {0: "AUTO", 1: "TILE128", 2: "TILE64", 3: "SKINNY", 4: "TF32X3", 5: "SKINNY_TF32X3",
+                       6: "SKINNY_MMA_SYNC", 7: "TILE32", 8: "PANEL_TF32X3", 9: "TALL_TF32X3"}
+
 # Every symbol include/veritac_b200.h declares, with its ctypes signature.
 SIGNATURES = {
     "vt_device_count": (c_int, []),

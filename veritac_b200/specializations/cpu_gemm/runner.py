@@ -90,7 +90,33 @@ def matmul_operands(M: int, K: int, N: int, dtype=np.float32):
     return a, b
 
 
-def benchmark_matmul(stmt_json: dict, M: int, K: int, N: int, num_runs: int = 5) -> dict:
+def schedule_hint(shape: dict) -> dict:
+    """What a recognised nest's schedule says about tiling, in this back end's terms.
+
+    The tile tactic leaves `<v>_outer` / `<v>_inner` loops (VeriTac/Tactic/Tile.lean:284-321); the innermost loop
+    of the row role and of the column role give the tile a CPU schedule meant to keep in cache, which on the GPU
+    is the CTA tile: up to 32 -> the 32x32 kernel, up to 64 -> the 64x64 kernel, beyond -> the 128x128 kernel.
+    A nest without a split row or column loop gives no hint (None).  The annotations are carried along for the
+    caller to show; on the GPU every output cell is computed in parallel whatever they say.
+    """
+    from ... import _native as nv
+
+    inner = {}
+    for var, extent, ann, role in shape["loops"]:
+        inner[role] = (var, extent)                      # the last loop of each role is its innermost
+    split = {role: sum(1 for l in shape["loops"] if l[3] == role) > 1 for role in ("i", "j", "k")}
+    tile_m = inner["i"][1] if split["i"] else None
+    tile_n = inner["j"][1] if split["j"] else None
+    variant = None
+    if tile_m or tile_n:
+        side = max(tile_m or 0, tile_n or 0)
+        variant = nv.VT_SGEMM_TILE32 if side <= 32 else nv.VT_SGEMM_TILE64 if side <= 64 else nv.VT_SGEMM_TILE128
+    return {"tile_m": tile_m, "tile_n": tile_n, "variant": variant,
+            "parallel": [v for v, _n, ann, _r in shape["loops"] if ann == "parallel"],
+            "vectorize": [v for v, _n, ann, _r in shape["loops"] if ann == "vectorize"]}
+
+
+def benchmark_matmul(stmt_json: dict, M: int, K: int, N: int, num_runs: int = 5, time_hint: bool = False) -> dict:
     """Time a matmul loop nest on the GPU against numpy and check its result.
 
     Args are the reference's: the loop-nest JSON, then M, K, N (note the order), then the number of
@@ -100,14 +126,18 @@ def benchmark_matmul(stmt_json: dict, M: int, K: int, N: int, num_runs: int = 5)
     Returns the reference's keys — c_time_ms (average device time of one matmul, operands resident
     in HBM, the counterpart of the reference timing `matmul()` on resident host buffers),
     numpy_time_ms, speedup, correct (the same four cells within 1e-6), c_first_values,
-    np_first_values — plus e2e_time_ms (one call with host buffers, copies included) and
-    rel_frobenius_error of the whole result against float64.
+    np_first_values — plus e2e_time_ms (one call with host buffers, copies included),
+    rel_frobenius_error of the whole result against float64, `kernel` (the kernel the library chose for the
+    shape) and `schedule_hint` (schedule_hint() of the nest).  The timed call always uses the library's own
+    choice; with `time_hint` the kernel the schedule's tile sizes point at is timed as well (`hint_time_ms`,
+    `hint_kernel`), so that a caller can see what honouring the schedule would have cost.
     """
     stmt = parse_stmt(stmt_json)
     try:
-        recognise_matmul(stmt, M, K, N)
+        shape = recognise_matmul(stmt, M, K, N)
     except NotAMatmul as exc:
         raise RuntimeError(f"loop nest is not a GEMM the B200 back end can execute: {exc}") from exc
+    hint = schedule_hint(shape)
 
     import torch  # device memory, stream and events only
 
@@ -134,6 +164,20 @@ def benchmark_matmul(stmt_json: dict, M: int, K: int, N: int, num_runs: int = 5)
             total_ms += start.elapsed_time(stop)
         nv.sync(dev, stream)
         c_host = dC.cpu().numpy()
+        chosen = nv.sgemm_auto_variant(M, N, K, dev=dev)
+        hint_ms = None
+        if time_hint and hint["variant"] is not None and num_runs:
+            tileable = hint["variant"] != nv.VT_SGEMM_TILE32 or (N % 4 == 0 and K % 4 == 0)
+            if tileable:
+                dH = torch.zeros((M, N), dtype=torch.float32, device="cuda")
+                nv.sgemm(dA, dB, dH, M, N, K, dev=dev, variant=hint["variant"], where=nv.VT_DEVICE, stream=stream)
+                start.record()
+                for _ in range(num_runs):
+                    nv.sgemm(dA, dB, dH, M, N, K, dev=dev, variant=hint["variant"], where=nv.VT_DEVICE, stream=stream)
+                stop.record()
+                stop.synchronize()
+                hint_ms = start.elapsed_time(stop) / num_runs
+                nv.sync(dev, stream)
         # once more through host buffers: what a caller without device memory pays
         c_e2e = np.empty((M, N), dtype=np.float32)
         t0 = time.perf_counter()
@@ -166,4 +210,8 @@ def benchmark_matmul(stmt_json: dict, M: int, K: int, N: int, num_runs: int = 5)
         "np_first_values": expected,
         "e2e_time_ms": e2e_ms,
         "rel_frobenius_error": rel,
+        "kernel": nv.SGEMM_VARIANT_NAMES.get(chosen, str(chosen)),
+        "schedule_hint": hint,
+        "hint_kernel": nv.SGEMM_VARIANT_NAMES.get(hint["variant"]) if hint["variant"] is not None else None,
+        "hint_time_ms": hint_ms,
     }

@@ -590,28 +590,6 @@ def run_gpu_arm(args, kind, M, N, K, batch, metric, unit):
     ms_per_step, launches = job.timed(steps, warm, sampler)
     value = job.value(ms_per_step)
 
-    # ---- the same step back to back for about a second: NVML's clock and power readings lag a region of a
-    # few milliseconds, so this is where the power cap shows; reported beside the timed region, not as it ----
-    sustained = None
-    if args.sustain_seconds > 0:
-        reps = max(steps, min(200000, int(args.sustain_seconds * 1e3 / max(ms_per_step, 1e-3))))
-        s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        barrier()
-        t_s0 = time.perf_counter()
-        s0.record()
-        for _ in range(reps):
-            job.step()
-        s1.record()
-        barrier()
-        t_s1 = time.perf_counter()
-        sus_ms = ctx["max"](s0.elapsed_time(s1) / reps)
-        nv.sync(dev, ctx["st"])
-        if rank == 0:
-            # the second half of the window: the readings have caught up with the load by then
-            sustained = sampler.window(0.5 * (t_s0 + t_s1), t_s1) or {}
-            sustained.update({"steps": reps, "ms_per_step": sus_ms, "seconds": t_s1 - t_s0})
-    clocks = sampler.stop() if rank == 0 else None
-
     # ---- parity of the device-resident run: this rank's C as the timed steps left it ----
     parity_device = job.check(job.C)
 
@@ -691,20 +669,15 @@ def run_gpu_arm(args, kind, M, N, K, batch, metric, unit):
     # ---- the weak-scaling figure beside the strong one: every rank the whole shape ----
     weak = None
     if world > 1 and args.scaling == "strong" and not job.replicas and not args.no_also:
-        job.release()
         wjob = Job(ctx, args.workload, "weak", args.i8_variant, args.sgemm_variant)
         w_ms, _ = wjob.timed(steps, warm)
         weak = {"ms_per_step": w_ms, "value": wjob.value(w_ms), "unit": unit, "rows_per_gpu": wjob.rows,
                 "parity_ok": bool(ctx["min"](1.0 if wjob.check(wjob.C)["ok"] else 0.0) > 0.5)}
         wjob.release()
-        job = None
 
     # ---- the other named workloads, each timed like the headline ----
     also = None
     if not args.no_also:
-        if job is not None:
-            job.release()
-            job = None
         also = {}
         for name, wl, variant in (("sgemm_8192", "sgemm_8192", nv.VT_SGEMM_AUTO),
                                   ("sgemm_8192_ffma", "sgemm_8192", nv.VT_SGEMM_TILE128),
@@ -724,6 +697,29 @@ def run_gpu_arm(args, kind, M, N, K, batch, metric, unit):
                           "roofline": {k: roof[k] for k in ("bound", "achieved", "peak", "unit", "frac")}}
             j.release()
 
+    # ---- the same step back to back for about a second: NVML's clock and power readings lag a region of a
+    # few milliseconds, so this is where the power cap shows; reported beside the timed region, not as it.  It
+    # comes last: a second at full power warms the GPU, and nothing else is measured after it ----
+    sustained = None
+    if args.sustain_seconds > 0:
+        reps = max(steps, min(200000, int(args.sustain_seconds * 1e3 / max(ms_per_step, 1e-3))))
+        s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        t_s0 = time.perf_counter()
+        s0.record()
+        for _ in range(reps):
+            job.step()
+        s1.record()
+        barrier()
+        t_s1 = time.perf_counter()
+        sus_ms = ctx["max"](s0.elapsed_time(s1) / reps)
+        nv.sync(dev, ctx["st"])
+        if rank == 0:
+            # the second half of the window: the readings have caught up with the load by then
+            sustained = sampler.window(0.5 * (t_s0 + t_s1), t_s1) or {}
+            sustained.update({"steps": reps, "ms_per_step": sus_ms, "seconds": t_s1 - t_s0})
+
+    clocks = sampler.stop() if rank == 0 else None
     if rank != 0:
         if world > 1:
             dist.barrier()

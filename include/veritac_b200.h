@@ -74,12 +74,17 @@ enum {
  *                          are added by the pair that owns the tile (exact).  Measured level with CTA_PAIR
  *                          (the pairs then no longer walk K in step and the L2 serves them more slowly),
  *                          so VT_I8_AUTO does not choose it.
+ *   CTA_PAIR_WIDE          two CTAs per 256x512 tile: both halves share the pair's rows of A, which cuts the
+ *                          operand traffic per product by a quarter; tensor memory is then full, so a tile's
+ *                          epilogue does not overlap the next tile's MMAs.  For products of few tiles per pair
+ *                          (row shards of a multi-GPU job).
  * All read B as stored and write C by TMA stores. */
 enum {
   VT_I8_AUTO = 0,
   VT_I8_B_AS_STORED = 1,
   VT_I8_CTA_PAIR_SHARED_TAIL = 2,
-  VT_I8_CTA_PAIR = 3
+  VT_I8_CTA_PAIR = 3,
+  VT_I8_CTA_PAIR_WIDE = 4
 };
 
 /* fp32 kernel variants.

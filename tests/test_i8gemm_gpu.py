@@ -142,7 +142,7 @@ def test_config2_int8_64_cubed_partial_sums(native, g):
         assert (stats["overwrites"], stats["accumulates"]) == (256, 768)
 
 
-@pytest.mark.parametrize("variant", [0, 1, 2, 3])
+@pytest.mark.parametrize("variant", [0, 1, 2, 3, 4])
 def test_shapes_rasters_variants(native, variant):
     rng = np.random.default_rng(11)
     shapes = [(16, 16, 16), (16, 80, 32), (80, 16, 32), (48, 32, 64), (128, 256, 128), (144, 272, 400),
@@ -155,7 +155,7 @@ def test_shapes_rasters_variants(native, variant):
             assert np.array_equal(gemm(native, a, b, m, n, k, variant=variant, raster=raster, batch_rows=br), want)
 
 
-@pytest.mark.parametrize("variant", [0, 1, 2])
+@pytest.mark.parametrize("variant", [0, 1, 2, 4])
 def test_host_buffers_large_enough_for_the_corner_pipeline(native, variant):
     """From 2048 x 2048 outputs on, host-buffer calls bring B in by column blocks and return C by
     regions (pitched copies, kernels on sub-matrices)."""
@@ -307,7 +307,7 @@ def test_stream_order_holds_across_overlapped_launches(native):
     dA, dB = torch.from_numpy(a).cuda(), torch.from_numpy(b).cuda()
     dC = torch.empty((m, n), dtype=torch.int32, device="cuda")
     st = native.torch_stream()
-    for variant in (0, 1, 2):
+    for variant in (0, 1, 2, 4):
         for rep in range(8):
             dC.fill_(-7 - rep)
             native.i8gemm(dA, dB, dC, m, n, k, variant=variant, where=native.VT_DEVICE, stream=st)
@@ -343,7 +343,7 @@ def _device_case(native, m, n, k, seed, variant=0, reps=2):
         assert torch.equal(C, want), (m, n, k, variant, rep)
 
 
-@pytest.mark.parametrize("variant", [0, 2])
+@pytest.mark.parametrize("variant", [0, 2, 4])
 def test_shared_tail_of_the_pair_kernel(native, variant):
     """Shapes whose 256 x 256 tiles do not fill whole waves of the 74 CTA pairs: the K blocks of the last wave
     are dealt to all pairs and partial int32 sums meet in scratch memory.  The 1024- and 2048-row shards of the
@@ -364,7 +364,7 @@ def test_shared_tail_equals_whole_tiles(native):
     B = torch.randint(-128, 128, (k, n), dtype=torch.int8, device="cuda", generator=gen)
     st = native.torch_stream()
     outs = []
-    for variant in (native.VT_I8_CTA_PAIR, native.VT_I8_CTA_PAIR_SHARED_TAIL):
+    for variant in (native.VT_I8_CTA_PAIR, native.VT_I8_CTA_PAIR_SHARED_TAIL, native.VT_I8_CTA_PAIR_WIDE):
         for raster, br in ((0, 1), (1, 1), (2, 3), (3, 1)):
             C = torch.full((m, n), -2**31, dtype=torch.int32, device="cuda")
             native.i8gemm(A, B, C, m, n, k, variant=variant, raster=raster, batch_rows=br, where=native.VT_DEVICE, stream=st)

@@ -38,10 +38,17 @@ void raster_for(int raster, int batch_rows, int64_t M, int* mode, int* group) {
   (void)M;
 }
 
-// Two CTAs per tile need at least 256 rows to have work for both; below that one CTA per tile.
-int resolve_i8_variant(int variant, int64_t M) {
+// Two CTAs per tile need at least 256 rows to have work for both; below that one CTA per tile.  Products of more
+// than one but at most two 256 x 256 tiles per CTA pair (a 1024-row shard of an 8192-wide product on 74 pairs) run
+// as 256 x 512 tiles: the pair kernel's second round would be its last, so there is no later tile whose MMAs
+// the wide form's exposed epilogue could have overlapped, and its K loop runs closer to the tensor pipe's rate
+// (measured 49.4 against 51.3 us at 1024 x 8192 x 8192; 96.8 against 98.1 at 2048 rows, 371 against 367 at 8192).
+int resolve_i8_variant(int variant, int64_t M, int64_t N, int sm_count) {
   if (variant != VT_I8_AUTO) return variant;
-  return M > 128 ? VT_I8_CTA_PAIR : VT_I8_B_AS_STORED;
+  if (M <= 128) return VT_I8_B_AS_STORED;
+  const int64_t tiles = ((M + 255) / 256) * ((N + 255) / 256);
+  const int64_t pairs = sm_count / 2;
+  return (tiles > pairs && tiles <= 2 * pairs && N > 256) ? VT_I8_CTA_PAIR_WIDE : VT_I8_CTA_PAIR;
 }
 
 cudaStream_t pick_stream(DeviceCtx* c, void* stream) { return stream ? static_cast<cudaStream_t>(stream) : c->stream; }
@@ -269,7 +276,7 @@ int vt_i8gemm(int dev, const int8_t* A, const int8_t* B, int32_t* C, int64_t M, 
   if (!c) return VT_ERR_CUDA;
   int mode, group;
   raster_for(raster, batch_rows, M, &mode, &group);
-  variant = resolve_i8_variant(variant, M);
+  variant = resolve_i8_variant(variant, M, N, c->sm_count);
   if (where == VT_HOST) return i8gemm_from_host(c, A, B, C, M, N, K, mode, group, variant);
   if (where == VT_HOST_AC_DEVICE_B) {
     const cudaStream_t b_ready = pick_stream(c, stream);

@@ -566,6 +566,7 @@ int launch_i8gemm(DeviceCtx* c, const int8_t* A, const int8_t* B, int32_t* C, in
   if (ldb == 0) ldb = N;
   if (ldc == 0) ldc = N;
   if (ldb < N || ldc < N || (ldb & 15) || (ldc & 3)) return fail(VT_ERR_INVALID, "bad row pitch for B or C");
+  if (variant == VT_I8_CTA_PAIR_WIDE) return launch_i8gemm_wide(c, A, B, C, M, N, K, raster_mode, group, s, ldb, ldc);
   if (variant < VT_I8_B_AS_STORED || variant > VT_I8_CTA_PAIR)
     return fail(VT_ERR_UNSUPPORTED, "i8gemm variant %d is not built", variant);
   if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(C)) & 15)

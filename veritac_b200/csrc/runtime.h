@@ -100,10 +100,14 @@ cudaError_t launch_overlapped(void (*kernel)(KArgs...), unsigned grid, unsigned 
 // ---- kernel launchers (device pointers only) ------------------------------------------------
 // raster_mode: 0 row-major tiles, 1 column-major tiles, 2 grouped (group = tile-rows per sweep).
 // variant: VT_I8_B_AS_STORED (one CTA per 128 x 256 tile), VT_I8_CTA_PAIR (two CTAs per 256 x 256 tile),
-// VT_I8_CTA_PAIR_SHARED_TAIL (the same with the last partial wave of tiles shared along K).
+// VT_I8_CTA_PAIR_SHARED_TAIL (the same with the last partial wave of tiles shared along K), VT_I8_CTA_PAIR_WIDE (two
+// CTAs per 256 x 512 tile).
 // ldb / ldc: row pitch of B and C in elements when they are sub-blocks of wider matrices (0 = N).
 int launch_i8gemm(DeviceCtx* c, const int8_t* A, const int8_t* B, int32_t* C, int64_t M, int64_t N, int64_t K,
                   int raster_mode, int group, int variant, cudaStream_t s, int64_t ldb = 0, int64_t ldc = 0);
+// VT_I8_CTA_PAIR_WIDE: CTA pairs on 256 x 512 tiles (i8gemm_wide_sm100.cu); launch_i8gemm forwards to it.
+int launch_i8gemm_wide(DeviceCtx* c, const int8_t* A, const int8_t* B, int32_t* C, int64_t M, int64_t N, int64_t K,
+                       int raster_mode, int group, cudaStream_t s, int64_t ldb, int64_t ldc);
 // Test hook: one CTA whose bounded wait runs out (see vt_test_expire_wait).
 int launch_expire_wait(DeviceCtx* c, cudaStream_t s);
 int launch_sgemm(DeviceCtx* c, const float* A, const float* B, float* C, int64_t M, int64_t N, int64_t K,

@@ -49,8 +49,10 @@ __device__ __forceinline__ void tile_coords(const TileRaster& rs, int t, int& mi
 // `merge`, when given, points at this lane's first 16 bytes of `ncontrib` partial accumulators of the same
 // tile (the layout epilogue_warp_partial writes, `merge_stride` uint4 apart); they are added before the
 // store.  The loads of one chunk are issued while the chunk before it is added and stored.
+// A `wide` area of fewer buffers than chunks (kWide) is used round-robin: a chunk then waits for the store that
+// last read its buffer.
 // Returns once the accumulator has been read (the stores may still be in flight).
-template <int kBufs = 2>
+template <int kBufs = 2, int kWide = 16>
 __device__ __forceinline__ void epilogue_warp_tile(uint32_t t_row, const CUtensorMap* tmC, uint8_t* staging, int M,
                                                    int N, int row0, int n0, int lane, uint64_t store_policy = 0,
                                                    uint8_t* wide = nullptr, const uint4* merge = nullptr,
@@ -86,9 +88,12 @@ __device__ __forceinline__ void epilogue_warp_tile(uint32_t t_row, const CUtenso
         r[4 * v + 3] += cur[v].w;
       }
     }
-    uint8_t* buf = wide ? wide + (c - c_begin) * EPI_BUF_BYTES : staging + (c & (kBufs - 1)) * EPI_BUF_BYTES;
+    uint8_t* buf = wide ? wide + ((c - c_begin) % kWide) * EPI_BUF_BYTES : staging + (c & (kBufs - 1)) * EPI_BUF_BYTES;
     if (!wide) {
       if (lane == 0) tma_store_wait_read<kBufs - 1>();   // the store that last read this buffer is done with it
+      __syncwarp();
+    } else if (c - c_begin >= kWide) {
+      if (lane == 0) tma_store_wait_read<kWide - 1>();
       __syncwarp();
     }
     const uint32_t base = smem_u32(buf) + uint32_t(lane) * 128u;

@@ -609,7 +609,12 @@ def run_gpu_arm(args, kind, M, N, K, batch, metric, unit):
         hB = torch.empty((K, N), dtype=job.B.dtype).pin_memory() if (rank == 0 or not shared_b) else None
         if hB is not None:
             hB.copy_(job.B)
-        dB = torch.empty_like(job.B) if shared_b else None
+        # B in column blocks, so that the first columns of C leave while later blocks of B still arrive
+        streamed = shared_b and kind == "i8"
+        blocks = sharding.column_blocks(N, 8) if streamed else None
+        dB = ([torch.empty((K, cols), dtype=job.B.dtype, device="cuda") for _c0, cols in blocks] if streamed
+              else torch.empty_like(job.B) if shared_b else None)
+        ready = [torch.cuda.Event() for _ in blocks] if streamed else None
 
         def host_call(a, b, c, where):
             if rows == 0:
@@ -621,8 +626,20 @@ def run_gpu_arm(args, kind, M, N, K, batch, metric, unit):
             else:
                 nv.i8gemm(a, b, c, rows, N, K, dev=dev, where=where, stream=ctx["st"])
 
+        def stage_block(j, buf, c0, cols):
+            nv.i8_stage_b_block(buf, hB, K, N, c0, cols, dev=dev, stream=ctx["st"])
+
+        def mark_ready(j):
+            ready[j].record()
+            return ready[j]
+
         def e2e_step():
-            if shared_b:
+            if streamed:
+                sharding.run_row_sharded_streamed(
+                    stage_block, lambda a, bs, evs, c: nv.i8gemm_rows_streamed_b(a, bs, [b.shape[1] for b in bs], evs, c,
+                                                                                 rows, N, K, dev=dev),
+                    hA, dB, hC, blocks, mark_ready=mark_ready)
+            elif shared_b:
                 sharding.run_row_sharded(lambda a, b, c: host_call(a, b, c, nv.VT_HOST_AC_DEVICE_B), hA, dB, hC,
                                          B_source=hB)
             else:
@@ -655,7 +672,12 @@ def run_gpu_arm(args, kind, M, N, K, batch, metric, unit):
         e2e = {"value": 2.0 * job.total_rows * N * K / e2e_s / 1e12, "unit": unit, "h2d_bytes_per_step": int(h2d),
                "d2h_bytes_per_step": int(d2h), "steps": e2e_steps, "ms_per_step": e2e_s * 1e3,
                "link_floor_ms": floor_s * 1e3, "over_link_floor": e2e_s / floor_s,
-               "bytes": "whole job, all ranks; " + ("B crosses the host link on rank 0 only and reaches the other "
+               "bytes": "whole job, all ranks; " + ("B crosses the host link on rank 0 only, in %d column blocks, and "
+                                                     "reaches the other GPUs by NCCL broadcasts inside the timed "
+                                                     "region; every rank computes and returns the columns of C a "
+                                                     "block completes while later blocks arrive"
+                                                     % len(blocks) if streamed else
+                                                     "B crosses the host link on rank 0 only and reaches the other "
                                                      "GPUs by the NCCL broadcast inside the timed region"
                                                      if shared_b else "every rank copies the operands it uses"),
                "link_floor": "plain cudaMemcpyAsync of the same bytes on every rank at once, host->device and "

@@ -20,7 +20,7 @@ def test_header_and_binding_agree(native):
     handle = ctypes.CDLL(str(native.LIB_PATH))
     for name in names:
         assert hasattr(handle, name), name
-    assert len(names) == 15
+    assert len(names) == 17
 
 
 def test_status_codes_match_header(native):

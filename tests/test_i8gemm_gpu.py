@@ -421,3 +421,30 @@ def test_load_strides_zero_one_and_beyond_a_row(native, g, stride_a, stride_b):
     want, want_stats = go.interpret(cmds, plan, A, B)
     got, stats = g.run_commands(cmds, plan, A, B)
     assert got == want and stats == want_stats
+
+
+def test_rows_with_b_streamed_in_column_blocks(native):
+    """One rank's step of the row-sharded job: A and C in pinned host memory, B staged block by block from host
+    memory into dense device blocks (what rank 0 does before each broadcast), an event per block, one call that
+    overlaps all of it.  Every cell against the exact product; ragged last block; a second call reuses the events."""
+    import torch
+    from veritac_b200.sharding import column_blocks
+    gen = torch.Generator(device="cuda").manual_seed(20260917 + 70)
+    st = native.torch_stream()
+    for (m, n, k, nb) in ((1024, 8192, 8192, 8), (528, 2000 * 16 // 16 * 16 + 48, 1040, 5), (16, 16, 16, 1)):
+        A = torch.randint(-128, 128, (m, k), dtype=torch.int8, device="cuda", generator=gen)
+        B = torch.randint(-128, 128, (k, n), dtype=torch.int8, device="cuda", generator=gen)
+        want = (A.double() @ B.double()).to(torch.int32).cpu()
+        hA, hB = A.cpu().pin_memory(), B.cpu().pin_memory()
+        blocks = column_blocks(n, nb)
+        bufs = [torch.empty((k, cols), dtype=torch.int8, device="cuda") for _c0, cols in blocks]
+        events = [torch.cuda.Event() for _ in blocks]
+        for rep in range(2):
+            hC = torch.full((m, n), -2**31, dtype=torch.int32).pin_memory()
+            for j, (c0, cols) in enumerate(blocks):
+                native.i8_stage_b_block(bufs[j], hB, k, n, c0, cols, stream=st)
+                events[j].record()
+            native.i8gemm_rows_streamed_b(hA, bufs, [c for _c0, c in blocks], events, hC, m, n, k)
+            assert torch.equal(hC, want), (m, n, k, rep)
+    with pytest.raises(native.NativeError):          # widths must add up to N
+        native.i8gemm_rows_streamed_b(hA, bufs, [32], events, hC, 16, 16, 16)

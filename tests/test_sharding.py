@@ -8,7 +8,7 @@ import sys
 import pytest
 
 from conftest import REPO
-from veritac_b200.sharding import batch_shard, row_shard
+from veritac_b200.sharding import batch_shard, column_blocks, row_shard
 
 
 def test_row_shard_tiles_the_range():
@@ -26,6 +26,19 @@ def test_row_shard_tiles_the_range():
         row_shard(100, 2, 0)
     with pytest.raises(ValueError):
         row_shard(64, 2, 2)
+
+
+def test_column_blocks_tile_the_columns():
+    for n in (16, 256, 272, 4096, 8192, 8192 + 48, 1000 * 16):
+        for nb in (1, 2, 3, 8, 64):
+            blocks = column_blocks(n, nb)
+            assert blocks[0][0] == 0 and sum(c for _, c in blocks) == n and len(blocks) <= nb
+            for (a0, ac), (b0, _bc) in zip(blocks, blocks[1:]):
+                assert a0 + ac == b0
+            assert all(c % 256 == 0 for _, c in blocks[:-1]) and all(c > 0 for _, c in blocks)
+    assert column_blocks(8192, 8) == [(i * 1024, 1024) for i in range(8)]
+    with pytest.raises(ValueError):
+        column_blocks(0, 4)
 
 
 WORKER = r"""
@@ -47,6 +60,19 @@ def compute(a, b, c):
     c[:] = go.matmul_exact(a, b.numpy(), a.shape[0], N, K).astype(np.int32)
 sharding.run_row_sharded(compute, A[r0:r1], B, C_rows, B_source=B_source)
 assert np.array_equal(B.numpy(), B_true)                         # it arrived by the broadcast
+# the same step with B delivered in column blocks: rank 0 stages each block, the broadcast carries it on
+blocks = sharding.column_blocks(N, 2, align=16)
+bufs = [torch.zeros((K, cols), dtype=torch.int8) for _c0, cols in blocks]
+C2 = np.full((r1 - r0, N), -2**31, dtype=np.int32)
+staged = []
+def stage(j, buf, c0, cols):
+    staged.append(j)
+    buf.copy_(torch.from_numpy(B_true[:, c0:c0 + cols].copy()))
+def compute_blocks(a, bs, markers, c):
+    assert markers == ["ready0", "ready1"]
+    c[:] = go.matmul_exact(a, np.concatenate([b.numpy() for b in bs], axis=1), a.shape[0], N, K).astype(np.int32)
+sharding.run_row_sharded_streamed(stage, compute_blocks, A[r0:r1], bufs, C2, blocks, mark_ready=lambda j: "ready%d" % j)
+assert staged == ([0, 1] if rank == 0 else []) and np.array_equal(C2, C_rows)
 parts = [None] * world
 dist.all_gather_object(parts, (r0, r1, C_rows))
 C = np.concatenate([p[2] for p in sorted(parts, key=lambda p: p[0])])

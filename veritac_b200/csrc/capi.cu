@@ -285,6 +285,66 @@ int vt_i8gemm(int dev, const int8_t* A, const int8_t* B, int32_t* C, int64_t M, 
   return launch_i8gemm(c, A, B, C, M, N, K, mode, group, variant, pick_stream(c, stream));
 }
 
+int vt_i8_stage_b_block(int dev, int8_t* dst, const int8_t* B_host, int64_t K, int64_t N, int64_t c0, int64_t cols,
+                        void* stream) {
+  clear_error_text();
+  if (!dst || !B_host) return fail(VT_ERR_INVALID, "null operand");
+  if (K < 1 || N < 1 || c0 < 0 || cols < 1 || c0 + cols > N) return fail(VT_ERR_INVALID, "column block outside B");
+  DeviceCtx* c = ctx_for(dev);
+  if (!c) return VT_ERR_CUDA;
+  VT_CUDA(cudaMemcpy2DAsync(dst, size_t(cols), B_host + c0, size_t(N), size_t(cols), size_t(K), cudaMemcpyHostToDevice,
+                            pick_stream(c, stream)));
+  return VT_OK;
+}
+
+int vt_i8gemm_rows_streamed_b(int dev, const int8_t* A, const int8_t* const* B_blocks, const int64_t* block_cols,
+                              void* const* block_ready, int n_blocks, int32_t* C, int64_t M, int64_t N, int64_t K,
+                              int raster, int batch_rows, int variant) {
+  clear_error_text();
+  if (!A || !B_blocks || !block_cols || !block_ready || !C) return fail(VT_ERR_INVALID, "null operand");
+  if (n_blocks < 1 || n_blocks > 64) return fail(VT_ERR_INVALID, "n_blocks must be in 1..64");
+  if (raster < VT_RASTER_BASELINE || raster > VT_RASTER_AUTO) return fail(VT_ERR_INVALID, "unknown raster %d", raster);
+  if (raster == VT_RASTER_BATCHED && (batch_rows < 1 || batch_rows > 64))
+    return fail(VT_ERR_INVALID, "batch_rows must be in 1..64 (accumulator rows 16..1024)");
+  int rc = check_i8_domain(M, N, K);
+  if (rc) return rc;
+  int64_t total = 0;
+  for (int j = 0; j < n_blocks; ++j) {
+    if (!B_blocks[j] || !block_ready[j]) return fail(VT_ERR_INVALID, "null block %d", j);
+    rc = check_i8_domain(M, block_cols[j], K);
+    if (rc) return rc;
+    total += block_cols[j];
+  }
+  if (total != N) return fail(VT_ERR_INVALID, "block widths add up to %lld, not N = %lld", (long long)total, (long long)N);
+  DeviceCtx* c = ctx_for(dev);
+  if (!c) return VT_ERR_CUDA;
+  int mode, group;
+  raster_for(raster, batch_rows, M, &mode, &group);
+  int8_t* dA = static_cast<int8_t*>(ctx_workspace(c, 0, size_t(M) * K));
+  int32_t* dC = static_cast<int32_t*>(ctx_workspace(c, 2, size_t(M) * N * sizeof(int32_t)));
+  if (!dA || !dC) return VT_ERR_CUDA;
+  cudaEvent_t ev_in = c->ev[1], ev_k = c->ev[2], ev_done = c->ev[3];
+  VT_CUDA(cudaMemcpyAsync(dA, A, size_t(M) * K, cudaMemcpyHostToDevice, c->copy_in));
+  VT_CUDA(cudaEventRecord(ev_in, c->copy_in));
+  VT_CUDA(cudaStreamWaitEvent(c->stream, ev_in, 0));
+  int64_t c0 = 0;
+  for (int j = 0; j < n_blocks; ++j) {
+    const int64_t cols = block_cols[j];
+    VT_CUDA(cudaStreamWaitEvent(c->stream, static_cast<cudaEvent_t>(block_ready[j]), 0));
+    rc = launch_i8gemm(c, dA, B_blocks[j], dC + c0, M, cols, K, mode, group, resolve_i8_variant(variant, M, cols, c->sm_count),
+                       c->stream, cols, N);
+    if (rc) return rc;
+    VT_CUDA(cudaEventRecord(ev_k, c->stream));
+    VT_CUDA(cudaStreamWaitEvent(c->copy_out, ev_k, 0));
+    VT_CUDA(cudaMemcpy2DAsync(C + c0, size_t(N) * 4, dC + c0, size_t(N) * 4, size_t(cols) * 4, size_t(M),
+                              cudaMemcpyDeviceToHost, c->copy_out));
+    c0 += cols;
+  }
+  VT_CUDA(cudaEventRecord(ev_done, c->copy_out));
+  VT_CUDA(cudaStreamWaitEvent(c->stream, ev_done, 0));
+  return ctx_check_status(c, c->stream);
+}
+
 int vt_i8gemm_shared_b(int dev, const int8_t* A, const int8_t* B, int32_t* C, int64_t batch, int64_t M, int64_t N,
                        int64_t K, int acc_rows, int where, void* stream) {
   clear_error_text();

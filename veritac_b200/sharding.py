@@ -95,3 +95,44 @@ def run_row_sharded(compute, A_rows, B_local, C_rows, B_source=None):
     if A_rows.shape[0] > 0:
         compute(A_rows, B_local, C_rows)
     return C_rows
+
+
+def column_blocks(N: int, n_blocks: int, align: int = 256) -> list[tuple[int, int]]:
+    """[(first column, width)] of at most `n_blocks` blocks that tile [0, N): widths are multiples of `align`
+    (the int8 kernels' tile width) except possibly the last, and differ by at most one `align`."""
+    if N <= 0 or n_blocks < 1:
+        raise ValueError("N and n_blocks must be positive")
+    units = -(-N // align)
+    n_blocks = min(n_blocks, units)
+    base, extra = divmod(units, n_blocks)
+    out, c0 = [], 0
+    for j in range(n_blocks):
+        cols = min((base + (1 if j < extra else 0)) * align, N - c0)
+        out.append((c0, cols))
+        c0 += cols
+    return out
+
+
+def run_row_sharded_streamed(stage_block, compute, A_rows, B_blocks, C_rows, blocks, mark_ready=None):
+    """The row-sharded step with B delivered in column blocks, so that a rank starts computing (and returning C)
+    while later blocks of B are still on the host link or the interconnect.
+
+    `blocks` is column_blocks(N, ...); `B_blocks[j]` is this rank's buffer for block j (a dense K x cols tensor).
+    On rank 0 `stage_block(j, B_blocks[j], c0, cols)` fills the buffer from wherever B originates (for the GPU job:
+    `_native.i8_stage_b_block` from pinned host memory); every block is then broadcast from rank 0, and
+    `mark_ready(j)` (for the GPU job: record a CUDA event after the broadcast) yields the marker the compute call
+    waits on.  `compute(A_rows, B_blocks, markers, C_rows)` runs once, after all blocks have been *queued*: on a GPU
+    the copies and broadcasts are asynchronous, so the call (`_native.i8gemm_rows_streamed_b`) overlaps them.
+    """
+    import torch.distributed as dist
+
+    rank = dist.get_rank() if dist.is_available() and dist.is_initialized() else 0
+    markers = []
+    for j, (c0, cols) in enumerate(blocks):
+        if rank == 0:
+            stage_block(j, B_blocks[j], c0, cols)
+        replicate_from_rank0(B_blocks[j])
+        markers.append(mark_ready(j) if mark_ready is not None else None)
+    if A_rows.shape[0] > 0:
+        compute(A_rows, B_blocks, markers, C_rows)
+    return C_rows

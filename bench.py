@@ -611,7 +611,8 @@ def run_gpu_arm(args, kind, M, N, K, batch, metric, unit):
             hB.copy_(job.B)
         # B in column blocks, so that the first columns of C leave while later blocks of B still arrive
         streamed = shared_b and kind == "i8"
-        blocks = sharding.column_blocks(N, 8) if streamed else None
+        blocks = sharding.column_blocks(N, 4) if streamed else None
+        dA_stream = torch.empty_like(job.A) if streamed else None
         dB = ([torch.empty((K, cols), dtype=job.B.dtype, device="cuda") for _c0, cols in blocks] if streamed
               else torch.empty_like(job.B) if shared_b else None)
         ready = [torch.cuda.Event() for _ in blocks] if streamed else None
@@ -635,10 +636,12 @@ def run_gpu_arm(args, kind, M, N, K, batch, metric, unit):
 
         def e2e_step():
             if streamed:
+                # this rank's rows of A go first, so that they do not queue behind B on the host link
+                dA_stream.copy_(hA, non_blocking=True)
                 sharding.run_row_sharded_streamed(
                     stage_block, lambda a, bs, evs, c: nv.i8gemm_rows_streamed_b(a, bs, [b.shape[1] for b in bs], evs, c,
-                                                                                 rows, N, K, dev=dev),
-                    hA, dB, hC, blocks, mark_ready=mark_ready)
+                                                                                 rows, N, K, dev=dev, a_where=nv.VT_DEVICE),
+                    dA_stream, dB, hC, blocks, mark_ready=mark_ready)
             elif shared_b:
                 sharding.run_row_sharded(lambda a, b, c: host_call(a, b, c, nv.VT_HOST_AC_DEVICE_B), hA, dB, hC,
                                          B_source=hB)

@@ -142,8 +142,11 @@ int vt_i8gemm(int dev, const int8_t* A, const int8_t* B, int32_t* C, int64_t M, 
 int vt_i8gemm_shared_b(int dev, const int8_t* A, const int8_t* B, int32_t* C, int64_t batch, int64_t M, int64_t N,
                        int64_t K, int acc_rows, int where, void* stream);
 
-/* One rank's step of a row-sharded int8 GEMM whose replicated operand arrives in pieces: A (M x K) and C (M x N)
- * are this rank's row blocks in HOST memory; B comes as `n_blocks` column blocks already in this GPU's memory,
+/* One rank's step of a row-sharded int8 GEMM whose replicated operand arrives in pieces: C (M x N) is this rank's
+ * row block in HOST memory; A (M x K), its rows of the left operand, is in host memory too (a_where = VT_HOST: the
+ * call copies it in first) or already on the device (VT_DEVICE: valid by the time block_ready[0] completes; a
+ * caller that queues its own copy of A *before* it stages the blocks of B keeps A from waiting behind them on the
+ * host link).  B comes as `n_blocks` column blocks already in this GPU's memory,
  * block j a dense K x block_cols[j] matrix (row pitch block_cols[j]) holding the next block_cols[j] columns of B,
  * valid once the cudaEvent_t block_ready[j] has completed (the caller records it after the broadcast that
  * delivered the block).  The call copies A in, computes the columns of C a block completes as soon as that block
@@ -151,9 +154,9 @@ int vt_i8gemm_shared_b(int dev, const int8_t* A, const int8_t* B, int32_t* C, in
  * the row-sharded form of vt_i8gemm it has no counterpart in the reference (which has no multi-device code); it
  * runs the arithmetic of run_commands() (specializations/gemmini_gemm/backend.py:433-562) on this rank's rows.
  * Block widths: multiples of 16, adding up to N; at most 64 blocks. */
-int vt_i8gemm_rows_streamed_b(int dev, const int8_t* A, const int8_t* const* B_blocks, const int64_t* block_cols,
-                              void* const* block_ready, int n_blocks, int32_t* C, int64_t M, int64_t N, int64_t K,
-                              int raster, int batch_rows, int variant);
+int vt_i8gemm_rows_streamed_b(int dev, const int8_t* A, int a_where, const int8_t* const* B_blocks,
+                              const int64_t* block_cols, void* const* block_ready, int n_blocks, int32_t* C, int64_t M,
+                              int64_t N, int64_t K, int raster, int batch_rows, int variant);
 
 /* Copies columns [c0, c0 + cols) of a row-major K x N int8 matrix in host memory (pinned, for the copy to be
  * asynchronous) into a dense K x cols block in device memory, on `stream`: how the rank that holds B feeds the

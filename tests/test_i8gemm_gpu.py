@@ -444,7 +444,11 @@ def test_rows_with_b_streamed_in_column_blocks(native):
             for j, (c0, cols) in enumerate(blocks):
                 native.i8_stage_b_block(bufs[j], hB, k, n, c0, cols, stream=st)
                 events[j].record()
-            native.i8gemm_rows_streamed_b(hA, bufs, [c for _c0, c in blocks], events, hC, m, n, k)
+            if rep == 0:
+                native.i8gemm_rows_streamed_b(hA, bufs, [c for _c0, c in blocks], events, hC, m, n, k)
+            else:       # A already on the device, queued on the same stream before the blocks' events
+                native.i8gemm_rows_streamed_b(A, bufs, [c for _c0, c in blocks], events, hC, m, n, k,
+                                              a_where=native.VT_DEVICE)
             assert torch.equal(hC, want), (m, n, k, rep)
     with pytest.raises(native.NativeError):          # widths must add up to N
         native.i8gemm_rows_streamed_b(hA, bufs, [32], events, hC, 16, 16, 16)

@@ -56,8 +56,8 @@ SIGNATURES = {
                           c_int, c_void_p]),
     "vt_i8gemm_shared_b": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int,
                                    c_int, c_void_p]),
-    "vt_i8gemm_rows_streamed_b": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int64, c_int64,
-                                          c_int64, c_int, c_int, c_int]),
+    "vt_i8gemm_rows_streamed_b": (c_int, [c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int64,
+                                          c_int64, c_int64, c_int, c_int, c_int]),
     "vt_i8_stage_b_block": (c_int, [c_int, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_void_p]),
     "vt_i8_tile_program": (c_int, [c_int, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int64, c_int64,
                                    c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p]),
@@ -158,14 +158,17 @@ def i8_stage_b_block(dst, B_host, K: int, N: int, c0: int, cols: int, *, dev: in
 
 
 def i8gemm_rows_streamed_b(A, B_blocks, block_cols, block_ready, C, M: int, N: int, K: int, *, dev: int = 0,
-                           raster: int = VT_RASTER_AUTO, batch_rows: int = 1, variant: int = VT_I8_AUTO) -> None:
+                           a_where: int = VT_HOST, raster: int = VT_RASTER_AUTO, batch_rows: int = 1,
+                           variant: int = VT_I8_AUTO) -> None:
     """One rank's rows of an int8 GEMM with B arriving in column blocks (see the header).  `B_blocks` are device
-    tensors or pointers, `block_ready` CUDA event handles (torch.cuda.Event.cuda_event or integers)."""
+    tensors or pointers, `block_ready` CUDA event handles (torch.cuda.Event.cuda_event or integers); `a_where`
+    says whether A is a host buffer the call copies in or already on the device."""
     n = len(B_blocks)
     ptrs = (c_void_p * n)(*[_ptr(b) for b in B_blocks])
     cols = (c_int64 * n)(*[int(x) for x in block_cols])
     evs = (c_void_p * n)(*[int(getattr(e, "cuda_event", e)) for e in block_ready])
-    check(lib().vt_i8gemm_rows_streamed_b(dev, _ptr(A), ptrs, cols, evs, n, _ptr(C), M, N, K, raster, batch_rows, variant))
+    check(lib().vt_i8gemm_rows_streamed_b(dev, _ptr(A), a_where, ptrs, cols, evs, n, _ptr(C), M, N, K, raster, batch_rows,
+                                          variant))
 
 
 def i8_tile_program(A, a_elems, B, b_elems, C, c_elems, lda, ldb, ldc, c_off, term_begin, a_off, b_off, *,

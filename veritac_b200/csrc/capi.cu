@@ -297,10 +297,11 @@ int vt_i8_stage_b_block(int dev, int8_t* dst, const int8_t* B_host, int64_t K, i
   return VT_OK;
 }
 
-int vt_i8gemm_rows_streamed_b(int dev, const int8_t* A, const int8_t* const* B_blocks, const int64_t* block_cols,
-                              void* const* block_ready, int n_blocks, int32_t* C, int64_t M, int64_t N, int64_t K,
-                              int raster, int batch_rows, int variant) {
+int vt_i8gemm_rows_streamed_b(int dev, const int8_t* A, int a_where, const int8_t* const* B_blocks,
+                              const int64_t* block_cols, void* const* block_ready, int n_blocks, int32_t* C, int64_t M,
+                              int64_t N, int64_t K, int raster, int batch_rows, int variant) {
   clear_error_text();
+  if (a_where != VT_HOST && a_where != VT_DEVICE) return fail(VT_ERR_INVALID, "a_where must be VT_HOST or VT_DEVICE");
   if (!A || !B_blocks || !block_cols || !block_ready || !C) return fail(VT_ERR_INVALID, "null operand");
   if (n_blocks < 1 || n_blocks > 64) return fail(VT_ERR_INVALID, "n_blocks must be in 1..64");
   if (raster < VT_RASTER_BASELINE || raster > VT_RASTER_AUTO) return fail(VT_ERR_INVALID, "unknown raster %d", raster);
@@ -320,13 +321,18 @@ int vt_i8gemm_rows_streamed_b(int dev, const int8_t* A, const int8_t* const* B_b
   if (!c) return VT_ERR_CUDA;
   int mode, group;
   raster_for(raster, batch_rows, M, &mode, &group);
-  int8_t* dA = static_cast<int8_t*>(ctx_workspace(c, 0, size_t(M) * K));
+  const int8_t* dA = A;
   int32_t* dC = static_cast<int32_t*>(ctx_workspace(c, 2, size_t(M) * N * sizeof(int32_t)));
-  if (!dA || !dC) return VT_ERR_CUDA;
+  if (!dC) return VT_ERR_CUDA;
   cudaEvent_t ev_in = c->ev[1], ev_k = c->ev[2], ev_done = c->ev[3];
-  VT_CUDA(cudaMemcpyAsync(dA, A, size_t(M) * K, cudaMemcpyHostToDevice, c->copy_in));
-  VT_CUDA(cudaEventRecord(ev_in, c->copy_in));
-  VT_CUDA(cudaStreamWaitEvent(c->stream, ev_in, 0));
+  if (a_where == VT_HOST) {
+    int8_t* wa = static_cast<int8_t*>(ctx_workspace(c, 0, size_t(M) * K));
+    if (!wa) return VT_ERR_CUDA;
+    VT_CUDA(cudaMemcpyAsync(wa, A, size_t(M) * K, cudaMemcpyHostToDevice, c->copy_in));
+    VT_CUDA(cudaEventRecord(ev_in, c->copy_in));
+    VT_CUDA(cudaStreamWaitEvent(c->stream, ev_in, 0));
+    dA = wa;
+  }
   int64_t c0 = 0;
   for (int j = 0; j < n_blocks; ++j) {
     const int64_t cols = block_cols[j];

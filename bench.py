@@ -433,7 +433,7 @@ class Job:
         self.i8_variant, self.sgemm_variant = i8_variant, sgemm_variant
         rank, world = ctx["rank"], ctx["world"]
         total = self.M * self.batch
-        self.replicas = world > 1 and total < 16 * world        # too few rows to split: every rank runs the whole shape
+        self.replicas = world > 1 and total < 64 * world        # too few rows to split: every rank runs the whole shape
         if scaling == "weak" or world == 1 or self.replicas:
             self.rows = total
         else:
@@ -707,7 +707,9 @@ def run_gpu_arm(args, kind, M, N, K, batch, metric, unit):
         for name, wl, variant in (("sgemm_8192", "sgemm_8192", nv.VT_SGEMM_AUTO),
                                   ("sgemm_8192_ffma", "sgemm_8192", nv.VT_SGEMM_TILE128),
                                   ("sgemm_skinny", "sgemm_skinny", nv.VT_SGEMM_AUTO),
-                                  ("i8_batched", "i8_batched", 0)):
+                                  ("i8_batched", "i8_batched", 0),
+                                  ("sgemm_256", "sgemm_256", nv.VT_SGEMM_AUTO),
+                                  ("i8_64", "i8_64", 0)):
             if wl == args.workload and variant == args.sgemm_variant:
                 continue
             j = Job(ctx, wl, "strong", 0, variant)

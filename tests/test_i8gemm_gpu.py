@@ -452,3 +452,43 @@ def test_rows_with_b_streamed_in_column_blocks(native):
             assert torch.equal(hC, want), (m, n, k, rep)
     with pytest.raises(native.NativeError):          # widths must add up to N
         native.i8gemm_rows_streamed_b(hA, bufs, [32], events, hC, 16, 16, 16)
+
+
+def test_two_streams_joined_by_events(native):
+    """Calls on one device must be ordered with one another on the GPU; two streams that hand over to each other
+    through events are such an order.  int8 and fp32 calls alternate between two streams, each waiting for the
+    other's last call; every result is checked (a race on the shared scratch, tickets or status word would show)."""
+    import torch
+    gen = torch.Generator(device="cuda").manual_seed(20260917 + 80)
+    s1, s2 = torch.cuda.Stream(), torch.cuda.Stream()
+    m, n, k = 1024, 8192, 2048
+    A = torch.randint(-128, 128, (m, k), dtype=torch.int8, device="cuda", generator=gen)
+    B = torch.randint(-128, 128, (k, n), dtype=torch.int8, device="cuda", generator=gen)
+    want = (A.double() @ B.double()).to(torch.int32)
+    fa = torch.rand((16, 4096), device="cuda", generator=gen) * 2 - 1
+    fb = torch.rand((4096, 4096), device="cuda", generator=gen) * 2 - 1
+    fwant = fa.double() @ fb.double()
+    outs_i, outs_f = [], []
+    torch.cuda.synchronize()
+    last = None
+    for rep in range(6):
+        stream = s1 if rep % 2 == 0 else s2
+        with torch.cuda.stream(stream):
+            if last is not None:
+                stream.wait_event(last)
+            C = torch.full((m, n), -2**31, dtype=torch.int32, device="cuda")
+            F = torch.full((16, 4096), float("nan"), device="cuda")
+            handle = int(stream.cuda_stream)
+            native.i8gemm(A, B, C, m, n, k, variant=native.VT_I8_CTA_PAIR_SHARED_TAIL if rep % 3 == 0 else 0,
+                          where=native.VT_DEVICE, stream=handle)
+            native.sgemm(fa, fb, F, 16, 4096, 4096, where=native.VT_DEVICE, stream=handle)
+            last = torch.cuda.Event()
+            last.record(stream)
+            outs_i.append(C)
+            outs_f.append(F)
+    torch.cuda.synchronize()
+    native.sync(0, int(s2.cuda_stream))
+    for C in outs_i:
+        assert torch.equal(C, want)
+    for F in outs_f:
+        assert float(torch.linalg.norm(F.double() - fwant) / torch.linalg.norm(fwant)) <= 1e-5

@@ -203,7 +203,8 @@ i8gemm_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1;
     }
-    if (lane == 0) tma_store_wait_all<0>();   // C fully written before shared memory goes away
+    // The stores have read their shared-memory buffers; the writes themselves complete before the grid does.
+    if (lane == 0) tma_store_wait_read<0>();
     __syncwarp();
   }
 
@@ -537,7 +538,8 @@ i8gemm_umma_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
       it = next;
       have = more;
     }
-    if (lane == 0) tma_store_wait_all<0>();
+    // The stores have read their shared-memory buffers; the writes themselves complete before the grid does.
+    if (lane == 0) tma_store_wait_read<0>();
     __syncwarp();
   }
 

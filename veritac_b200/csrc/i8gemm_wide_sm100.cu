@@ -205,7 +205,8 @@ i8gemm_umma_pair_wide_kernel(const __grid_constant__ CUtensorMap tmA, const __gr
       if (lane == 0) mbar_arrive_remote(&ps->tmem_empty, 0);
       acc_phase ^= 1;
     }
-    if (lane == 0) tma_store_wait_all<0>();
+    // The stores have read their shared-memory buffers; the writes themselves complete before the grid does.
+    if (lane == 0) tma_store_wait_read<0>();
     __syncwarp();
   }
 

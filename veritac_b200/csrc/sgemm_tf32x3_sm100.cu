@@ -308,7 +308,8 @@ sgemm_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_
         }
       }
     }
-    if (lane == 0) tma_store_wait_all<0>();
+    // The stores have read their shared-memory buffers; the writes themselves complete before the grid does.
+    if (lane == 0) tma_store_wait_read<0>();
     __syncwarp();
   }
 

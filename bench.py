@@ -719,7 +719,7 @@ def run_gpu_arm(args, kind, M, N, K, batch, metric, unit):
             also[name] = {"metric": metric_of(wl)[0], "ms_per_step": a_ms, "value": j.value(a_ms), "unit": metric_of(wl)[1],
                           "rows_per_gpu": j.rows, "global_rows": int(j.total_rows), "launches": int(a_launches),
                           "steps": steps, "parity_ok": ok,
-                          "sharding": "replicas (16 rows do not shard); value is one replica's" if j.replicas else
+                          "sharding": "replicas (too few rows to shard); value is one replica's" if j.replicas else
                                       ("batch dealt over the ranks" if j.kind == "i8b" else "M rows per rank") if world > 1 else "single GPU",
                           "roofline": {k: roof[k] for k in ("bound", "achieved", "peak", "unit", "frac")}}
             j.release()

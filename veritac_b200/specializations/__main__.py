@@ -1,23 +1,29 @@
-"""`python -m veritac_b200.specializations list|show <id>`: print descriptions; launches nothing."""
-import argparse
+"""Command line of the specialization catalog: `python -m veritac_b200.specializations list` prints every
+description, `... show <id>` prints one.  Reads JSON files only; no device, no numpy, no torch.
+
+Same two commands, same JSON on stdout and the same error texts as the reference's `python -m specializations`.
+"""
 import json
+import sys
 
-from .catalog import describe, list_specializations
+from . import catalog
+
+USAGE = "usage: python -m veritac_b200.specializations list | show <specialization>"
 
 
-def main():
-    parser = argparse.ArgumentParser(description=__doc__)
-    sub = parser.add_subparsers(dest="command", required=True)
-    sub.add_parser("list", help="List specializations without loading hardware dependencies")
-    show = sub.add_parser("show", help="Show one specialization description")
-    show.add_argument("specialization")
-    args = parser.parse_args()
-    try:
-        result = list_specializations() if args.command == "list" else describe(args.specialization)
-    except ValueError as error:
-        parser.error(str(error))
-    print(json.dumps(result, indent=2))
+def run(argv):
+    """Returns (exit status, text).  Status 2 with a usage / error message, as argparse would give."""
+    if argv == ["list"]:
+        return 0, json.dumps(catalog.list_specializations(), indent=2)
+    if len(argv) == 2 and argv[0] == "show":
+        try:
+            return 0, json.dumps(catalog.describe(argv[1]), indent=2)
+        except ValueError as problem:
+            return 2, "%s\nerror: %s" % (USAGE, problem)
+    return 2, USAGE
 
 
 if __name__ == "__main__":
-    main()
+    status, text = run(sys.argv[1:])
+    print(text, file=sys.stdout if status == 0 else sys.stderr)
+    sys.exit(status)

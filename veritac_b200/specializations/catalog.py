@@ -1,28 +1,39 @@
-"""Find specialization descriptions without importing any runtime (no numpy, torch or CUDA).
+"""The specialization catalog: descriptions of the back ends, readable without any runtime.
 
-Drop-in for the reference's specializations/catalog.py (:13-26): `describe(name)` and
-`list_specializations()` read `<name>/specialization.json` next to this file and raise ValueError
-for a malformed identifier, an unknown name or a description whose id / schema_version is wrong.
+Each back end keeps a `specialization.json` in its package directory.  `describe(name)` returns one,
+`list_specializations()` all of them in name order.  Nothing here imports numpy, torch or the CUDA library, so a
+tool can list what exists on a machine that has none of them.  The two functions, their return values and the
+ValueError texts are those of the reference's specializations/catalog.py:13-26, which callers match on.
 """
 import json
+import re
 from pathlib import Path
 
-PACKAGES = Path(__file__).resolve().parent
+PACKAGES = Path(__file__).resolve().parent          # one sub-directory per specialization
 ROOT = PACKAGES.parent
-_ALLOWED = frozenset("abcdefghijklmnopqrstuvwxyz0123456789_")
+SCHEMA_VERSION = 1
+_IDENTIFIER = re.compile(r"[a-z0-9_]+\Z")
+
+
+def _description_file(name):
+    return PACKAGES / name / "specialization.json"
 
 
 def describe(name):
-    if not isinstance(name, str) or not name or not set(name) <= _ALLOWED:
+    """The description of specialization `name`; ValueError for a name that is not lower-case letters, digits
+    and underscores, for a name without a description file, and for a file that names another id or schema."""
+    if not (isinstance(name, str) and _IDENTIFIER.match(name)):
         raise ValueError("invalid specialization identifier")
-    path = PACKAGES / name / "specialization.json"
-    if not path.is_file():
-        raise ValueError(f"unknown specialization: {name}")
-    info = json.loads(path.read_text())
-    if info.get("id") != name or info.get("schema_version") != 1:
-        raise ValueError(f"invalid specialization description: {name}")
-    return info
+    source = _description_file(name)
+    if not source.is_file():
+        raise ValueError("unknown specialization: %s" % name)
+    with open(source, encoding="utf-8") as handle:
+        description = json.load(handle)
+    if (description.get("id"), description.get("schema_version")) != (name, SCHEMA_VERSION):
+        raise ValueError("invalid specialization description: %s" % name)
+    return description
 
 
 def list_specializations():
-    return [describe(p.parent.name) for p in sorted(PACKAGES.glob("*/specialization.json"))]
+    names = sorted(entry.name for entry in PACKAGES.iterdir() if _description_file(entry.name).is_file())
+    return [describe(name) for name in names]

@@ -33,7 +33,11 @@ void raster_for(int raster, int batch_rows, int64_t M, int* mode, int* group) {
       *group = int((rows + 127) / 128);
       break;
     }
-    default: *mode = 2; *group = 16; break;
+    // VT_RASTER_AUTO: sweeps of 32 tile-rows of 128 (16 pair tiles): the rows of A of a sweep (32 MiB at K = 8192) stay
+    // in L2 while B streams past once per sweep.  Measured at 8192^3, one process, 30-launch bursts, us per launch:
+    // 16 tile-rows 358.7, 24 356.8, 32 354.6, 40 359.4, 48 369.4, 64 396-461, 8 378.7; the same order at
+    // 16384 x 8192 x 4096 (389.2 / 383.3) and 8192 x 16384 x 8192 (711.7 / 705.0).
+    default: *mode = 2; *group = 32; break;
   }
   (void)M;
 }

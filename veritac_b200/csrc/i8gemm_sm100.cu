@@ -232,8 +232,14 @@ constexpr int P_A_BYTES = 128 * BK;                 // this CTA's 128 rows of A
 constexpr int P_B_BYTES = 128 * BK;                 // this CTA's 128 columns of B (one TMA box)
 constexpr int P_STAGE_BYTES = P_A_BYTES + P_B_BYTES;
 constexpr int P_STAGES = 6;
-constexpr int P_THREADS = 320;                      // 1 TMA warp, 1 MMA warp, 8 epilogue warps (two per TMEM lane quarter)
-constexpr int P_EPI_WARPS = 8;
+// Epilogue warps per CTA: four (one per TMEM lane quarter, 32 rows x 256 columns each) or eight (two per quarter, 128
+// columns each).  Measured in one process at 8192^3 and at 2048 x 8192 x 8192: four are 2 % ahead (350.4 against
+// 357.5 us, 94.7 against 96.6 us); the launch runs at the power cap, and warps that only wait still cost.
+constexpr int P_EPI_WARPS = 4;
+constexpr int P_EPI_BUFS = 1;                       // store buffers (4 KiB) per epilogue warp
+constexpr int P_THREADS = 32 * (2 + P_EPI_WARPS);   // 1 TMA warp, 1 MMA warp, the epilogue warps
+constexpr int P_WARP_CHUNKS = 8 / (P_EPI_WARPS / 4);   // 32-column chunks of the accumulator one epilogue warp moves
+static_assert(P_EPI_WARPS == 4 || P_EPI_WARPS == 8, "one or two epilogue warps per TMEM lane quarter");
 constexpr int P_RANGE_TABLE = 32;
 constexpr int P_TAIL_ITEMS = 4;                     // a pair's range is at most one tile long: a partial piece and <= 2 tiles
 constexpr size_t P_SLOT_UINT4 = size_t(128) * 256 * 4 / 16;   // one CTA's partial accumulator
@@ -266,7 +272,9 @@ struct PairRangeTable {
   }
 };
 
-constexpr size_t PAIR_SMEM_BYTES = 1024 + size_t(P_STAGES) * P_STAGE_BYTES + size_t(P_EPI_WARPS) * EPI_BUF_BYTES + 512;
+constexpr size_t PAIR_SMEM_BYTES =
+    1024 + size_t(P_STAGES) * P_STAGE_BYTES + size_t(P_EPI_WARPS) * P_EPI_BUFS * EPI_BUF_BYTES + 512;
+static_assert(PAIR_SMEM_BYTES <= 227 * 1024, "shared memory per CTA");
 static_assert(sizeof(PairPipeState) <= 512, "pipeline state outgrew its shared-memory reserve");
 
 // Item `i` of this pair in execution order (pair_item of i8_pair_sched.cuh, with the tail items read from shared
@@ -306,7 +314,7 @@ i8gemm_umma_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
   // C is written once and never read here: its lines should be the first to leave L2, so that A and B
   // (128 MiB at 8192^3, about the size of L2) stay (measured +0.5 %).
   const uint64_t store_policy = l2_policy_evict_first();
-  PairPipeState* ps = reinterpret_cast<PairPipeState*>(staging + P_EPI_WARPS * EPI_BUF_BYTES);
+  PairPipeState* ps = reinterpret_cast<PairPipeState*>(staging + P_EPI_WARPS * P_EPI_BUFS * EPI_BUF_BYTES);
   volatile int* abort_word = &ps->abort_word;
 
   const int warp = threadIdx.x >> 5;
@@ -460,11 +468,11 @@ i8gemm_umma_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
     }
     __syncwarp();
   } else {
-    // ------------------------------ epilogue (both CTAs, 8 warps) ------------------------------
-    // Warp e of 8 owns TMEM lane quarter (warp % 4) and column half (e / 4): 32 rows x 128 columns.
+    // ------------------------------ epilogue (both CTAs) ------------------------------
+    // Epilogue warp e owns TMEM lane quarter (warp % 4) and, with two warps per quarter, column half (e / 4).
     const int e = warp - 2;
     const int q = warp & 3;
-    const int c_begin = (e >> 2) * 4, c_end = c_begin + 4;
+    const int c_begin = (e >> 2) * P_WARP_CHUNKS, c_end = c_begin + P_WARP_CHUNKS;
     int acc = 0;
     uint32_t acc_phase = 0;
     // This quarter's part of a CTA's scratch slot and this warp's flag: pair p, CTA rank r -> slot 2p + r.
@@ -500,9 +508,10 @@ i8gemm_umma_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
           merge = partials + (size_t(it.contrib0) * 2 + rank) * P_SLOT_UINT4 + warp_off;
         }
         // The last item's epilogue overlaps nothing, and by now every MMA of this pair has read its operands and
-        // no load is in flight: the operand ring serves as one store buffer per column chunk (8 warps x 16 KiB).
-        uint8_t* wide = more ? nullptr : tiles + size_t(e) * 4 * EPI_BUF_BYTES;
-        epilogue_warp_tile<1>(t_row, &tmC, staging + e * EPI_BUF_BYTES, M, N, m0 + q * 32, n0, lane, store_policy, wide,
+        // no load is in flight: the operand ring serves as one store buffer per column chunk (128 KiB in all).
+        uint8_t* wide = more ? nullptr : tiles + size_t(e) * P_WARP_CHUNKS * EPI_BUF_BYTES;
+        epilogue_warp_tile<P_EPI_BUFS>(t_row, &tmC, staging + e * P_EPI_BUFS * EPI_BUF_BYTES, M, N, m0 + q * 32, n0, lane,
+                                       store_policy, wide,
                               merge, n_merge, 2 * P_SLOT_UINT4, c_begin, c_end);
         if (n_merge > 0) {
           __syncwarp();

@@ -26,8 +26,11 @@ namespace {
 constexpr int W_BK = 128;                           // int8 elements == bytes: one 128-byte swizzle row of K
 constexpr int W_UMMA_K = 32;
 constexpr int W_STAGES = 4;
-constexpr int W_THREADS = 320;                      // 1 TMA warp, 1 MMA warp, 8 epilogue warps
-constexpr int W_EPI_WARPS = 8;
+constexpr int W_EPI_WARPS = 8;                      // two per TMEM lane quarter: one per half of the wide tile
+constexpr int W_THREADS = 32 * (2 + W_EPI_WARPS);   // 1 TMA warp, 1 MMA warp, the epilogue warps
+constexpr int W_WARP_CHUNKS = 16 / (W_EPI_WARPS / 4);   // 32-column chunks of the two accumulators one warp moves
+constexpr int W_WIDE_BUFS = 48 / W_EPI_WARPS;       // store buffers per warp that the idle operand ring (192 KiB) provides
+static_assert(W_EPI_WARPS == 4 || W_EPI_WARPS == 8, "one or two epilogue warps per TMEM lane quarter");
 constexpr int W_A_BYTES = 128 * W_BK;               // this CTA's 128 rows of A
 constexpr int W_B_BYTES = 128 * W_BK;               // this CTA's 128 columns of one half's B
 constexpr int W_STAGE_BYTES = W_A_BYTES + 2 * W_B_BYTES;   // 48 KiB
@@ -182,10 +185,10 @@ i8gemm_umma_pair_wide_kernel(const __grid_constant__ CUtensorMap tmA, const __gr
     __syncwarp();
   } else {
     // ------------------------------ epilogue (both CTAs, 8 warps) ------------------------------
-    // Warp e of 8 owns TMEM lane quarter (warp % 4) and one half of the wide tile (e / 4): 32 rows x 256 columns.
+    // Epilogue warp e owns TMEM lane quarter (warp % 4) and, with two warps per quarter, one half of the wide tile.
     const int e = warp - 2;
     const int q = warp & 3;
-    const int c_begin = (e >> 2) * 8, c_end = c_begin + 8;
+    const int c_begin = (e >> 2) * W_WARP_CHUNKS, c_end = c_begin + W_WARP_CHUNKS;
     uint32_t acc_phase = 0;
     for (int t = pair; t < num_tiles; t += num_pairs) {
       int mi, ni;
@@ -196,9 +199,9 @@ i8gemm_umma_pair_wide_kernel(const __grid_constant__ CUtensorMap tmA, const __gr
       tc_fence_after_sync();
       const uint32_t t_row = tmem_base + (uint32_t(q * 32) << 16);
       // After the pair's last tile every MMA has read its operands and no load is in flight: the operand ring then
-      // serves as six store buffers per warp (8 x 24 KiB), so that few stores wait for a buffer.
-      uint8_t* wide = t + num_pairs >= num_tiles ? tiles + size_t(e) * 6 * EPI_BUF_BYTES : nullptr;
-      epilogue_warp_tile<1, 6>(t_row, &tmC, staging + e * EPI_BUF_BYTES, M, N, m0 + q * 32, n0, lane, store_policy, wide,
+      // serves as store buffers (192 KiB shared out between the warps), so that few stores wait for a buffer.
+      uint8_t* wide = t + num_pairs >= num_tiles ? tiles + size_t(e) * W_WIDE_BUFS * EPI_BUF_BYTES : nullptr;
+      epilogue_warp_tile<1, W_WIDE_BUFS>(t_row, &tmC, staging + e * EPI_BUF_BYTES, M, N, m0 + q * 32, n0, lane, store_policy, wide,
                                nullptr, 0, 0, c_begin, c_end);
       tc_fence_before_sync();
       __syncwarp();

@@ -27,7 +27,7 @@ struct DeviceCtx {
   int* status = nullptr;               // device word kernels write a KSTAT_* code into
   int* status_host = nullptr;          // pinned mirror
   int* tickets = nullptr;              // kTicketCount zeroed counters (per-slab arrival counts of the skinny kernel)
-  // int8 CTA-pair kernel: one 128 x 256 int32 partial accumulator per CTA and eight flags, one per epilogue warp (zero
+  // int8 CTA-pair kernel: one 128 x 256 int32 partial accumulator per CTA and up to eight flags, one per epilogue warp (zero
   // between launches), sized for one CTA per SM at context creation so that no launch ever allocates
   void* i8_partials = nullptr;
   int* i8_flags = nullptr;

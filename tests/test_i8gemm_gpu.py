@@ -492,3 +492,33 @@ def test_two_streams_joined_by_events(native):
         assert torch.equal(C, want)
     for F in outs_f:
         assert float(torch.linalg.norm(F.double() - fwant) / torch.linalg.norm(fwant)) <= 1e-5
+
+
+def test_host_rows_against_a_device_resident_b(native):
+    """where = VT_HOST_AC_DEVICE_B: a rank's rows of A and C in host memory, the replicated B already on the device,
+    produced on the stream the call is given (here a copy queued right before the call, standing in for the
+    broadcast).  Plain and batched entry points, pinned and pageable host buffers, every cell against the exact product."""
+    import torch
+    gen = torch.Generator(device="cuda").manual_seed(20260917 + 71)
+    st = native.torch_stream()
+    for (m, n, k) in ((1024, 8192, 8192), (4096 + 16, 2048 + 16, 528), (16, 16, 16)):
+        A = torch.randint(-128, 128, (m, k), dtype=torch.int8, device="cuda", generator=gen)
+        B = torch.randint(-128, 128, (k, n), dtype=torch.int8, device="cuda", generator=gen)
+        want = (A.double() @ B.double()).to(torch.int32).cpu()
+        hA = A.cpu().pin_memory()
+        hC = torch.full((m, n), -2**31, dtype=torch.int32).pin_memory()
+        dB = torch.zeros_like(B)
+        dB.copy_(B, non_blocking=True)                       # still in flight on `st` when the call is made
+        native.i8gemm(hA, dB, hC, m, n, k, where=native.VT_HOST_AC_DEVICE_B, stream=st)
+        assert torch.equal(hC, want), (m, n, k)
+        pageable = np.full((m, n), -2**31, dtype=np.int32)
+        native.i8gemm(A.cpu().numpy(), dB, pageable, m, n, k, where=native.VT_HOST_AC_DEVICE_B, stream=st)
+        assert np.array_equal(pageable, want.numpy())
+    batch, m, n, k = 3, 256, 512, 384
+    A = torch.randint(-128, 128, (batch * m, k), dtype=torch.int8, device="cuda", generator=gen)
+    B = torch.randint(-128, 128, (k, n), dtype=torch.int8, device="cuda", generator=gen)
+    hC = torch.full((batch * m, n), -2**31, dtype=torch.int32).pin_memory()
+    native.i8gemm_shared_b(A.cpu().pin_memory(), B, hC, batch, m, n, k, acc_rows=32, where=native.VT_HOST_AC_DEVICE_B, stream=st)
+    assert torch.equal(hC, (A.double() @ B.double()).to(torch.int32).cpu())
+    with pytest.raises(native.NativeError):                 # no such form for the other `where` values
+        native.i8gemm(hA, dB, hC, 16, 16, 16, where=7)

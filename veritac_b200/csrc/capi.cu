@@ -44,7 +44,7 @@ void raster_for(int raster, int batch_rows, int64_t M, int* mode, int* group) {
 
 // Two CTAs per tile need at least 256 rows to have work for both; below that one CTA per tile.  Products of more
 // than one but at most two 256 x 256 tiles per CTA pair (a 1024-row shard of an 8192-wide product on 74 pairs) run
-// as 256 x 512 tiles: the pair kernel's second round would be its last, so there is no later tile whose MMAs
+// as 256 x 512 tiles: the pair kernel's second wave of tiles would be its last, so there is no later tile whose MMAs
 // the wide form's exposed epilogue could have overlapped, and its K loop runs closer to the tensor pipe's rate
 // (measured 49.4 against 51.3 us at 1024 x 8192 x 8192; 96.8 against 98.1 at 2048 rows, 371 against 367 at 8192).
 int resolve_i8_variant(int variant, int64_t M, int64_t N, int sm_count) {

@@ -228,10 +228,14 @@ int choose_sgemm_variant(DeviceCtx* c, const float* dA, const float* dB, const f
       sgemm_skinny_umma_supported(dA, dB, dC, 1, N, K))
     return VT_SGEMM_PANEL_TF32X3;
   // Few columns against a large A: the mirror image (measured ahead of the tile kernels and the 3xTF32 pair kernel
-  // from 4 Mi elements of A up to 32 columns, from 12 Mi up to 64, from 16 Mi up to 128; two panels of 128 columns
-  // are level with the pair kernel and stay there).
+  // from 4 Mi elements of A up to 32 columns, from 12 Mi up to 64, from 16 Mi up to 128).
   if (N <= SKINNY_UMMA_MAX_ROWS && K >= 256 &&
       double(M) * double(K) >= (N <= 32 ? 4.0e6 : N <= 64 ? 1.2e7 : 1.6e7) && sgemm_tall_umma_supported(dA, dB, dC, M, N, K))
+    return VT_SGEMM_TALL_TF32X3;
+  // Two panels of 128 columns against a very large A: still ahead of the pair kernel (8192 x 256 x 8192: 0.294
+  // against 0.326 ms).
+  if (N <= 2 * SKINNY_UMMA_MAX_ROWS && K >= 256 && double(M) * double(K) >= 6.4e7 &&
+      sgemm_tall_umma_supported(dA, dB, dC, M, N, K))
     return VT_SGEMM_TALL_TF32X3;
   // Large products go to the tensor cores (3xTF32, measured ~1e-6 relative Frobenius error at any K) when that
   // is clearly faster than the best FFMA tile kernel.  Its time is modelled as two launches (6 us), the pass that

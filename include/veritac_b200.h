@@ -74,6 +74,11 @@ enum {
  *                          are added by the pair that owns the tile (exact).  Measured level with CTA_PAIR
  *                          (the pairs then no longer walk K in step and the L2 serves them more slowly),
  *                          so VT_I8_AUTO does not choose it.
+ *   CTA_PAIR_SPLIT_TAIL    the same kernel; when the last wave has at most half as many tiles as there are CTA
+ *                          pairs, every tile of it is cut into 2 to 4 equal K pieces that as many pairs compute
+ *                          last and side by side; the pair with the last piece adds the others' sums (exact).
+ *                          Measured level with CTA_PAIR as well (a pair's K block takes less time while other
+ *                          pairs idle, so a half-empty last wave costs little); VT_I8_AUTO does not choose it.
  *   CTA_PAIR_WIDE          two CTAs per 256x512 tile: both halves share the pair's rows of A, which cuts the
  *                          operand traffic per product by a quarter; tensor memory is then full, so a tile's
  *                          epilogue does not overlap the next tile's MMAs.  For products of few tiles per pair
@@ -84,7 +89,8 @@ enum {
   VT_I8_B_AS_STORED = 1,
   VT_I8_CTA_PAIR_SHARED_TAIL = 2,
   VT_I8_CTA_PAIR = 3,
-  VT_I8_CTA_PAIR_WIDE = 4
+  VT_I8_CTA_PAIR_WIDE = 4,
+  VT_I8_CTA_PAIR_SPLIT_TAIL = 5
 };
 
 /* fp32 kernel variants.

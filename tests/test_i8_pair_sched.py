@@ -19,9 +19,9 @@ PROGRAM = r'''
 #include "i8_pair_sched.cuh"
 int main(int argc, char** argv) {
   const int pairs = atoi(argv[1]), tiles = atoi(argv[2]), kb = atoi(argv[3]), share = atoi(argv[4]);
-  vt::PairSched s = vt::make_pair_sched(pairs, tiles, kb, share != 0);
-  if (s.tail == 0) s = vt::make_pair_sched(tiles < pairs ? tiles : pairs, tiles, kb, false);
-  printf("S %d %d %d\n", s.pairs, s.whole_waves, s.tail);
+  vt::PairSched s = vt::make_pair_sched(pairs, tiles, kb, share);
+  if (s.tail == 0) s = vt::make_pair_sched(tiles < pairs ? tiles : pairs, tiles, kb, vt::PAIR_SHARE_NONE);
+  printf("S %d %d %d %d\n", s.pairs, s.whole_waves, s.tail, s.split);
   for (int p = 0; p < s.pairs; ++p) {
     vt::PairItem it;
     for (int i = 0; vt::pair_item(s, p, i, it); ++i)
@@ -56,7 +56,10 @@ def run(exe, pairs, tiles, kb, share=1):
 
 
 def check(head, items, tiles, kb):
-    grid_pairs, whole_waves, tail = head
+    grid_pairs, whole_waves, tail, split = head
+    last_index = {}
+    for p, i, *_rest in items:
+        last_index[p] = max(last_index.get(p, 0), i)
     covered = {}
     finished = {}
     partial_of = {}
@@ -72,7 +75,10 @@ def check(head, items, tiles, kb):
             assert (tile, k) not in covered, "K block computed twice"
             covered[(tile, k)] = p
         if kind == 1:
-            assert i == 0, "a partial sum must be the pair's first item"
+            if split:     # equal split: every piece is its pair's last item, so all pieces start together
+                assert i == last_index[p] and kb1 - kb0 in (kb // split, kb // split + 1)
+            else:
+                assert i == 0, "a partial sum must be the pair's first item"
             assert p not in partial_of, "one scratch slot per pair"
             assert kb1 < kb, "the piece that holds a tile's last K block finishes the tile"
             partial_of[p] = tile
@@ -83,6 +89,8 @@ def check(head, items, tiles, kb):
     assert len(covered) == tiles * kb
     assert sorted(finished) == list(range(tiles))
     for tile, (p, kb0, c0, nc) in finished.items():
+        if split and nc:
+            assert nc == split - 1 and [x for x in items if x[0] == p][-1][2] == tile   # the owner's piece is its last item
         contributors = sorted(q for q, t in partial_of.items() if t == tile)
         assert contributors == list(range(c0, c0 + nc)) if nc else contributors == []
         assert (kb0 > 0) == (nc > 0)
@@ -99,15 +107,28 @@ CASES = [(74, 128, 64), (74, 256, 64), (74, 1024, 64), (74, 54, 64), (74, 1, 64)
          (66, 128, 64), (3, 7, 5), (74, 111, 17), (74, 4096, 32), (74, 129, 2)]
 
 
-@pytest.mark.parametrize("share", [1, 0])
+@pytest.mark.parametrize("share", [1, 2, 0])
 def test_every_k_block_once_and_every_tile_finished_once(sched_program, share):
-    for pairs, tiles, kb in CASES:
+    for pairs, tiles, kb in CASES + [(74, 256, 64), (74, 90, 64), (74, 108, 96), (74, 37 + 74, 33), (74, 10, 256)]:
         head, items = run(sched_program, pairs, tiles, kb, share)
         busiest, tail = check(head, items, tiles, kb)
         whole = -(-tiles // pairs) * kb
         assert busiest <= whole
         if not share:
             assert tail == 0 and busiest == whole
+
+
+def test_equal_split_of_a_short_tail(sched_program):
+    """2048 rows of an 8192-wide C: 256 tiles on 74 pairs, 34 left over: each is cut in two halves that 68 pairs
+    compute last, so the busiest pair does three and a half tiles instead of four.  A tail of more than half the
+    pairs is not split."""
+    head, items = run(sched_program, 74, 256, 64, 2)
+    busiest, tail = check(head, items, 256, 64)
+    assert head[3] == 2 and tail == 34 and busiest == 3 * 64 + 32
+    head, items = run(sched_program, 74, 128, 64, 2)
+    assert head[2] == 0 and head[3] == 0
+    head, items = run(sched_program, 74, 74 + 10, 64, 2)
+    assert head[3] == 4 and check(head, items, 84, 64)[0] == 64 + 16
 
 
 def test_shared_tail_balances_the_strong_scaling_shards(sched_program):

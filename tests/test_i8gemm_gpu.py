@@ -142,7 +142,7 @@ def test_config2_int8_64_cubed_partial_sums(native, g):
         assert (stats["overwrites"], stats["accumulates"]) == (256, 768)
 
 
-@pytest.mark.parametrize("variant", [0, 1, 2, 3, 4])
+@pytest.mark.parametrize("variant", [0, 1, 2, 3, 4, 5])
 def test_shapes_rasters_variants(native, variant):
     rng = np.random.default_rng(11)
     shapes = [(16, 16, 16), (16, 80, 32), (80, 16, 32), (48, 32, 64), (128, 256, 128), (144, 272, 400),
@@ -343,14 +343,16 @@ def _device_case(native, m, n, k, seed, variant=0, reps=2):
         assert torch.equal(C, want), (m, n, k, variant, rep)
 
 
-@pytest.mark.parametrize("variant", [0, 2, 4])
+@pytest.mark.parametrize("variant", [0, 2, 4, 5])
 def test_shared_tail_of_the_pair_kernel(native, variant):
     """Shapes whose 256 x 256 tiles do not fill whole waves of the 74 CTA pairs: the K blocks of the last wave
     are dealt to all pairs and partial int32 sums meet in scratch memory.  The 1024- and 2048-row shards of the
     8192^3 problem (8 and 4 GPUs), fewer tiles than pairs, ragged edges, K not a multiple of the 128-value
     block, a long K with several contributors per tile."""
     shapes = [(1024, 8192, 8192), (2048, 8192, 8192), (1536, 4864, 4096), (512, 5376, 4096), (1000 - 8, 8192 - 48, 8192 + 48),
-              (768, 3072, 32768), (256, 2560, 65536), (2048 + 16, 5120 + 16, 16384 + 16)]
+              (768, 3072, 32768), (256, 2560, 65536), (2048 + 16, 5120 + 16, 16384 + 16),
+              # tails of at most half the pairs: cut into 2, 3 and 4 equal pieces by the equal-split form
+              (2048 - 16, 8192 + 32, 4096 + 16), (1280, 4352, 3072), (768, 7168, 2048)]
     for i, (m, n, k) in enumerate(shapes):
         _device_case(native, m, n, k, 20260917 + 40 + i, variant=variant)
 
@@ -364,7 +366,8 @@ def test_shared_tail_equals_whole_tiles(native):
     B = torch.randint(-128, 128, (k, n), dtype=torch.int8, device="cuda", generator=gen)
     st = native.torch_stream()
     outs = []
-    for variant in (native.VT_I8_CTA_PAIR, native.VT_I8_CTA_PAIR_SHARED_TAIL, native.VT_I8_CTA_PAIR_WIDE):
+    for variant in (native.VT_I8_CTA_PAIR, native.VT_I8_CTA_PAIR_SHARED_TAIL, native.VT_I8_CTA_PAIR_WIDE,
+                    native.VT_I8_CTA_PAIR_SPLIT_TAIL):
         for raster, br in ((0, 1), (1, 1), (2, 3), (3, 1)):
             C = torch.full((m, n), -2**31, dtype=torch.int32, device="cuda")
             native.i8gemm(A, B, C, m, n, k, variant=variant, raster=raster, batch_rows=br, where=native.VT_DEVICE, stream=st)

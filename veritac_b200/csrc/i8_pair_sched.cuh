@@ -17,6 +17,14 @@
 //   * a pair without a partial piece runs  owned tail tiles, whole tiles,  and a pair without whole tiles
 //     partial, owned tail tiles: there the contributors' sums are added in the epilogue of the owned tile
 //     (overlapping the whole tile after it, where there is one).
+//
+// A second way to share the tail ("equal split") keeps the pairs walking K in step, which the L2 rewards:
+// when the tail has at most half as many tiles as there are pairs, every tail tile is cut into
+// s = floor(P / tail) equal K pieces (at most 4), piece k of tile j goes to pair j * s + k, and every pair runs
+// its piece *last*, after its whole tiles, so that all pieces start together.  The pair with the last piece owns
+// the tile and adds the others' sums in its epilogue; their partial sums are the last thing those pairs do, and
+// nobody waits for anything else, so the owners' waits end.  The merge is then exposed at the end of the launch
+// (a few microseconds) in exchange for (1 - 1/s) of a tile's time.
 #pragma once
 
 #include <stdint.h>
@@ -31,7 +39,10 @@ struct PairSched {
   int kblocks;      // KB
   int whole_waves;  // whole tiles per pair
   int tail;         // tiles whose K-blocks are shared (0: every tile is computed whole by one pair)
+  int split;        // 0: the tail's K-blocks are cut into one range per pair; s >= 2: every tail tile into s equal pieces
 };
+
+enum : int { PAIR_SHARE_NONE = 0, PAIR_SHARE_RANGES = 1, PAIR_SHARE_EQUAL_SPLIT = 2 };
 
 enum : int { PAIR_ITEM_TO_C = 0, PAIR_ITEM_PARTIAL = 1 };
 
@@ -46,15 +57,25 @@ struct PairItem {
 
 // Whether sharing the tail pays: the idle part of the last wave must be worth more than the extra
 // epilogues and the merge (about ten K-blocks' time per pair), and ranges must not be slivers.
-__host__ __device__ inline PairSched make_pair_sched(int pairs, int tiles, int kblocks, bool share_tail) {
+__host__ __device__ inline PairSched make_pair_sched(int pairs, int tiles, int kblocks, int share) {
   PairSched s;
   s.pairs = pairs;
   s.tiles = tiles;
   s.kblocks = kblocks;
   s.whole_waves = tiles / pairs;
   s.tail = 0;
+  s.split = 0;
   const int tail = tiles - s.whole_waves * pairs;
-  if (share_tail && tail > 0) {
+  if (share == PAIR_SHARE_EQUAL_SPLIT && tail > 0) {
+    int pieces = pairs / tail;
+    if (pieces > 4) pieces = 4;                       // more contributors cost the owner more than they save
+    while (pieces >= 2 && kblocks / pieces < 8) --pieces;   // no slivers
+    if (pieces >= 2) {
+      s.tail = tail;
+      s.split = pieces;
+    }
+  }
+  if (share == PAIR_SHARE_RANGES && tail > 0) {
     const long long units = (long long)tail * kblocks;
     const long long per = units / pairs;
     const long long idle = (long long)(pairs - tail) * kblocks;   // pair-K-blocks the whole-tile order leaves unused
@@ -89,6 +110,7 @@ struct PairRangeDirect {
 template <class RangeBegin>
 __host__ __device__ inline int pair_tail_items(const PairSched& s, int pair, const RangeBegin& begin) {
   if (s.tail == 0) return 0;
+  if (s.split) return pair < s.tail * s.split ? 1 : 0;
   const int u0 = begin(pair), u1 = begin(pair + 1);
   if (u1 <= u0) return 0;
   const int j_end = u1 / s.kblocks;
@@ -104,12 +126,26 @@ template <class RangeBegin>
 __host__ __device__ inline void pair_tail_item(const PairSched& s, int pair, int t, PairItem& out, const RangeBegin& begin) {
   const int KB = s.kblocks;
   const int first_tail_tile = s.whole_waves * s.pairs;
-  const int u0 = begin(pair), u1 = begin(pair + 1);
-  const int j_first = u0 / KB, j_end = u1 / KB;                // tail tiles [j_first, j_end) end inside the range
-  const bool has_partial = u1 > u0 && u1 != j_end * KB;
   out.contrib0 = 0;
   out.ncontrib = 0;
   out.preload = 0;
+  if (s.split) {
+    const int j = pair / s.split, part = pair - j * s.split;
+    out.tile = first_tail_tile + j;
+    out.kb0 = part * KB / s.split;
+    out.kb1 = (part + 1) * KB / s.split;
+    if (part + 1 < s.split) {
+      out.kind = PAIR_ITEM_PARTIAL;
+    } else {
+      out.kind = PAIR_ITEM_TO_C;
+      out.contrib0 = j * s.split;
+      out.ncontrib = s.split - 1;
+    }
+    return;
+  }
+  const int u0 = begin(pair), u1 = begin(pair + 1);
+  const int j_first = u0 / KB, j_end = u1 / KB;                // tail tiles [j_first, j_end) end inside the range
+  const bool has_partial = u1 > u0 && u1 != j_end * KB;
   if (has_partial) {
     if (t == 0) {
       const int base = j_end * KB;
@@ -140,8 +176,10 @@ __host__ __device__ inline void pair_tail_item(const PairSched& s, int pair, int
   }
 }
 
-// Position of the whole tiles in a pair's order: after the partial piece when it has one, else after the tail.
-__host__ __device__ inline int pair_whole_first(int tail_items, bool first_is_partial) {
+// Position of the whole tiles in a pair's order.  Ranges: after the partial piece when the pair has one, else
+// after its tail items.  Equal split: first.
+__host__ __device__ inline int pair_whole_first(const PairSched& s, int tail_items, bool first_is_partial) {
+  if (s.split) return 0;
   return first_is_partial ? 1 : tail_items;
 }
 
@@ -167,7 +205,7 @@ __host__ __device__ inline bool pair_item(const PairSched& s, int pair, int idx,
     pair_tail_item(s, pair, 0, first, begin);
     first_is_partial = first.kind == PAIR_ITEM_PARTIAL;
   }
-  const int w0 = pair_whole_first(n_tail, first_is_partial);
+  const int w0 = pair_whole_first(s, n_tail, first_is_partial);
   if (idx >= w0 && idx < w0 + s.whole_waves) {
     out.tile = pair + (idx - w0) * s.pairs;
     return true;

@@ -281,7 +281,7 @@ static_assert(sizeof(PairPipeState) <= 512, "pipeline state outgrew its shared-m
 // memory): whole tiles come after the partial piece when the pair has one, else after its tail items.
 __device__ __forceinline__ bool pair_next(const PairSched& sched, const PairPipeState* ps, int pair, int i, PairItem& it) {
   const int n_tail = ps->tail_items;
-  const int w0 = pair_whole_first(n_tail, n_tail > 0 && ps->tail_item[0].kind == PAIR_ITEM_PARTIAL);
+  const int w0 = pair_whole_first(sched, n_tail, n_tail > 0 && ps->tail_item[0].kind == PAIR_ITEM_PARTIAL);
   if (i >= w0 && i < w0 + sched.whole_waves) {
     const long long tile = (long long)pair + (long long)(i - w0) * sched.pairs;
     if (tile < sched.tiles) {
@@ -578,7 +578,7 @@ int launch_i8gemm(DeviceCtx* c, const int8_t* A, const int8_t* B, int32_t* C, in
   if (ldc == 0) ldc = N;
   if (ldb < N || ldc < N || (ldb & 15) || (ldc & 3)) return fail(VT_ERR_INVALID, "bad row pitch for B or C");
   if (variant == VT_I8_CTA_PAIR_WIDE) return launch_i8gemm_wide(c, A, B, C, M, N, K, raster_mode, group, s, ldb, ldc);
-  if (variant < VT_I8_B_AS_STORED || variant > VT_I8_CTA_PAIR)
+  if ((variant < VT_I8_B_AS_STORED || variant > VT_I8_CTA_PAIR) && variant != VT_I8_CTA_PAIR_SPLIT_TAIL)
     return fail(VT_ERR_UNSUPPORTED, "i8gemm variant %d is not built", variant);
   if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(C)) & 15)
     return fail(VT_ERR_INVALID, "i8gemm operands must be 16-byte aligned");
@@ -616,12 +616,15 @@ int launch_i8gemm(DeviceCtx* c, const int8_t* A, const int8_t* B, int32_t* C, in
     VT_CUDA(cudaGetLastError());
     return VT_OK;
   }
-  // VT_I8_CTA_PAIR_SHARED_TAIL: the tail is shared only when all pairs of the device take part; otherwise, and for
-  // VT_I8_CTA_PAIR, every tile is computed whole by one pair.
+  // VT_I8_CTA_PAIR_SHARED_TAIL / _SPLIT_TAIL: the tail is shared only when all pairs of the device take part;
+  // otherwise, and for VT_I8_CTA_PAIR, every tile is computed whole by one pair.
   const int max_pairs = c->sm_count / 2;
   const int kblocks = int((K + BK - 1) / BK);
-  PairSched sched = make_pair_sched(max_pairs, int(tiles), kblocks, variant == VT_I8_CTA_PAIR_SHARED_TAIL);
-  if (sched.tail == 0) sched = make_pair_sched(int(tiles < max_pairs ? tiles : max_pairs), int(tiles), kblocks, false);
+  const int share = variant == VT_I8_CTA_PAIR_SHARED_TAIL ? PAIR_SHARE_RANGES
+                    : variant == VT_I8_CTA_PAIR_SPLIT_TAIL ? PAIR_SHARE_EQUAL_SPLIT : PAIR_SHARE_NONE;
+  PairSched sched = make_pair_sched(max_pairs, int(tiles), kblocks, share);
+  if (sched.tail == 0)
+    sched = make_pair_sched(int(tiles < max_pairs ? tiles : max_pairs), int(tiles), kblocks, PAIR_SHARE_NONE);
   if (!(c->func_attr_mask & 4u)) {
     VT_CUDA(cudaFuncSetAttribute(i8gemm_umma_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  int(PAIR_SMEM_BYTES)));

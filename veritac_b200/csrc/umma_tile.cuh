@@ -53,61 +53,91 @@ __device__ __forceinline__ void tile_coords(const TileRaster& rs, int t, int& mi
 // last read its buffer.
 // Returns once the accumulator has been read (the stores may still be in flight).
 template <int kBufs = 2, int kWide = 16>
+__device__ __forceinline__ void epilogue_store_chunk(const uint32_t (&r)[32], int c, int c_begin, const CUtensorMap* tmC,
+                                                     uint8_t* staging, int M, int N, int row0, int n0, int lane,
+                                                     uint64_t store_policy, uint8_t* wide) {
+  uint8_t* buf = wide ? wide + ((c - c_begin) % kWide) * EPI_BUF_BYTES : staging + (c & (kBufs - 1)) * EPI_BUF_BYTES;
+  if (!wide) {
+    if (lane == 0) tma_store_wait_read<kBufs - 1>();   // the store that last read this buffer is done with it
+    __syncwarp();
+  } else if (c - c_begin >= kWide) {
+    if (lane == 0) tma_store_wait_read<kWide - 1>();
+    __syncwarp();
+  }
+  const uint32_t base = smem_u32(buf) + uint32_t(lane) * 128u;
+#pragma unroll
+  for (int v = 0; v < 8; ++v)
+    st_shared_v4(base + (uint32_t(v ^ (lane & 7)) << 4), r[4 * v], r[4 * v + 1], r[4 * v + 2], r[4 * v + 3]);
+  fence_proxy_async_smem();
+  __syncwarp();
+  if (lane == 0) {
+    if (row0 < M && n0 + c * 32 < N) {
+      if (store_policy) tma_store_2d_hint(tmC, buf, n0 + c * 32, row0, store_policy);
+      else tma_store_2d(tmC, buf, n0 + c * 32, row0);
+    }
+    tma_store_commit();
+  }
+}
+
+template <int kBufs = 2, int kWide = 16>
 __device__ __forceinline__ void epilogue_warp_tile(uint32_t t_row, const CUtensorMap* tmC, uint8_t* staging, int M,
                                                    int N, int row0, int n0, int lane, uint64_t store_policy = 0,
                                                    uint8_t* wide = nullptr, const uint4* merge = nullptr,
                                                    int ncontrib = 0, size_t merge_stride = 0, int c_begin = 0,
                                                    int c_end = BN / 32) {
-  uint4 nxt[8];
-  if (ncontrib > 0) {
-#pragma unroll
-    for (int v = 0; v < 8; ++v) nxt[v] = ld_global_cg_v4(merge + size_t(c_begin) * 256 + v * 32);
+  if (ncontrib == 0) {
+#pragma unroll 1
+    for (int c = c_begin; c < c_end; ++c) {
+      uint32_t r[32];
+      tmem_ld_32x32b_x32(t_row + uint32_t(c * 32), r);
+      tmem_ld_wait();
+      epilogue_store_chunk<kBufs, kWide>(r, c, c_begin, tmC, staging, M, N, row0, n0, lane, store_policy, wide);
+    }
+    return;
   }
-#pragma unroll 1
-  for (int c = c_begin; c < c_end; ++c) {
-    uint32_t r[32];
-    tmem_ld_32x32b_x32(t_row + uint32_t(c * 32), r);
-    tmem_ld_wait();
-#pragma unroll 1
-    for (int x = 0; x < ncontrib; ++x) {
-      uint4 cur[8];
+  // With partial sums to add, the loads from scratch memory (L2 hits, ~1 us each way) set the pace unless several
+  // are in flight: the (chunk, contributor) steps are walked with kDepth loads of 128 bytes per lane outstanding.
+  constexpr int kDepth = 3;
+  const int steps = (c_end - c_begin) * ncontrib;
+  auto source = [&](int t) {
+    const int c = c_begin + t / ncontrib, x = t - (t / ncontrib) * ncontrib;
+    return merge + size_t(x) * merge_stride + size_t(c) * 256;
+  };
+  uint4 ahead[kDepth][8];
 #pragma unroll
-      for (int v = 0; v < 8; ++v) cur[v] = nxt[v];
-      const int nx = x + 1 == ncontrib ? 0 : x + 1;
-      const int nc = x + 1 == ncontrib ? c + 1 : c;
-      if (nc < c_end) {
-        const uint4* src = merge + size_t(nx) * merge_stride + size_t(nc) * 256;
+  for (int d = 0; d < kDepth; ++d)
+    if (d < steps) {
+      const uint4* src = source(d);
 #pragma unroll
-        for (int v = 0; v < 8; ++v) nxt[v] = ld_global_cg_v4(src + v * 32);
-      }
-#pragma unroll
-      for (int v = 0; v < 8; ++v) {
-        r[4 * v] += cur[v].x;
-        r[4 * v + 1] += cur[v].y;
-        r[4 * v + 2] += cur[v].z;
-        r[4 * v + 3] += cur[v].w;
-      }
+      for (int v = 0; v < 8; ++v) ahead[d][v] = ld_global_cg_v4(src + v * 32);
     }
-    uint8_t* buf = wide ? wide + ((c - c_begin) % kWide) * EPI_BUF_BYTES : staging + (c & (kBufs - 1)) * EPI_BUF_BYTES;
-    if (!wide) {
-      if (lane == 0) tma_store_wait_read<kBufs - 1>();   // the store that last read this buffer is done with it
-      __syncwarp();
-    } else if (c - c_begin >= kWide) {
-      if (lane == 0) tma_store_wait_read<kWide - 1>();
-      __syncwarp();
-    }
-    const uint32_t base = smem_u32(buf) + uint32_t(lane) * 128u;
+  uint32_t r[32];
+#pragma unroll 1
+  for (int t0 = 0; t0 < steps; t0 += kDepth) {
 #pragma unroll
-    for (int v = 0; v < 8; ++v)
-      st_shared_v4(base + (uint32_t(v ^ (lane & 7)) << 4), r[4 * v], r[4 * v + 1], r[4 * v + 2], r[4 * v + 3]);
-    fence_proxy_async_smem();
-    __syncwarp();
-    if (lane == 0) {
-      if (row0 < M && n0 + c * 32 < N) {
-        if (store_policy) tma_store_2d_hint(tmC, buf, n0 + c * 32, row0, store_policy);
-        else tma_store_2d(tmC, buf, n0 + c * 32, row0);
+    for (int d = 0; d < kDepth; ++d) {
+      const int t = t0 + d;
+      if (t < steps) {
+        const int c = c_begin + t / ncontrib, x = t - (t / ncontrib) * ncontrib;
+        if (x == 0) {
+          tmem_ld_32x32b_x32(t_row + uint32_t(c * 32), r);
+          tmem_ld_wait();
+        }
+#pragma unroll
+        for (int v = 0; v < 8; ++v) {
+          r[4 * v] += ahead[d][v].x;
+          r[4 * v + 1] += ahead[d][v].y;
+          r[4 * v + 2] += ahead[d][v].z;
+          r[4 * v + 3] += ahead[d][v].w;
+        }
+        if (t + kDepth < steps) {
+          const uint4* src = source(t + kDepth);
+#pragma unroll
+          for (int v = 0; v < 8; ++v) ahead[d][v] = ld_global_cg_v4(src + v * 32);
+        }
+        if (x == ncontrib - 1)
+          epilogue_store_chunk<kBufs, kWide>(r, c, c_begin, tmC, staging, M, N, row0, n0, lane, store_policy, wide);
       }
-      tma_store_commit();
     }
   }
 }

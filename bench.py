@@ -802,7 +802,8 @@ SHAPE_GRID = ((256, 256, 256), (512, 512, 512), (768, 768, 768), (1024, 1024, 10
               (65536, 16, 1024), (4096, 32, 4096), (2048, 64, 2048), (16384, 128, 512), (16, 8192, 8192), (64, 8192, 8192),
               (128, 8192, 8192), (300, 8192, 8192), (384, 4096, 4096), (512, 8192, 8192), (1024, 8192, 1024), (128, 512, 512),
               (200, 300, 400), (2000, 200, 2000), (4096, 4096, 256), (4096, 4096, 64), (8192, 8192, 128), (128, 128, 65536),
-              (1024, 64, 16384), (640, 640, 640), (1536, 1536, 1536), (3072, 512, 3072), (512, 3072, 3072))
+              (1024, 64, 16384), (640, 640, 640), (1536, 1536, 1536), (3072, 512, 3072), (512, 3072, 3072), (896, 896, 896),
+              (1000, 1000, 1000), (384, 384, 4096), (332, 776, 1112), (128, 128, 16384))
 
 
 def run_shape_grid(shapes):
@@ -817,6 +818,7 @@ def run_shape_grid(shapes):
     build.build()
     torch.backends.cuda.matmul.allow_tf32 = False
     names = {nv.VT_SGEMM_TILE128: "tile128", nv.VT_SGEMM_TILE64: "tile64", nv.VT_SGEMM_TILE32: "tile32",
+             nv.VT_SGEMM_PIPE128: "pipe128", nv.VT_SGEMM_PIPE64X128: "pipe64x128", nv.VT_SGEMM_PIPE64: "pipe64",
              nv.VT_SGEMM_TF32X3: "tf32x3", nv.VT_SGEMM_PANEL_TF32X3: "panel", nv.VT_SGEMM_TALL_TF32X3: "tall"}
     st = nv.torch_stream()
 
@@ -891,7 +893,7 @@ def main() -> int:
     ap.add_argument("--no-also", action="store_true", help="skip the other workloads and the weak figure")
     ap.add_argument("--shape-grid", nargs="*", metavar="MxNxK", default=None,
                     help="instead of a bench line: time every fp32 kernel variant, the automatic choice and cuBLAS on "
-                         "these shapes (no shapes: the built-in grid of 35) and print a markdown table")
+                         "these shapes (no shapes: the built-in grid of 40) and print a markdown table")
     args = ap.parse_args()
     if args.shape_grid is not None:
         return run_shape_grid([tuple(int(x) for x in a.lower().split("x")) for a in args.shape_grid] or list(SHAPE_GRID))

@@ -95,6 +95,13 @@ enum {
 
 /* fp32 kernel variants.
  *   TILE128 / TILE64  register-tiled FFMA kernel (true fp32 arithmetic), 128x128 or 64x64 CTA tiles
+ *   PIPE128 / PIPE64X128 / PIPE64
+ *                     true fp32 FFMA as well, second design: 128x128, 64x128 or 64x64 CTA tiles fed by a
+ *                     three-stage cp.async ring in the operands' own layout, 8x8 outputs per thread as packed pairs
+ *                     (fma.rn.f32x2); with few tiles K is split over the CTAs of a thread-block cluster, which add
+ *                     their partial tiles through each other's shared memory, in a fixed order: the mid-sized
+ *                     products, where the first design leaves SMs idle (N % 4 == 0, K % 4 == 0, 16-byte aligned
+ *                     operands)
  *   TILE32            32x32 CTA tiles, K brought in 256 at a time and split four ways inside the CTA (true fp32):
  *                     for products too small to fill the GPU with 64x64 tiles (N % 4 == 0, K % 4 == 0, aligned)
  *   SKINNY            M <= 16, N % 4 == 0: streams B once (HBM-bound), true fp32 FFMA arithmetic
@@ -122,7 +129,10 @@ enum {
   VT_SGEMM_SKINNY_MMA_SYNC = 6,
   VT_SGEMM_TILE32 = 7,
   VT_SGEMM_PANEL_TF32X3 = 8,
-  VT_SGEMM_TALL_TF32X3 = 9
+  VT_SGEMM_TALL_TF32X3 = 9,
+  VT_SGEMM_PIPE128 = 10,
+  VT_SGEMM_PIPE64 = 11,
+  VT_SGEMM_PIPE64X128 = 12
 };
 
 /* Number of CUDA devices visible, or a negative VT_ERR_* code. */
@@ -230,6 +240,14 @@ int vt_test_set_wait_hooks(int dev, int64_t wait_limit_cycles, int i8_stop_fill)
 /* TEST HOOK.  Launches one small CTA on `stream` that waits, with the bound set above, for a barrier that
  * nothing ever completes; the wait runs out and the kernel records its status and returns. */
 int vt_test_expire_wait(int dev, void* stream);
+
+/* TEST HOOK.  The FFMA tile kernels (VT_SGEMM_TILE128 / TILE64 / TILE32) split K over several CTAs per output
+ * tile when the tile grid alone would leave most of the GPU idle.  `splits` > 0 forces that many for later calls
+ * on `dev` (as far as K allows, at most 16; the 128- and 64-wide kernels exchange up to 8 partial tiles through
+ * the shared memory of a thread-block cluster and more through scratch memory), `splits` < 0 forces -splits
+ * through scratch memory, 0 restores the automatic choice.  Results are bit-identical from call to call for a
+ * given split (partial tiles are added in split order). */
+int vt_test_set_sgemm_splits(int dev, int splits);
 
 /* Pinned host memory for VT_HOST calls. */
 void* vt_host_alloc(size_t bytes);

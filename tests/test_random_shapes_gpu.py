@@ -48,8 +48,8 @@ def test_random_fp32_shapes(native):
         b = rng.random((k, n), dtype=np.float32) * 2 - 1
         ref = a.astype(np.float64) @ b.astype(np.float64)
         A, B = torch.from_numpy(a).cuda(), torch.from_numpy(b).cuda()
-        for variant in (0, 1, 2, 4, 7):
-            if variant in (4, 7) and (n % 4 or k % 4):
+        for variant in (0, 1, 2, 4, 7, 10, 11, 12):
+            if variant in (4, 7, 10, 11, 12) and (n % 4 or k % 4):
                 continue
             C = torch.full((m, n), float("nan"), device="cuda")
             native.sgemm(A, B, C, m, n, k, variant=variant, where=native.VT_DEVICE, stream=st)

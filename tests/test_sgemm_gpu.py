@@ -19,13 +19,13 @@ def uniform(rng, shape):
     return (rng.random(shape, dtype=np.float32) * 2 - 1)
 
 
-@pytest.mark.parametrize("variant", [0, 1, 2, 4, 7])
+@pytest.mark.parametrize("variant", [0, 1, 2, 4, 7, 10, 11, 12])
 def test_shapes_against_float64(native, variant):
     rng = np.random.default_rng(20260917 + 1)
     for (m, n, k) in ((256, 256, 256), (1, 1, 1), (5, 3, 2), (77, 130, 33), (300, 200, 100), (128, 128, 16),
                       (129, 127, 17), (512, 384, 1000), (1024, 1024, 1024), (64, 2048, 96), (40, 36, 260), (512, 512, 512),
                       (33, 4, 4)):
-        if variant in (4, 7) and (n % 4 or k % 4):
+        if variant in (4, 7, 10, 11, 12) and (n % 4 or k % 4):
             with pytest.raises(native.NativeError):     # the tensor-core variant needs 16-byte row pitches
                 native.sgemm(uniform(rng, (m, k)), uniform(rng, (k, n)), np.zeros((m, n), np.float32), m, n, k,
                              variant=variant)
@@ -34,6 +34,37 @@ def test_shapes_against_float64(native, variant):
         c = np.full((m, n), np.nan, dtype=np.float32)
         native.sgemm(a, b, c, m, n, k, variant=variant)
         assert relfro(c, a.astype(np.float64) @ b.astype(np.float64)) <= TOL, (m, n, k)
+
+
+@pytest.mark.parametrize("variant", [10, 12, 11, 7])
+def test_k_split_every_count_and_bit_identical_repeats(native, variant):
+    """The FFMA kernels that split K over several CTAs per output tile (the pipelined kernel over the CTAs of a
+    cluster, through their shared memory; the 32-wide kernel through scratch memory and a ticket per tile): every
+    split count the hook can force, on shapes with ragged edges, K not a multiple of a stage, more splits than K
+    has stages and more tiles than one wave of clusters holds, against float64; and the same call twice gives the
+    same bits, because partial tiles are added in split order whichever CTA finishes last."""
+    import torch
+    st = native.torch_stream()
+    gen = torch.Generator(device="cuda").manual_seed(811)
+    shapes = ((640, 640, 640), (200, 300, 400), (77, 132, 36), (128, 128, 4096), (1, 4, 64), (384, 520, 1000),
+              (1500, 1400, 260), (64, 64, 8192))
+    try:
+        for (m, n, k) in shapes:
+            A = torch.rand((m, k), device="cuda", generator=gen) * 2 - 1
+            B = torch.rand((k, n), device="cuda", generator=gen) * 2 - 1
+            ref = (A.double() @ B.double()).cpu().numpy()
+            for splits in ((0, 1, 2, 3, 5, 8) if variant != 7 else (0, 1, 2, 4, 7, 16)):
+                native.test_set_sgemm_splits(splits)
+                out = []
+                for rep in range(2):
+                    C = torch.full((m, n), float("nan"), device="cuda")
+                    native.sgemm(A, B, C, m, n, k, variant=variant, where=native.VT_DEVICE, stream=st)
+                    native.sync(0, st)
+                    out.append(C)
+                assert relfro(out[0].cpu().numpy(), ref) <= TOL, (m, n, k, splits)
+                assert torch.equal(out[0], out[1]), (m, n, k, splits)
+    finally:
+        native.test_set_sgemm_splits(0)
 
 
 def test_tf32x3_error_does_not_grow_with_k(native):
@@ -294,7 +325,8 @@ def test_stream_order_holds_across_overlapped_launches(native):
 
 
 @pytest.mark.parametrize("variant,shape", [(1, (512, 384, 640)), (2, (320, 448, 200)), (9, (16384, 32, 512)),
-                                           (8, (96, 1024, 1024)), (4, (512, 512, 512))])
+                                           (8, (96, 1024, 1024)), (4, (512, 512, 512)), (10, (640, 640, 640)),
+                                           (12, (768, 768, 768)), (7, (256, 256, 4096))])
 def test_inputs_written_by_the_kernel_before(native, variant, shape):
     """B is rewritten and C poisoned by ordinary kernels right before each product, with no synchronisation:
     a product that started reading or writing before those kernels had finished would see the other B or lose
@@ -326,6 +358,13 @@ def test_automatic_choice_at_its_boundaries(native):
     assert nv.sgemm_auto_variant(8192, 16, 8192) == nv.VT_SGEMM_TALL_TF32X3
     assert nv.sgemm_auto_variant(8192, 8192, 8192) == nv.VT_SGEMM_TF32X3
     assert nv.sgemm_auto_variant(256, 256, 256) == nv.VT_SGEMM_TILE32
+    # mid-sized products go to the pipelined FFMA kernel with its cluster K split, long-K small ones to the 32-wide
+    # kernel with its own split, cubes from ~900 up to the tensor cores
+    assert nv.sgemm_auto_variant(640, 640, 640) in (nv.VT_SGEMM_PIPE128, nv.VT_SGEMM_PIPE64X128, nv.VT_SGEMM_PIPE64)
+    assert nv.sgemm_auto_variant(512, 512, 8192) in (nv.VT_SGEMM_PIPE128, nv.VT_SGEMM_PIPE64X128, nv.VT_SGEMM_PIPE64)
+    assert nv.sgemm_auto_variant(256, 256, 8192) == nv.VT_SGEMM_TILE32
+    assert nv.sgemm_auto_variant(128, 128, 65536) == nv.VT_SGEMM_TILE32
+    assert nv.sgemm_auto_variant(1024, 1024, 1024) == nv.VT_SGEMM_TF32X3
     limit = 4096 * 128
     assert nv.sgemm_auto_variant(16, limit, 1024) == nv.VT_SGEMM_SKINNY_TF32X3
     assert nv.sgemm_auto_variant(16, limit + 128, 1024) not in (nv.VT_SGEMM_SKINNY_TF32X3, nv.VT_SGEMM_PANEL_TF32X3)

@@ -45,9 +45,13 @@ VT_SGEMM_SKINNY_MMA_SYNC = 6
 VT_SGEMM_TILE32 = 7
 VT_SGEMM_PANEL_TF32X3 = 8
 VT_SGEMM_TALL_TF32X3 = 9
+VT_SGEMM_PIPE128 = 10
+VT_SGEMM_PIPE64 = 11
+VT_SGEMM_PIPE64X128 = 12
 
 SGEMM_VARIANT_NAMES = {0: "AUTO", 1: "TILE128", 2: "TILE64", 3: "SKINNY", 4: "TF32X3", 5: "SKINNY_TF32X3",
-                       6: "SKINNY_MMA_SYNC", 7: "TILE32", 8: "PANEL_TF32X3", 9: "TALL_TF32X3"}
+                       6: "SKINNY_MMA_SYNC", 7: "TILE32", 8: "PANEL_TF32X3", 9: "TALL_TF32X3",
+                       10: "PIPE128", 11: "PIPE64", 12: "PIPE64X128"}
 
 # Every symbol include/veritac_b200.h declares, with its ctypes signature.
 SIGNATURES = {
@@ -67,6 +71,7 @@ SIGNATURES = {
     "vt_sgemm_skinny_static_scratch": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,
                                                c_void_p]),
     "vt_test_set_wait_hooks": (c_int, [c_int, c_int64, c_int]),
+    "vt_test_set_sgemm_splits": (c_int, [c_int, c_int]),
     "vt_test_expire_wait": (c_int, [c_int, c_void_p]),
     "vt_sync": (c_int, [c_int, c_void_p]),
     "vt_host_alloc": (c_void_p, [c_size_t]),
@@ -200,6 +205,11 @@ def sgemm_skinny_static_scratch(A, B, C, M: int, N: int, K: int, *, dev: int = 0
 def test_set_wait_hooks(dev: int = 0, wait_limit_cycles: int = 0, i8_stop_fill: int = -1) -> None:
     """Test hook: bound of the device-side waits (0 = default) and the int8 pair kernel's induced stop."""
     check(lib().vt_test_set_wait_hooks(dev, wait_limit_cycles, i8_stop_fill))
+
+
+def test_set_sgemm_splits(splits: int = 0, dev: int = 0) -> None:
+    """Test hook: K split of the FFMA tile kernels (0 = automatic)."""
+    check(lib().vt_test_set_sgemm_splits(dev, splits))
 
 
 def test_expire_wait(dev: int = 0, stream: int = 0) -> None:

@@ -225,8 +225,21 @@ int choose_sgemm_variant(DeviceCtx* c, const float* dA, const float* dB, const f
   // from 4 Mi up to 256 rows, from 16 Mi up to 384 rows).
   if (M > 16 && M <= 3 * SKINNY_UMMA_MAX_ROWS && N >= 128 && K >= 512 &&
       double(N) * double(K) >= (M <= 32 ? 1.0e6 : M <= 2 * SKINNY_UMMA_MAX_ROWS ? 4.0e6 : 1.6e7) &&
-      sgemm_skinny_umma_supported(dA, dB, dC, 1, N, K))
-    return VT_SGEMM_PANEL_TF32X3;
+      sgemm_skinny_umma_supported(dA, dB, dC, 1, N, K)) {
+    // With few columns and a very long K every CTA holds a piece of the same few slabs, and one CTA per slab adds all
+    // the partial tiles (128 x 128 x 65536: 148 of them, 0.15 ms, against 0.08 ms for the 32-wide FFMA kernel with
+    // its own K split): the panel kernel's time is modelled as the stream of B (a panel of 16 rows at the rate of
+    // the stream, one of 128 rows at half of it) plus that adding at 60 GB/s, and compared with the FFMA choice.
+    const int64_t rows = M < SKINNY_UMMA_MAX_ROWS ? M : SKINNY_UMMA_MAX_ROWS;
+    const int64_t panels = (M + SKINNY_UMMA_MAX_ROWS - 1) / SKINNY_UMMA_MAX_ROWS;
+    int ctas, slabs, max_parts;
+    sgemm_skinny_umma_plan(rows, N, K, c->sm_count, &ctas, &slabs, &max_parts);
+    const double stream = double(K) * double(N) * 4.0 / 5.0e12 * (1.0 + (rows > 16 ? double(rows - 16) / 112.0 : 0.0));
+    const double adding = max_parts > 1 ? double(max_parts) * double(rows) * 512.0 / 6.0e10 : 0.0;
+    int tile_variant;
+    if (double(panels) * (6.0e-6 + stream + adding) < sgemm_tile_choice(c, dA, dB, dC, M, N, K, &tile_variant))
+      return VT_SGEMM_PANEL_TF32X3;
+  }
   // Few columns against a large A: the mirror image (measured ahead of the tile kernels and the 3xTF32 pair kernel
   // from 4 Mi elements of A up to 32 columns, from 12 Mi up to 64, from 16 Mi up to 128).
   if (N <= SKINNY_UMMA_MAX_ROWS && K >= 256 &&
@@ -240,17 +253,18 @@ int choose_sgemm_variant(DeviceCtx* c, const float* dA, const float* dB, const f
   // Large products go to the tensor cores (3xTF32, measured ~1e-6 relative Frobenius error at any K) when that
   // is clearly faster than the best FFMA tile kernel.  Its time is modelled as two launches (6 us), the pass that
   // writes the lo parts and the write of C (8 bytes per element of A and B, 4 per element of C, at ~5.5 TB/s) and
-  // K x 34 ns for every wave of 256x256 tiles over the 74 CTA pairs (8192^3: 4.1 ms).  Below ~0.5 GFLOP the two
+  // K x 29 ns for every wave of 256x256 tiles over the 74 CTA pairs (measured on cubes of 896 to 1536, which is where
+  // the comparison is close; at 8192^3, under the power cap, a wave takes K x 34 ns).  Below ~0.5 GFLOP the two
   // passes cost more than they save.
   if (M >= 128 && N >= 16 && K >= 64 && double(M) * double(N) * double(K) >= 5.0e8 &&
       sgemm_tf32x3_supported(dA, dB, dC, M, N, K)) {
     int tile_variant;
-    const double t_tile = sgemm_tile_choice(dA, dB, dC, M, N, K, c->sm_count, &tile_variant);
+    const double t_tile = sgemm_tile_choice(c, dA, dB, dC, M, N, K, &tile_variant);
     const double pair_tiles = double((M + 255) / 256) * double((N + 255) / 256);
     const double pairs = c->sm_count / 2;
     const double waves = pair_tiles <= pairs ? 1.0 : double(int64_t((pair_tiles + pairs - 1) / pairs));
     const double t_tc = 6.0e-6 + ((double(M) * K + double(K) * N) * 8.0 + double(M) * N * 4.0) / 5.5e12 +
-                        waves * double(K) * 3.4e-8;
+                        waves * double(K) * 2.9e-8;
     if (t_tc < 0.9 * t_tile) return VT_SGEMM_TF32X3;
   }
   return VT_SGEMM_AUTO;
@@ -454,7 +468,7 @@ int vt_sgemm(int dev, const float* A, const float* B, float* C, int64_t M, int64
   if (where != VT_HOST && where != VT_DEVICE) return fail(VT_ERR_INVALID, "where must be VT_HOST or VT_DEVICE");
   if (M < 1 || N < 1 || K < 1) return fail(VT_ERR_INVALID, "dimensions must be positive");
   if (M > 0x7fffffffLL || N > 0x7fffffffLL || K > 0x7fffffffLL) return fail(VT_ERR_INVALID, "dimension overflows int");
-  if (variant < VT_SGEMM_AUTO || variant > VT_SGEMM_TALL_TF32X3) return fail(VT_ERR_INVALID, "unknown sgemm variant %d", variant);
+  if (variant < VT_SGEMM_AUTO || variant > VT_SGEMM_PIPE64X128) return fail(VT_ERR_INVALID, "unknown sgemm variant %d", variant);
   DeviceCtx* c = ctx_for(dev);
   if (!c) return VT_ERR_CUDA;
   cudaStream_t s = where == VT_HOST ? c->stream : pick_stream(c, stream);
@@ -574,7 +588,7 @@ int vt_sgemm_auto_variant(int dev, int64_t M, int64_t N, int64_t K) {
   if (!c) return VT_ERR_CUDA;
   const float* aligned = reinterpret_cast<const float*>(uintptr_t(256));   // never dereferenced
   int variant = choose_sgemm_variant(c, aligned, aligned, aligned, M, N, K);
-  if (variant == VT_SGEMM_AUTO) sgemm_tile_choice(aligned, aligned, aligned, M, N, K, c->sm_count, &variant);
+  if (variant == VT_SGEMM_AUTO) sgemm_tile_choice(c, aligned, aligned, aligned, M, N, K, &variant);
   return variant;
 }
 
@@ -584,6 +598,14 @@ int vt_test_set_wait_hooks(int dev, int64_t wait_limit_cycles, int i8_stop_fill)
   if (!c) return VT_ERR_CUDA;
   c->wait_limit_cycles = wait_limit_cycles > 0 ? (long long)wait_limit_cycles : 4000000000LL;
   c->i8_stop_fill = i8_stop_fill < 0 ? -1 : i8_stop_fill;
+  return VT_OK;
+}
+
+int vt_test_set_sgemm_splits(int dev, int splits) {
+  clear_error_text();
+  DeviceCtx* c = ctx_for(dev);
+  if (!c) return VT_ERR_CUDA;
+  c->sgemm_force_splits = splits;
   return VT_OK;
 }
 

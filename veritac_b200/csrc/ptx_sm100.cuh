@@ -120,6 +120,15 @@ __device__ __forceinline__ void mbar_complete_tx(uint64_t* bar, uint32_t bytes) 
   asm volatile("mbarrier.complete_tx.relaxed.cta.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
                : "memory");
 }
+// 16-byte load from the shared memory of a CTA of this cluster (address from mapa_shared).
+__device__ __forceinline__ float4 ld_shared_cluster_v4f(uint32_t cluster_addr) {
+  float4 v;
+  asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+               : "r"(cluster_addr)
+               : "memory");
+  return v;
+}
 // 32-bit store into the shared memory of a CTA of this cluster (address from mapa_shared).
 __device__ __forceinline__ void st_shared_cluster_u32(uint32_t cluster_addr, uint32_t v) {
   asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");

@@ -36,6 +36,10 @@ struct DeviceCtx {
   // CTA of every int8 pair stops (-1: never).
   long long wait_limit_cycles = 4000000000LL;
   int i8_stop_fill = -1;
+  // pipelined FFMA kernel: clusters of 1..8 CTAs of each tile shape the device holds at once (filled on first use)
+  int ffma_capacity[3][9] = {};
+  bool ffma_capacity_known = false;
+  int sgemm_force_splits = 0;          // test hook (vt_test_set_sgemm_splits): K split of the FFMA tile kernels, 0 = automatic
   // grow-only device workspace for host-pointer calls and operand re-layouts
   void* ws[4] = {nullptr, nullptr, nullptr, nullptr};
   size_t ws_bytes[4] = {0, 0, 0, 0};
@@ -97,6 +101,27 @@ cudaError_t launch_overlapped(void (*kernel)(KArgs...), unsigned grid, unsigned 
   return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 
+// The same for a kernel that runs in thread-block clusters of `cluster` consecutive CTAs (grid a multiple of it).
+template <class... KArgs, class... Args>
+cudaError_t launch_overlapped_cluster(void (*kernel)(KArgs...), unsigned grid, unsigned block, size_t smem,
+                                      unsigned cluster, cudaStream_t s, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(block);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  attr[1].id = cudaLaunchAttributeClusterDimension;
+  attr[1].val.clusterDim.x = cluster;
+  attr[1].val.clusterDim.y = 1;
+  attr[1].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 2;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 // ---- kernel launchers (device pointers only) ------------------------------------------------
 // raster_mode: 0 row-major tiles, 1 column-major tiles, 2 grouped (group = tile-rows per sweep).
 // variant: VT_I8_B_AS_STORED (one CTA per 128 x 256 tile), VT_I8_CTA_PAIR (two CTAs per 256 x 256 tile),
@@ -112,7 +137,12 @@ int launch_i8gemm_wide(DeviceCtx* c, const int8_t* A, const int8_t* B, int32_t* 
 int launch_expire_wait(DeviceCtx* c, cudaStream_t s);
 int launch_sgemm(DeviceCtx* c, const float* A, const float* B, float* C, int64_t M, int64_t N, int64_t K,
                  int variant, cudaStream_t s);
-double sgemm_tile_choice(const float* A, const float* B, const float* C, int64_t M, int64_t N, int64_t K, int sm_count,
+// Pipelined FFMA kernel (sgemm_ffma_sm100.cu); shape 0: 128 x 128 tiles, 1: 64 x 128, 2: 64 x 64.
+bool sgemm_ffma_supported(const float* A, const float* B, const float* C, int64_t N, int64_t K);
+double sgemm_ffma_plan(DeviceCtx* c, int shape, int64_t M, int64_t N, int64_t K, int forced, int* splits_out);
+int launch_sgemm_ffma(DeviceCtx* c, const float* A, const float* B, float* C, int64_t M, int64_t N, int64_t K, int shape,
+                      cudaStream_t s);
+double sgemm_tile_choice(DeviceCtx* c, const float* A, const float* B, const float* C, int64_t M, int64_t N, int64_t K,
                          int* variant);
 int launch_sgemm_skinny(DeviceCtx* c, const float* A, const float* B, float* C, float* partials, int64_t M,
                         int64_t N, int64_t K, int ksplit, cudaStream_t s);

@@ -42,6 +42,39 @@ __device__ __forceinline__ void cp_async_wait() {
   asm volatile("cp.async.wait_group %0;" ::"n"(kPending) : "memory");
 }
 
+// K split over CTAs ("splits" CTAs per output tile, each with its own range of K): every CTA leaves its partial
+// tile in scratch memory (float4 slot `j` of thread `tid` at [(tile * splits + split) * kSlots + j] * kThreads + tid)
+// and takes a ticket for the tile; the CTA that draws the last ticket adds the partial tiles in split order, its
+// own included, so the sum does not depend on which CTA that is.  Nobody waits for anybody.
+// Called by the kThreads threads (named barrier kBar) that have stored a partial tile; true in the last CTA.
+template <int kThreads, int kBar>
+__device__ __forceinline__ bool splitk_arrive(int tile, int splits, int* __restrict__ tickets, int* last_flag, int tid) {
+  __threadfence();
+  asm volatile("bar.sync %0, %1;" ::"n"(kBar), "n"(kThreads) : "memory");
+  if (tid == 0) {
+    const int arrived = atomicAdd(&tickets[tile], 1);
+    const int last = arrived == splits - 1;
+    if (last) tickets[tile] = 0;      // every CTA of the tile has arrived: the counter is free for the next launch
+    *last_flag = last;
+  }
+  asm volatile("bar.sync %0, %1;" ::"n"(kBar), "n"(kThreads) : "memory");
+  if (!*last_flag) return false;
+  __threadfence();
+  return true;
+}
+__device__ __forceinline__ float4 splitk_sum(const float4* __restrict__ first, size_t split_stride, int splits) {
+  float4 sum = __ldcg(first);
+#pragma unroll 4
+  for (int s = 1; s < splits; ++s) {
+    const float4 v = __ldcg(first + size_t(s) * split_stride);
+    sum.x += v.x;
+    sum.y += v.y;
+    sum.z += v.z;
+    sum.w += v.w;
+  }
+  return sum;
+}
+
 
 template <int RM, int RN, bool kGuard>
 __global__ void __launch_bounds__(SG_THREADS, (RM * RN >= 4) ? 2 : 3)
@@ -382,12 +415,16 @@ constexpr size_t SS_SMEM_BYTES = size_t(SS_TILE * SS_APITCH + SS_KC * SS_TILE) *
 
 __global__ void __launch_bounds__(SS_THREADS, 2)
 sgemm_small_kernel(const float* __restrict__ A, const float* __restrict__ B, float* __restrict__ C, int M, int N,
-                   int K, int tiles_n) {
+                   int K, int tiles_n, int n_tiles, int splits, int k_per_split, float* __restrict__ partials,
+                   int* __restrict__ tickets) {
   extern __shared__ __align__(16) float ss_smem[];
   float* As = ss_smem;                            // [32][SS_APITCH]
   float* Bs = ss_smem + SS_TILE * SS_APITCH;      // [256][32]
   const int tid = threadIdx.x;
-  const int m0 = (blockIdx.x / tiles_n) * SS_TILE, n0 = (blockIdx.x % tiles_n) * SS_TILE;
+  const int split = blockIdx.x / n_tiles, tile = blockIdx.x - split * n_tiles;   // K split: as in sgemm_tile_kernel
+  const int m0 = (tile / tiles_n) * SS_TILE, n0 = (tile % tiles_n) * SS_TILE;
+  const int k_begin = split * k_per_split;
+  const int k_end = min(K, k_begin + k_per_split);
   const int kg = tid >> 6;                        // which quarter of a burst's K values
   const int t = tid & 63, tx = t & 7, ty = t >> 3;
 
@@ -403,21 +440,21 @@ sgemm_small_kernel(const float* __restrict__ A, const float* __restrict__ B, flo
   grid_dependency_wait();
   grid_launch_dependents();
 
-  for (int k0 = 0; k0 < K; k0 += SS_KC) {
-    if (k0 > 0) __syncthreads();                  // everyone is done with the previous burst
+  for (int k0 = k_begin; k0 < k_end; k0 += SS_KC) {
+    if (k0 > k_begin) __syncthreads();            // everyone is done with the previous burst
     // A: 32 rows x 64 float4; B: 256 rows x 8 float4.  2048 copies each, 8 + 8 per thread.
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
       const int idx = tid + SS_THREADS * i;
       const int row = idx >> 6, c4 = (idx & 63) * 4;
-      const bool ok = (m0 + row < M) && (k0 + c4 < K);
+      const bool ok = (m0 + row < M) && (k0 + c4 < k_end);
       cp_async_16_zfill(As + row * SS_APITCH + c4, ok ? A + size_t(m0 + row) * K + k0 + c4 : A, ok);
     }
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
       const int idx = tid + SS_THREADS * i;
       const int row = idx >> 3, c4 = (idx & 7) * 4;
-      const bool ok = (k0 + row < K) && (n0 + c4 < N);
+      const bool ok = (k0 + row < k_end) && (n0 + c4 < N);
       cp_async_16_zfill(Bs + row * SS_TILE + c4, ok ? B + size_t(k0 + row) * N + n0 + c4 : B, ok);
     }
     cp_async_commit();
@@ -476,12 +513,29 @@ sgemm_small_kernel(const float* __restrict__ A, const float* __restrict__ B, flo
         acc[i][3] += v.w;
       }
     const int col = n0 + tx * 4;
+    if (splits == 1) {
+      if (col < N) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int row = m0 + ty * 4 + i;
+          if (row < M)
+            *reinterpret_cast<float4*>(C + size_t(row) * N + col) = make_float4(acc[i][0], acc[i][1], acc[i][2], acc[i][3]);
+        }
+      }
+      return;
+    }
+    constexpr size_t kSplitStride = 4 * 64;          // float4s per partial tile
+    float4* first = reinterpret_cast<float4*>(partials) + size_t(tile) * splits * kSplitStride + t;
+    float4* mine = first + size_t(split) * kSplitStride;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) __stcg(mine + i * 64, make_float4(acc[i][0], acc[i][1], acc[i][2], acc[i][3]));
+    int* last_flag = reinterpret_cast<int*>(ss_smem + 3 * 64 * 16);   // behind the fold area above
+    if (!splitk_arrive<64, 1>(tile, splits, tickets, last_flag, t)) return;
     if (col < N) {
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         const int row = m0 + ty * 4 + i;
-        if (row < M)
-          *reinterpret_cast<float4*>(C + size_t(row) * N + col) = make_float4(acc[i][0], acc[i][1], acc[i][2], acc[i][3]);
+        if (row < M) *reinterpret_cast<float4*>(C + size_t(row) * N + col) = splitk_sum(first + i * 64, kSplitStride, splits);
       }
     }
   }
@@ -492,15 +546,44 @@ bool sgemm_small_ok(const float* A, const float* B, const float* C, int64_t N, i
          ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(C)) & 15) == 0;
 }
 
-int launch_small(const float* A, const float* B, float* C, int M, int N, int K, cudaStream_t s) {
+// How many CTAs share the K range of one output tile.  A grid that fills at most half the CTA slots of the GPU
+// (`slots`) leaves SMs idle, or one CTA alone on an SM with nothing to overlap its loads; splitting K fills one
+// wave instead.  Every split gets at least `min_k` values of K and a tile at most `most` partial tiles.
+// `forced` (vt_test_set_sgemm_splits) overrides the count.
+constexpr int kMaxSplits = 16;
+int splits_for(long long tiles, int K, int slots, int min_k, int most, int forced) {
+  long long s = 1;
+  if (forced != 0) s = forced < 0 ? -forced : forced;
+  else if (tiles * 2 <= slots) s = slots / tiles;
+  if (s > most) s = most;
+  if (s > K / min_k) s = K / min_k;
+  if (tiles > kTicketCount) s = 1;     // one arrival counter per tile
+  return s < 1 ? 1 : int(s);
+}
+// K values per split (a multiple of `step`) and the number of splits that then have any.
+void split_ranges(int K, int step, int* splits, int* k_per_split) {
+  const int steps = (K + step - 1) / step;
+  const int per = (steps + *splits - 1) / *splits;
+  *k_per_split = per * step;
+  *splits = (steps + per - 1) / per;
+}
+
+int launch_small(DeviceCtx* c, const float* A, const float* B, float* C, int M, int N, int K, cudaStream_t s) {
   if (!sgemm_small_ok(A, B, C, N, K))
     return fail(VT_ERR_UNSUPPORTED, "the 32x32-tile kernel needs N %% 4 == 0, K %% 4 == 0 and 16-byte aligned operands");
   const int tiles_m = (M + SS_TILE - 1) / SS_TILE, tiles_n = (N + SS_TILE - 1) / SS_TILE;
   const long long tiles = 1LL * tiles_m * tiles_n;
   if (tiles > 0x7fffffffLL) return fail(VT_ERR_INVALID, "sgemm tile count overflows int");
+  int splits = splits_for(tiles, K, 2 * c->sm_count, 2 * SS_KC, kMaxSplits, c->sgemm_force_splits), k_per_split;
+  split_ranges(K, SS_KC, &splits, &k_per_split);
+  float* partials = nullptr;
+  if (splits > 1) {
+    partials = static_cast<float*>(ctx_workspace(c, 3, size_t(tiles) * splits * SS_TILE * SS_TILE * sizeof(float)));
+    if (!partials) return VT_ERR_CUDA;
+  }
   VT_CUDA(cudaFuncSetAttribute(sgemm_small_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(SS_SMEM_BYTES)));
-  VT_CUDA(launch_overlapped(sgemm_small_kernel, unsigned(tiles), unsigned(SS_THREADS), size_t(SS_SMEM_BYTES), s, A, B, C,
-                            M, N, K, tiles_n));
+  VT_CUDA(launch_overlapped(sgemm_small_kernel, unsigned(tiles * splits), unsigned(SS_THREADS), size_t(SS_SMEM_BYTES), s, A,
+                            B, C, M, N, K, tiles_n, int(tiles), splits, k_per_split, partials, c->tickets));
   count_launch();
   VT_CUDA(cudaGetLastError());
   return VT_OK;
@@ -583,14 +666,18 @@ int launch_sgemm_skinny(DeviceCtx* c, const float* A, const float* B, float* C, 
   return VT_OK;
 }
 
-// Which FFMA tile kernel to run, and about how long it will take (seconds): the work of the padded tile
-// grid over the rate that tile shape reaches (measured: 53, 32 and 32 TFLOPS for 128-, 64- and 32-wide
-// tiles with every SM busy), scaled down while the grid has fewer tiles than SMs; the smallest tile has
-// to win by 10 %.  Measured points the rule reproduces: 256^3 6.6 (32-wide) against 12.3 us (64-wide),
-// 512^3 13.3 against 20.5 us, 768^3 32.7 against 28.8 us, 8192 x 16 x 8192 151 against 399 us,
-// 65536 x 16 x 1024 140 against 281 us, 8192 x 256 x 8192 0.91 ms (128-wide) against 1.07 ms.
-double sgemm_tile_choice(const float* A, const float* B, const float* C, int64_t M, int64_t N, int64_t K, int sm_count,
+// Which FFMA kernel to run, and about how long it will take (seconds).  First design (sgemm_tile_kernel,
+// sgemm_small_kernel): the work of the padded tile grid over the rate that tile shape reaches (measured: 58, 32 and
+// 32 TFLOPS for 128-, 64- and 32-wide tiles with every SM busy), scaled down while the grid has fewer CTAs than
+// SMs; the smallest tile has to win by 10 %; the 32-wide kernel splits K over several CTAs per tile when its grid is
+// small (launch_small), which adds about 4 us.  Measured points the rule reproduces: 256^3 6.6 (32-wide) against
+// 12.3 us (64-wide), 512^3 13.3 against 20.5 us, 8192 x 16 x 8192 151 against 399 us, 65536 x 16 x 1024 140 against
+// 281 us, 8192 x 256 x 8192 0.91 ms (128-wide) against 1.07 ms, 256 x 256 x 8192 42 us (32-wide, split four ways).
+// Second design (sgemm_ffma_kernel): sgemm_ffma_plan's model, which includes its cluster K split; it takes the
+// mid-sized products (640^3: 18 us against 24).
+double sgemm_tile_choice(DeviceCtx* c, const float* A, const float* B, const float* C, int64_t M, int64_t N, int64_t K,
                          int* variant) {
+  const int sm_count = c->sm_count;
   const bool small_ok = sgemm_small_ok(A, B, C, N, K);
   static const double kRate[3] = {58e12, 32e12, 32e12};
   static const double kBias[3] = {1.0, 1.0, 1.1};
@@ -602,11 +689,28 @@ double sgemm_tile_choice(const float* A, const float* B, const float* C, int64_t
     if (i == 2 && !small_ok) continue;
     const double tm = double((M + kTile[i] - 1) / kTile[i]), tn = double((N + kTile[i] - 1) / kTile[i]);
     const double work = 2.0 * tm * tn * kTile[i] * kTile[i] * double(K);
-    const double busy = tm * tn < sm_count ? tm * tn / sm_count : 1.0;
-    const double t = work / (kRate[i] * busy) * kBias[i];
+    int splits = 1, per;
+    if (i == 2 && tm * tn < 1e9) {
+      splits = splits_for((long long)(tm * tn), int(K), 2 * sm_count, 2 * SS_KC, kMaxSplits, 0);
+      split_ranges(int(K), SS_KC, &splits, &per);
+    }
+    const double ctas = tm * tn * splits;
+    const double busy = ctas < sm_count ? ctas / sm_count : 1.0;
+    const double t = 5.0e-6 + work / (kRate[i] * busy) * kBias[i] + (splits > 1 ? 4.0e-6 : 0.0);   // 5 us: what a launch costs beside its loop
     if (best == 0 || t < best) {
       best = t;
       *variant = kVariant[i];
+    }
+  }
+  if (sgemm_ffma_supported(A, B, C, N, K)) {
+    static const int kPipe[3] = {VT_SGEMM_PIPE128, VT_SGEMM_PIPE64X128, VT_SGEMM_PIPE64};
+    for (int shape = 0; shape < 3; ++shape) {
+      int splits;
+      const double t = 1.1 * sgemm_ffma_plan(c, shape, M, N, K, 0, &splits);   // has to win by 10 %
+      if (t < best) {
+        best = t;
+        *variant = kPipe[shape];
+      }
     }
   }
   return best;
@@ -615,8 +719,10 @@ double sgemm_tile_choice(const float* A, const float* B, const float* C, int64_t
 int launch_sgemm(DeviceCtx* c, const float* A, const float* B, float* C, int64_t M, int64_t N, int64_t K,
                  int variant, cudaStream_t s) {
   if (M > 0x7fffffffLL || N > 0x7fffffffLL || K > 0x7fffffffLL) return fail(VT_ERR_INVALID, "dimension overflows int");
-  if (variant == 0) sgemm_tile_choice(A, B, C, M, N, K, c->sm_count, &variant);
-  if (variant == VT_SGEMM_TILE32) return launch_small(A, B, C, int(M), int(N), int(K), s);
+  if (variant == 0) sgemm_tile_choice(c, A, B, C, M, N, K, &variant);
+  if (variant == VT_SGEMM_PIPE128 || variant == VT_SGEMM_PIPE64X128 || variant == VT_SGEMM_PIPE64)
+    return launch_sgemm_ffma(c, A, B, C, M, N, K, variant == VT_SGEMM_PIPE128 ? 0 : variant == VT_SGEMM_PIPE64X128 ? 1 : 2, s);
+  if (variant == VT_SGEMM_TILE32) return launch_small(c, A, B, C, int(M), int(N), int(K), s);
   if (variant == 1) return launch_tile<2, 2>(A, B, C, int(M), int(N), int(K), s);
   if (variant == 2) return launch_tile<1, 1>(A, B, C, int(M), int(N), int(K), s);
   return fail(VT_ERR_UNSUPPORTED, "sgemm variant %d is not built", variant);

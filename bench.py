@@ -19,8 +19,9 @@ no data-path collective.  `--scaling weak` gives every rank the whole shape inst
              run and from the host-buffer run, against the exact product; ok = all ranks passed
   roofline   achieved = algorithmic ops (or bytes) per launch / average launch duration of the
              timed region; peak from MEASURED_PEAKS.json (fallback stated if absent)
-  also       the other named workloads, each timed like the headline (fp32 8192^3 by the automatic
-             choice and by the FFMA kernel, fp32 16 x 8192 x 8192, the batched B-reuse int8 workload)
+  also       the other named workloads, each timed like the headline (fp32 256^3 and 640^3, fp32 8192^3 by
+             the automatic choice and by the FFMA kernel, fp32 16 x 8192 x 8192, the batched B-reuse int8
+             workload), short launches first, a quarter of a second apart
   cpu_baseline  the oracle's OpenMP C restatement of the reference's CPU arithmetic, timed on this
              host's cores on a bounded sample of the same workload (N = 1 only)
 
@@ -62,6 +63,7 @@ WORKLOADS = {
     "i8_batched_32": ("i8b", 1024, 4096, 4096, 32),      # one GPU's share of the batched workload on 8 GPUs
     "sgemm_8192": ("f32", 8192, 8192, 8192, 1),
     "sgemm_256": ("f32", 256, 256, 256, 1),
+    "sgemm_640": ("f32", 640, 640, 640, 1),               # a mid-sized product: FFMA with K split over a cluster
     "sgemm_skinny": ("f32", 16, 8192, 8192, 1),
     "sgemm_panel_64": ("f32", 64, 8192, 8192, 1),         # few rows against a large B: the row-panel kernel
     "sgemm_panel_128": ("f32", 128, 8192, 8192, 1),
@@ -433,7 +435,8 @@ class Job:
         self.i8_variant, self.sgemm_variant = i8_variant, sgemm_variant
         rank, world = ctx["rank"], ctx["world"]
         total = self.M * self.batch
-        self.replicas = world > 1 and total < 64 * world        # too few rows to split: every rank runs the whole shape
+        # too few rows to split (or a shape that is about one GPU's grid of tiles): every rank runs the whole shape
+        self.replicas = world > 1 and (total < 64 * world or workload == "sgemm_640")
         if scaling == "weak" or world == 1 or self.replicas:
             self.rows = total
         else:
@@ -704,14 +707,19 @@ def run_gpu_arm(args, kind, M, N, K, batch, metric, unit):
     also = None
     if not args.no_also:
         also = {}
-        for name, wl, variant in (("sgemm_8192", "sgemm_8192", nv.VT_SGEMM_AUTO),
-                                  ("sgemm_8192_ffma", "sgemm_8192", nv.VT_SGEMM_TILE128),
+        # The short launches first, and a pause before each: right after a second at the power cap the GPU runs a
+        # 20 us kernel half as fast again (640^3: 28 us in that position, 18.5 us on its own), which says nothing
+        # about the kernel.
+        for name, wl, variant in (("sgemm_256", "sgemm_256", nv.VT_SGEMM_AUTO),
+                                  ("sgemm_640", "sgemm_640", nv.VT_SGEMM_AUTO),
+                                  ("i8_64", "i8_64", 0),
                                   ("sgemm_skinny", "sgemm_skinny", nv.VT_SGEMM_AUTO),
-                                  ("i8_batched", "i8_batched", 0),
-                                  ("sgemm_256", "sgemm_256", nv.VT_SGEMM_AUTO),
-                                  ("i8_64", "i8_64", 0)):
+                                  ("sgemm_8192", "sgemm_8192", nv.VT_SGEMM_AUTO),
+                                  ("sgemm_8192_ffma", "sgemm_8192", nv.VT_SGEMM_TILE128),
+                                  ("i8_batched", "i8_batched", 0)):
             if wl == args.workload and variant == args.sgemm_variant:
                 continue
+            time.sleep(0.25)
             j = Job(ctx, wl, "strong", 0, variant)
             a_ms, a_launches = j.timed(steps, warm)
             ok = bool(ctx["min"](1.0 if j.check(j.C)["ok"] else 0.0) > 0.5)
@@ -722,6 +730,9 @@ def run_gpu_arm(args, kind, M, N, K, batch, metric, unit):
                           "sharding": "replicas (too few rows to shard); value is one replica's" if j.replicas else
                                       ("batch dealt over the ranks" if j.kind == "i8b" else "M rows per rank") if world > 1 else "single GPU",
                           "roofline": {k: roof[k] for k in ("bound", "achieved", "peak", "unit", "frac")}}
+            if j.kind == "f32":
+                chosen = variant or nv.sgemm_auto_variant(j.rows, j.N, j.K)
+                also[name]["kernel"] = nv.SGEMM_VARIANT_NAMES.get(chosen, str(chosen))
             j.release()
 
     # ---- the same step back to back for about a second: NVML's clock and power readings lag a region of a

@@ -731,7 +731,7 @@ def run_gpu_arm(args, kind, M, N, K, batch, metric, unit):
                                       ("batch dealt over the ranks" if j.kind == "i8b" else "M rows per rank") if world > 1 else "single GPU",
                           "roofline": {k: roof[k] for k in ("bound", "achieved", "peak", "unit", "frac")}}
             if j.kind == "f32":
-                chosen = variant or nv.sgemm_auto_variant(j.rows, j.N, j.K)
+                chosen = variant or nv.sgemm_auto_variant(j.rows, j.N, j.K, dev=ctx["dev"])
                 also[name]["kernel"] = nv.SGEMM_VARIANT_NAMES.get(chosen, str(chosen))
             j.release()
 

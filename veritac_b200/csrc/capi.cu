@@ -584,6 +584,12 @@ int vt_sgemm_auto_variant(int dev, int64_t M, int64_t N, int64_t K) {
   clear_error_text();
   if (M < 1 || N < 1 || K < 1) return fail(VT_ERR_INVALID, "dimensions must be positive");
   if (M > 0x7fffffffLL || N > 0x7fffffffLL || K > 0x7fffffffLL) return fail(VT_ERR_INVALID, "dimension overflows int");
+  // A question, not a launch: the caller's current device is put back.
+  struct Restore {
+    int prev = -1;
+    Restore() { if (cudaGetDevice(&prev) != cudaSuccess) prev = -1; }
+    ~Restore() { if (prev >= 0) cudaSetDevice(prev); }
+  } restore;
   DeviceCtx* c = ctx_for(dev);
   if (!c) return VT_ERR_CUDA;
   const float* aligned = reinterpret_cast<const float*>(uintptr_t(256));   // never dereferenced

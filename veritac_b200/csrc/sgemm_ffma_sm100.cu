@@ -241,8 +241,7 @@ int launch_ffma(DeviceCtx* c, const float* A, const float* B, float* C, int M, i
   }
   if (tiles * splits > 0x7fffffffLL) return fail(VT_ERR_INVALID, "sgemm tile count overflows int");
   auto kernel = sgemm_ffma_kernel<kWarpsM, kWarpsN, kStages>;
-  VT_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(S::kSmemBytes)));
-  (void)c;
+  (void)c;      // the kernel's shared-memory opt-in was set on this device when its cluster capacities were queried
   if (splits > 1)
     VT_CUDA(launch_overlapped_cluster(kernel, unsigned(tiles * splits), unsigned(S::kThreads), size_t(S::kSmemBytes),
                                       unsigned(splits), s, A, B, C, M, N, K, tiles_m, tiles_n, group, splits, k_per_split));

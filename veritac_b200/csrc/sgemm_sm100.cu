@@ -581,7 +581,11 @@ int launch_small(DeviceCtx* c, const float* A, const float* B, float* C, int M, 
     partials = static_cast<float*>(ctx_workspace(c, 3, size_t(tiles) * splits * SS_TILE * SS_TILE * sizeof(float)));
     if (!partials) return VT_ERR_CUDA;
   }
-  VT_CUDA(cudaFuncSetAttribute(sgemm_small_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(SS_SMEM_BYTES)));
+  constexpr uint32_t kAttrBit = 1u << 3;       // once per device: this launch is a few microseconds long
+  if (!(c->func_attr_mask & kAttrBit)) {
+    VT_CUDA(cudaFuncSetAttribute(sgemm_small_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(SS_SMEM_BYTES)));
+    c->func_attr_mask |= kAttrBit;
+  }
   VT_CUDA(launch_overlapped(sgemm_small_kernel, unsigned(tiles * splits), unsigned(SS_THREADS), size_t(SS_SMEM_BYTES), s, A,
                             B, C, M, N, K, tiles_n, int(tiles), splits, k_per_split, partials, c->tickets));
   count_launch();

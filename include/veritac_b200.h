@@ -11,7 +11,11 @@
  *   - Every function returns VT_OK (0) or a negative VT_ERR_* code and never aborts the process;
  *     the text for the calling thread's last failure is vt_last_error().
  *   - `dev` is a CUDA device ordinal.  The library keeps one context per device (a stream, a status
- *     word, grow-only workspace) created on first use and freed by vt_shutdown().
+ *     word, grow-only workspace) created on first use and freed by vt_shutdown().  A call that takes
+ *     `dev` makes it the calling thread's current CUDA device and leaves it so, as cudaSetDevice(dev)
+ *     would (a caller that allocates on "the current device" afterwards allocates there); the two
+ *     calls that only answer a question or use a fixed array, vt_sgemm_auto_variant and
+ *     vt_sgemm_skinny_static_scratch, put the previous device back.
  *   - `where`: VT_HOST  = A, B, C are host pointers; the call copies in, computes, copies out and
  *                         returns when C is complete (pinned memory from vt_host_alloc makes the
  *                         copies run at full PCIe rate).

@@ -31,8 +31,7 @@
  *   - One host thread per device at a time; different devices may be driven concurrently.
  *   - All calls on one device must be ordered with one another on the GPU (the same stream, or streams joined
  *     by events): they share the device's status word, arrival counters and scratch memory (K-split partial
- *     tiles, lo parts, the int8 kernel's partial accumulators), so two calls whose kernels could overlap
- *     race on them.
+ *     tiles, lo parts), so two calls whose kernels could overlap race on them.
  *   - A VT_DEVICE call that needs more scratch memory than any call before it on that device grows the
  *     workspace, which synchronises the device and allocates; issue the largest shape once before
  *     latency-critical work or stream capture.
@@ -73,16 +72,6 @@ enum {
  * exist so that a design choice can be measured against its alternative:
  *   B_AS_STORED            one CTA per 128x256 tile
  *   CTA_PAIR               two CTAs per 256x256 tile (tcgen05 cta_group::2), every tile computed by one pair
- *   CTA_PAIR_SHARED_TAIL   the same kernel; when the tiles do not fill a whole number of waves of CTA pairs,
- *                          the K blocks of the last wave are shared by all pairs and the partial int32 sums
- *                          are added by the pair that owns the tile (exact).  Measured level with CTA_PAIR
- *                          (the pairs then no longer walk K in step and the L2 serves them more slowly),
- *                          so VT_I8_AUTO does not choose it.
- *   CTA_PAIR_SPLIT_TAIL    the same kernel; when the last wave has at most half as many tiles as there are CTA
- *                          pairs, every tile of it is cut into 2 to 4 equal K pieces that as many pairs compute
- *                          last and side by side; the pair with the last piece adds the others' sums (exact).
- *                          Measured level with CTA_PAIR as well (a pair's K block takes less time while other
- *                          pairs idle, so a half-empty last wave costs little); VT_I8_AUTO does not choose it.
  *   CTA_PAIR_WIDE          two CTAs per 256x512 tile: both halves share the pair's rows of A, which cuts the
  *                          operand traffic per product by a quarter; tensor memory is then full, so a tile's
  *                          epilogue does not overlap the next tile's MMAs.  For products of few tiles per pair
@@ -91,10 +80,8 @@ enum {
 enum {
   VT_I8_AUTO = 0,
   VT_I8_B_AS_STORED = 1,
-  VT_I8_CTA_PAIR_SHARED_TAIL = 2,
-  VT_I8_CTA_PAIR = 3,
-  VT_I8_CTA_PAIR_WIDE = 4,
-  VT_I8_CTA_PAIR_SPLIT_TAIL = 5
+  VT_I8_CTA_PAIR = 3,      /* 2 and 5 were forms that shared the last round of tiles along K: measured level, retired */
+  VT_I8_CTA_PAIR_WIDE = 4
 };
 
 /* fp32 kernel variants.

@@ -30,7 +30,7 @@ def test_status_codes_match_header(native):
         m = re.search(r"\b%s\s*=\s*(-?\d+)" % name, text)
         assert m and int(m.group(1)) == getattr(native, name)
     for group in ("VT_RASTER_BASELINE|VT_RASTER_REUSE_B|VT_RASTER_BATCHED|VT_RASTER_AUTO",
-                  "VT_I8_AUTO|VT_I8_B_AS_STORED|VT_I8_CTA_PAIR_SHARED_TAIL|VT_I8_CTA_PAIR|VT_I8_CTA_PAIR_WIDE|VT_I8_CTA_PAIR_SPLIT_TAIL",
+                  "VT_I8_AUTO|VT_I8_B_AS_STORED|VT_I8_CTA_PAIR|VT_I8_CTA_PAIR_WIDE",
                   "VT_SGEMM_AUTO|VT_SGEMM_TILE128|VT_SGEMM_TILE64|VT_SGEMM_SKINNY|VT_SGEMM_TF32X3|VT_SGEMM_SKINNY_TF32X3|VT_SGEMM_SKINNY_MMA_SYNC|VT_SGEMM_TILE32|VT_SGEMM_PANEL_TF32X3|VT_SGEMM_TALL_TF32X3|VT_SGEMM_PIPE128|VT_SGEMM_PIPE64|VT_SGEMM_PIPE64X128", "VT_HOST|VT_DEVICE|VT_HOST_AC_DEVICE_B"):
         for name in group.split("|"):
             m = re.search(r"\b%s\s*=\s*(\d+)" % name, text)

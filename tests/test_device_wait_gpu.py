@@ -16,7 +16,7 @@ pytestmark = pytest.mark.gpu
 SHORT = 4_000_000        # cycles: about 2 ms
 
 
-def exact_call(native, m, n, k, seed, variant=2):
+def exact_call(native, m, n, k, seed, variant=3):
     import torch
     gen = torch.Generator(device="cuda").manual_seed(seed)
     A = torch.randint(-128, 128, (m, k), dtype=torch.int8, device="cuda", generator=gen)
@@ -48,8 +48,8 @@ def test_a_wait_that_runs_out_is_reported_and_cleared(native):
 def test_pair_kernel_tears_down_when_its_peer_stops(native, shape):
     """The odd CTA of every pair stops feeding operands at the sixth ring fill.  The even CTA's wait for that
     fill runs out, both CTAs agree to give up, the even CTA settles the books of its barriers and waits for
-    the copies in flight, and the kernel returns.  The second shape shares its tail tiles between pairs, so
-    flags and partial sums of the aborted launch are what the next launch finds."""
+    the copies in flight, and the kernel returns.  The second shape gives most pairs two tiles, so the give-up
+    comes with accumulators in both states."""
     import torch
     m, n, k = shape
     st = native.torch_stream()
@@ -59,7 +59,7 @@ def test_pair_kernel_tears_down_when_its_peer_stops(native, shape):
     C = torch.zeros((m, n), dtype=torch.int32, device="cuda")
     try:
         native.test_set_wait_hooks(0, SHORT, 5)
-        native.i8gemm(A, B, C, m, n, k, variant=native.VT_I8_CTA_PAIR_SHARED_TAIL, where=native.VT_DEVICE, stream=st)
+        native.i8gemm(A, B, C, m, n, k, variant=native.VT_I8_CTA_PAIR, where=native.VT_DEVICE, stream=st)
         with pytest.raises(native.NativeError) as err:
             native.sync(0, st)
         assert err.value.code == native.VT_ERR_DEVICE_WAIT

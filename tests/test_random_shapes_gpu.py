@@ -105,7 +105,7 @@ def test_random_int8_shapes(native):
         b = rng.integers(-128, 128, (k, n), dtype=np.int8)
         want = go.matmul_exact(a.reshape(-1), b.reshape(-1), m, n, k).reshape(m, n)
         A, B = torch.from_numpy(a).cuda(), torch.from_numpy(b).cuda()
-        for variant in (0, 1, 2, 3, 4, 5):
+        for variant in (0, 1, 3, 4):
             C = torch.full((m, n), -2**31, dtype=torch.int32, device="cuda")
             native.i8gemm(A, B, C, m, n, k, variant=variant, raster=int(rng.integers(0, 4)),
                           batch_rows=int(rng.integers(1, 65)), where=native.VT_DEVICE, stream=st)

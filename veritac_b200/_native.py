@@ -30,10 +30,8 @@ VT_RASTER_AUTO = 3
 
 VT_I8_AUTO = 0
 VT_I8_B_AS_STORED = 1
-VT_I8_CTA_PAIR_SHARED_TAIL = 2
 VT_I8_CTA_PAIR = 3
 VT_I8_CTA_PAIR_WIDE = 4
-VT_I8_CTA_PAIR_SPLIT_TAIL = 5
 
 VT_SGEMM_AUTO = 0
 VT_SGEMM_TILE128 = 1

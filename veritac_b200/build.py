@@ -17,7 +17,7 @@ CSRC = PKG / "csrc"
 LIB = PKG / "libveritac_b200.so"
 SOURCES = ["runtime.cu", "i8gemm_sm100.cu", "i8gemm_wide_sm100.cu", "i8_tileprog.cu", "sgemm_sm100.cu", "sgemm_ffma_sm100.cu", "sgemm_tf32x3_sm100.cu",
            "sgemm_skinny_tma_sm100.cu", "sgemm_skinny_umma_sm100.cu", "capi.cu"]
-HEADERS = ["runtime.h", "ptx_sm100.cuh", "umma_tile.cuh", "skinny_sched.cuh", "i8_pair_sched.cuh", "../../include/veritac_b200.h"]
+HEADERS = ["runtime.h", "ptx_sm100.cuh", "umma_tile.cuh", "skinny_sched.cuh", "../../include/veritac_b200.h"]
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 
 

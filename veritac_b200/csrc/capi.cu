@@ -47,12 +47,17 @@ void raster_for(int raster, int batch_rows, int64_t M, int* mode, int* group) {
 // as 256 x 512 tiles: the pair kernel's second wave of tiles would be its last, so there is no later tile whose MMAs
 // the wide form's exposed epilogue could have overlapped, and its K loop runs closer to the tensor pipe's rate
 // (measured 49.4 against 51.3 us at 1024 x 8192 x 8192; 96.8 against 98.1 at 2048 rows, 371 against 367 at 8192).
-int resolve_i8_variant(int variant, int64_t M, int64_t N, int sm_count) {
+// 256 x 512 tiles where the 256 x 256 form would run a second round that most pairs take part in, on a long K:
+// measured (K = 8192, whole tiles / wide, us) 128 tiles 49.8 / 48.8 and 47.5 / 47.0, 144 tiles 50.3 / 48.9 and
+// 53.4 / 51.9; but 112 tiles 47.4 / 47.8, 96 tiles 48.2 / 51.8, 80 tiles 47.8 / 54.6 (the few pairs of a short
+// second round run it fast, the wide form makes everybody's tile twice as long), and at K = 2048 128 tiles 21.8 / 22.2
+// (the unoverlapped epilogue weighs more).
+int resolve_i8_variant(int variant, int64_t M, int64_t N, int64_t K, int sm_count) {
   if (variant != VT_I8_AUTO) return variant;
   if (M <= 128) return VT_I8_B_AS_STORED;
   const int64_t tiles = ((M + 255) / 256) * ((N + 255) / 256);
   const int64_t pairs = sm_count / 2;
-  return (tiles > pairs && tiles <= 2 * pairs && N > 256) ? VT_I8_CTA_PAIR_WIDE : VT_I8_CTA_PAIR;
+  return (tiles * 10 >= pairs * 17 && tiles <= 2 * pairs && N > 256 && K >= 4096) ? VT_I8_CTA_PAIR_WIDE : VT_I8_CTA_PAIR;
 }
 
 cudaStream_t pick_stream(DeviceCtx* c, void* stream) { return stream ? static_cast<cudaStream_t>(stream) : c->stream; }
@@ -298,7 +303,7 @@ int vt_i8gemm(int dev, const int8_t* A, const int8_t* B, int32_t* C, int64_t M, 
   if (!c) return VT_ERR_CUDA;
   int mode, group;
   raster_for(raster, batch_rows, M, &mode, &group);
-  variant = resolve_i8_variant(variant, M, N, c->sm_count);
+  variant = resolve_i8_variant(variant, M, N, K, c->sm_count);
   if (where == VT_HOST) return i8gemm_from_host(c, A, B, C, M, N, K, mode, group, variant);
   if (where == VT_HOST_AC_DEVICE_B) {
     const cudaStream_t b_ready = pick_stream(c, stream);
@@ -359,7 +364,7 @@ int vt_i8gemm_rows_streamed_b(int dev, const int8_t* A, int a_where, const int8_
   for (int j = 0; j < n_blocks; ++j) {
     const int64_t cols = block_cols[j];
     VT_CUDA(cudaStreamWaitEvent(c->stream, static_cast<cudaEvent_t>(block_ready[j]), 0));
-    rc = launch_i8gemm(c, dA, B_blocks[j], dC + c0, M, cols, K, mode, group, resolve_i8_variant(variant, M, cols, c->sm_count),
+    rc = launch_i8gemm(c, dA, B_blocks[j], dC + c0, M, cols, K, mode, group, resolve_i8_variant(variant, M, cols, K, c->sm_count),
                        c->stream, cols, N);
     if (rc) return rc;
     VT_CUDA(cudaEventRecord(ev_k, c->stream));

@@ -20,7 +20,6 @@
 // column-major for reuse_b j,k,i, grouped for the batched B-reuse lowering); the order changes L2
 // reuse only, never results.
 #include "ptx_sm100.cuh"
-#include "i8_pair_sched.cuh"
 #include "runtime.h"
 #include "umma_tile.cuh"
 
@@ -224,9 +223,9 @@ i8gemm_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
 //   * both producers signal the even CTA's "full" barrier (it expects both CTAs' bytes);
 //   * tcgen05.commit multicasts the "empty" and "accumulator full" arrivals to both CTAs;
 //   * both CTAs' epilogue warps arrive on the even CTA's "accumulator empty" barrier (8 arrivals).
-// The work list (i8_pair_sched.cuh) shares the K blocks of the last, partial wave of tiles between all
-// pairs: a pair may leave a partial accumulator of a tile in scratch memory (`partials`, one
-// 128 x 256 int32 slot per CTA) and set a flag per epilogue warp; the pair that owns the tile adds it.
+// Tiles go to the pairs round-robin, a whole tile at a time.  (Sharing the K blocks of a last, partial round of tiles
+// between the pairs was built three ways, bit-exact, and measured level: while some pairs idle the others run their
+// K blocks faster, so a half-empty last round costs little.)
 // ---------------------------------------------------------------------------------------------
 constexpr int P_A_BYTES = 128 * BK;                 // this CTA's 128 rows of A
 constexpr int P_B_BYTES = 128 * BK;                 // this CTA's 128 columns of B (one TMA box)
@@ -240,36 +239,16 @@ constexpr int P_EPI_BUFS = 1;                       // store buffers (4 KiB) per
 constexpr int P_THREADS = 32 * (2 + P_EPI_WARPS);   // 1 TMA warp, 1 MMA warp, the epilogue warps
 constexpr int P_WARP_CHUNKS = 8 / (P_EPI_WARPS / 4);   // 32-column chunks of the accumulator one epilogue warp moves
 static_assert(P_EPI_WARPS == 4 || P_EPI_WARPS == 8, "one or two epilogue warps per TMEM lane quarter");
-constexpr int P_RANGE_TABLE = 32;
-constexpr int P_TAIL_ITEMS = 4;                     // a pair's range is at most one tile long: a partial piece and <= 2 tiles
-constexpr size_t P_SLOT_UINT4 = size_t(128) * 256 * 4 / 16;   // one CTA's partial accumulator
-
 struct PairPipeState {
   uint64_t full[P_STAGES];
   uint64_t empty[P_STAGES];
   uint64_t tmem_full[2];
   uint64_t tmem_empty[2];
-  uint64_t preload_done;   // even CTA: every epilogue warp of the pair has written the contributors' sums into the accumulator
   uint32_t tmem_base;
   int abort_word;
   uint32_t peer_abort;     // the peer CTA's abort word, written by the peer before the closing cluster barrier
   uint32_t fills_own;      // ring fills this CTA's producer issued
   uint32_t fills_peer;     // even CTA only: ring fills the odd CTA's producer issued
-  int tail_items;          // this pair's items in the shared tail (range order), worked out once during set-up
-  PairItem tail_item[P_TAIL_ITEMS];
-  int range_begin[P_RANGE_TABLE];   // range begins of pairs [pair - 30, pair + 1]
-};
-
-// Range begins from the table in shared memory; a pair further back than the table reaches is computed directly
-// (a tile has at most eight pieces, so its contributors are the few pairs just before the owner).
-struct PairRangeTable {
-  const int* table;
-  int first;
-  const PairSched& s;
-  __device__ int operator()(int p) const {
-    const int i = p - first;
-    return (i >= 0 && i < P_RANGE_TABLE) ? table[i] : pair_range_begin(s, p);
-  }
 };
 
 constexpr size_t PAIR_SMEM_BYTES =
@@ -277,37 +256,13 @@ constexpr size_t PAIR_SMEM_BYTES =
 static_assert(PAIR_SMEM_BYTES <= 227 * 1024, "shared memory per CTA");
 static_assert(sizeof(PairPipeState) <= 512, "pipeline state outgrew its shared-memory reserve");
 
-// Item `i` of this pair in execution order (pair_item of i8_pair_sched.cuh, with the tail items read from shared
-// memory): whole tiles come after the partial piece when the pair has one, else after its tail items.
-__device__ __forceinline__ bool pair_next(const PairSched& sched, const PairPipeState* ps, int pair, int i, PairItem& it) {
-  const int n_tail = ps->tail_items;
-  const int w0 = pair_whole_first(sched, n_tail, n_tail > 0 && ps->tail_item[0].kind == PAIR_ITEM_PARTIAL);
-  if (i >= w0 && i < w0 + sched.whole_waves) {
-    const long long tile = (long long)pair + (long long)(i - w0) * sched.pairs;
-    if (tile < sched.tiles) {
-      it.tile = int(tile);
-      it.kb0 = 0;
-      it.kb1 = sched.kblocks;
-      it.kind = PAIR_ITEM_TO_C;
-      it.contrib0 = it.ncontrib = it.preload = 0;
-      return true;
-    }
-    if (sched.tail == 0) return false;               // whole_waves is an upper bound when nothing is shared
-  }
-  const int t = i < w0 ? i : i - sched.whole_waves;
-  if (t >= n_tail) return false;
-  it = ps->tail_item[t];
-  return true;
-}
-
 // `wait_limit`: cycles a device-side wait may take before the pair gives up (kWaitLimitCycles in production).
 // `stop_fill`: test hook, -1 in production; the odd CTA's producer stops before this ring fill as if its wait for the
 // stage had run out, so the fill never completes, the even CTA's wait for it runs out and the teardown runs.
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
 i8gemm_umma_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                        const __grid_constant__ CUtensorMap tmC, int M, int N, int K, TileRaster rs, PairSched sched,
-                        uint4* __restrict__ partials, int* __restrict__ flags, int* __restrict__ status,
-                        long long wait_limit, int stop_fill) {
+                        const __grid_constant__ CUtensorMap tmC, int M, int N, int K, TileRaster rs,
+                        int* __restrict__ status, long long wait_limit, int stop_fill) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* staging = tiles + size_t(P_STAGES) * P_STAGE_BYTES;
@@ -322,23 +277,10 @@ i8gemm_umma_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
   const uint32_t rank = cluster_cta_rank();          // 0 = even CTA (issues the MMAs), 1 = its peer
   const int pair = blockIdx.x >> 1;
 
-  if (warp == 2) {
-    // The work list depends on the launch arguments only: worked out here, before the wait for the kernel ahead
-    // on the stream, it costs nothing.  Each lane takes one range begin (a division each), lane 0 builds the items.
-    ps->range_begin[lane] = pair_range_begin(sched, pair - (P_RANGE_TABLE - 2) + lane);   // pairs [pair - 30, pair + 1]
-    __syncwarp();
-    if (lane == 0) {
-      const PairRangeTable begin{ps->range_begin, pair - (P_RANGE_TABLE - 2), sched};
-      int n = pair_tail_items(sched, pair, begin);
-      if (n > P_TAIL_ITEMS) n = P_TAIL_ITEMS;          // cannot happen: a range is at most one tile long
-      for (int i = 0; i < n; ++i) {
-        PairItem it;
-        pair_tail_item(sched, pair, i, it, begin);
-        ps->tail_item[i] = it;
-      }
-      ps->tail_items = n;
-    }
-  }
+  const int num_pairs = gridDim.x >> 1;
+  const int num_tiles = rs.mt * rs.nt;
+  const int kblocks = (K + BK - 1) / BK;
+
   if (threadIdx.x == 0) {
     for (int s = 0; s < P_STAGES; ++s) {
       mbar_init(&ps->full[s], 1);                    // the even CTA's producer arrives (with both CTAs' bytes)
@@ -348,7 +290,6 @@ i8gemm_umma_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
       mbar_init(&ps->tmem_full[b], 1);               // one multicast commit
       mbar_init(&ps->tmem_empty[b], 2 * P_EPI_WARPS);   // the epilogue warps of both CTAs
     }
-    mbar_init(&ps->preload_done, 2 * P_EPI_WARPS);
     ps->abort_word = 0;
     ps->peer_abort = 0;
     ps->fills_own = 0;
@@ -367,8 +308,8 @@ i8gemm_umma_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
   cluster_sync_all();                                // peer barriers exist before anything signals them
   tc_fence_after_sync();
   const uint32_t tmem_base = ps->tmem_base;
-  // The set-up above may overlap the end of the kernel before this one on the stream; operands, C, scratch,
-  // flags and the status word are not touched before that kernel has completed.
+  // The set-up above may overlap the end of the kernel before this one on the stream; operands, C and the status
+  // word are not touched before that kernel has completed.
   grid_dependency_wait();
   grid_launch_dependents();
 
@@ -379,12 +320,11 @@ i8gemm_umma_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
       uint32_t phase = 0;
       uint32_t fills = 0;
       bool ok = true;
-      PairItem it;
-      for (int i = 0; ok && pair_next(sched, ps, pair, i, it); ++i) {
+      for (int t = pair; t < num_tiles && ok; t += num_pairs) {
         int mi, ni;
-        tile_coords(rs, it.tile, mi, ni);
+        tile_coords(rs, t, mi, ni);
         const int m0 = mi * 256 + int(rank) * 128, n0 = ni * 256 + int(rank) * 128;
-        for (int kb = it.kb0; kb < it.kb1; ++kb) {
+        for (int kb = 0; kb < kblocks; ++kb) {
           if (!mbar_wait(&ps->empty[stage], phase ^ 1, abort_word, KSTAT_WAIT_EXPIRED_PRODUCER, wait_limit)) {
             ok = false;
             break;
@@ -432,15 +372,11 @@ i8gemm_umma_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
-      PairItem it;
-      for (int i = 0; ok && pair_next(sched, ps, pair, i, it); ++i) {
+      for (int t = pair; t < num_tiles && ok; t += num_pairs) {
         if (!mbar_wait<true>(&ps->tmem_empty[acc], acc_phase ^ 1, abort_word, KSTAT_WAIT_EXPIRED_MMA, wait_limit)) break;
-        // An owned tail tile whose contributors' sums the epilogue warps write into the accumulator first (at most
-        // one per launch, so the barrier is used once).
-        if (it.preload && !mbar_wait<true>(&ps->preload_done, 0, abort_word, KSTAT_WAIT_EXPIRED_MMA, wait_limit)) break;
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + uint32_t(acc * BN);
-        for (int kb = it.kb0; kb < it.kb1; ++kb) {
+        for (int kb = 0; kb < kblocks; ++kb) {
           if (!mbar_wait<true>(&ps->full[stage], phase, abort_word, KSTAT_WAIT_EXPIRED_MMA, wait_limit)) {
             ok = false;
             break;
@@ -452,7 +388,7 @@ i8gemm_umma_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
           for (int kk = 0; kk < BK / UMMA_K; ++kk) {
             const uint64_t a_desc = umma_smem_desc_sw128(a_addr + kk * UMMA_K, 16, 1024);
             const uint64_t b_desc = umma_smem_desc_sw128(b_addr + kk * UMMA_K * 128, P_B_BYTES, 1024);
-            umma_i8<2>(d_tmem, a_desc, b_desc, idesc, uint32_t(it.preload != 0 || kb != it.kb0 || kk != 0));
+            umma_i8<2>(d_tmem, a_desc, b_desc, idesc, uint32_t((kb | kk) != 0));
           }
           umma_commit_pair(&ps->empty[stage], 3);
           if (++stage == P_STAGES) {
@@ -475,77 +411,24 @@ i8gemm_umma_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
     const int c_begin = (e >> 2) * P_WARP_CHUNKS, c_end = c_begin + P_WARP_CHUNKS;
     int acc = 0;
     uint32_t acc_phase = 0;
-    // This quarter's part of a CTA's scratch slot and this warp's flag: pair p, CTA rank r -> slot 2p + r.
-    const size_t warp_off = size_t(q) * (P_SLOT_UINT4 / 4) + size_t(lane);
-    uint4* my_slot = partials + (size_t(pair) * 2 + rank) * P_SLOT_UINT4 + warp_off;
-    int* my_flag = flags + (pair * 2 + int(rank)) * P_EPI_WARPS + e;
-    PairItem it, next;
-    bool have = pair_next(sched, ps, pair, 0, it);
-    for (int i = 0; have; ++i) {
-      const bool more = pair_next(sched, ps, pair, i + 1, next);
+    for (int t = pair; t < num_tiles; t += num_pairs) {
       int mi, ni;
-      tile_coords(rs, it.tile, mi, ni);
+      tile_coords(rs, t, mi, ni);
       const int m0 = mi * 256 + int(rank) * 128, n0 = ni * 256;
       const bool ready = mbar_wait<true>(&ps->tmem_full[acc], acc_phase, abort_word, KSTAT_WAIT_EXPIRED_EPILOGUE, wait_limit);
       if (!__all_sync(0xffffffffu, ready)) break;
       tc_fence_after_sync();
       const uint32_t t_row = tmem_base + (uint32_t(q * 32) << 16) + uint32_t(acc * BN);
-      if (it.kind == PAIR_ITEM_PARTIAL) {
-        epilogue_warp_partial(t_row, my_slot, c_begin, c_end);
-        __threadfence();
-        __syncwarp();
-        if (lane == 0) st_release_gpu(my_flag, 1);
-      } else {
-        const uint4* merge = nullptr;
-        const int n_merge = it.preload ? 0 : it.ncontrib;      // preloaded sums are in the accumulator already
-        if (n_merge > 0) {
-          // Same warp, same lane of the contributors' CTAs of this rank: their flags first, then their sums.
-          bool there = true;
-          for (int x = 0; x < it.ncontrib && there; ++x)
-            there = flag_wait(flags + ((it.contrib0 + x) * 2 + int(rank)) * P_EPI_WARPS + e, abort_word,
-                              KSTAT_WAIT_EXPIRED_PEER, wait_limit);
-          if (!__all_sync(0xffffffffu, there)) break;
-          merge = partials + (size_t(it.contrib0) * 2 + rank) * P_SLOT_UINT4 + warp_off;
-        }
-        // The last item's epilogue overlaps nothing, and by now every MMA of this pair has read its operands and
-        // no load is in flight: the operand ring serves as one store buffer per column chunk (128 KiB in all).
-        uint8_t* wide = more ? nullptr : tiles + size_t(e) * P_WARP_CHUNKS * EPI_BUF_BYTES;
-        epilogue_warp_tile<P_EPI_BUFS>(t_row, &tmC, staging + e * P_EPI_BUFS * EPI_BUF_BYTES, M, N, m0 + q * 32, n0, lane,
-                                       store_policy, wide,
-                              merge, n_merge, 2 * P_SLOT_UINT4, c_begin, c_end);
-        if (n_merge > 0) {
-          __syncwarp();
-          if (lane == 0)
-            for (int x = 0; x < it.ncontrib; ++x)
-              flags[((it.contrib0 + x) * 2 + int(rank)) * P_EPI_WARPS + e] = 0;   // for the next launch
-        }
-      }
+      // The last tile's epilogue overlaps nothing, and by now every MMA of this pair has read its operands and
+      // no load is in flight: the operand ring serves as one store buffer per column chunk (128 KiB in all).
+      uint8_t* wide = t + num_pairs < num_tiles ? nullptr : tiles + size_t(e) * P_WARP_CHUNKS * EPI_BUF_BYTES;
+      epilogue_warp_tile<P_EPI_BUFS>(t_row, &tmC, staging + e * P_EPI_BUFS * EPI_BUF_BYTES, M, N, m0 + q * 32, n0, lane,
+                                     store_policy, wide, c_begin, c_end);
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive_remote(&ps->tmem_empty[acc], 0);
-      // The item after next uses this accumulator again.  If it is an owned tail tile to preload, this warp adds
-      // the contributors' sums into its own part of the accumulator now, while the item in between is multiplied.
-      PairItem ahead;
-      if (more && pair_next(sched, ps, pair, i + 2, ahead) && ahead.preload) {
-        bool there = true;
-        for (int x = 0; x < ahead.ncontrib && there; ++x)
-          there = flag_wait(flags + ((ahead.contrib0 + x) * 2 + int(rank)) * P_EPI_WARPS + e, abort_word,
-                            KSTAT_WAIT_EXPIRED_PEER, wait_limit);
-        if (!__all_sync(0xffffffffu, there)) break;
-        preload_warp_tile(t_row, partials + (size_t(ahead.contrib0) * 2 + rank) * P_SLOT_UINT4 + warp_off, ahead.ncontrib,
-                          2 * P_SLOT_UINT4, c_begin, c_end);
-        tc_fence_before_sync();
-        __syncwarp();
-        if (lane == 0) {
-          mbar_arrive_remote(&ps->preload_done, 0);
-          for (int x = 0; x < ahead.ncontrib; ++x)
-            flags[((ahead.contrib0 + x) * 2 + int(rank)) * P_EPI_WARPS + e] = 0;   // for the next launch
-        }
-      }
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1;
-      it = next;
-      have = more;
     }
     // The stores have read their shared-memory buffers; the writes themselves complete before the grid does.
     if (lane == 0) tma_store_wait_read<0>();
@@ -578,7 +461,7 @@ int launch_i8gemm(DeviceCtx* c, const int8_t* A, const int8_t* B, int32_t* C, in
   if (ldc == 0) ldc = N;
   if (ldb < N || ldc < N || (ldb & 15) || (ldc & 3)) return fail(VT_ERR_INVALID, "bad row pitch for B or C");
   if (variant == VT_I8_CTA_PAIR_WIDE) return launch_i8gemm_wide(c, A, B, C, M, N, K, raster_mode, group, s, ldb, ldc);
-  if ((variant < VT_I8_B_AS_STORED || variant > VT_I8_CTA_PAIR) && variant != VT_I8_CTA_PAIR_SPLIT_TAIL)
+  if (variant != VT_I8_B_AS_STORED && variant != VT_I8_CTA_PAIR)
     return fail(VT_ERR_UNSUPPORTED, "i8gemm variant %d is not built", variant);
   if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(C)) & 15)
     return fail(VT_ERR_INVALID, "i8gemm operands must be 16-byte aligned");
@@ -616,23 +499,15 @@ int launch_i8gemm(DeviceCtx* c, const int8_t* A, const int8_t* B, int32_t* C, in
     VT_CUDA(cudaGetLastError());
     return VT_OK;
   }
-  // VT_I8_CTA_PAIR_SHARED_TAIL / _SPLIT_TAIL: the tail is shared only when all pairs of the device take part;
-  // otherwise, and for VT_I8_CTA_PAIR, every tile is computed whole by one pair.
   const int max_pairs = c->sm_count / 2;
-  const int kblocks = int((K + BK - 1) / BK);
-  const int share = variant == VT_I8_CTA_PAIR_SHARED_TAIL ? PAIR_SHARE_RANGES
-                    : variant == VT_I8_CTA_PAIR_SPLIT_TAIL ? PAIR_SHARE_EQUAL_SPLIT : PAIR_SHARE_NONE;
-  PairSched sched = make_pair_sched(max_pairs, int(tiles), kblocks, share);
-  if (sched.tail == 0)
-    sched = make_pair_sched(int(tiles < max_pairs ? tiles : max_pairs), int(tiles), kblocks, PAIR_SHARE_NONE);
+  const int pairs = int(tiles < max_pairs ? tiles : max_pairs);
   if (!(c->func_attr_mask & 4u)) {
     VT_CUDA(cudaFuncSetAttribute(i8gemm_umma_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  int(PAIR_SMEM_BYTES)));
     c->func_attr_mask |= 4u;
   }
-  VT_CUDA(launch_overlapped(i8gemm_umma_pair_kernel, unsigned(2 * sched.pairs), unsigned(P_THREADS), PAIR_SMEM_BYTES, s,
-                            tmA, tmB, tmC, iM, iN, iK, rs, sched, static_cast<uint4*>(c->i8_partials), c->i8_flags,
-                            c->status, c->wait_limit_cycles, c->i8_stop_fill));
+  VT_CUDA(launch_overlapped(i8gemm_umma_pair_kernel, unsigned(2 * pairs), unsigned(P_THREADS), PAIR_SMEM_BYTES, s, tmA, tmB,
+                            tmC, iM, iN, iK, rs, c->status, c->wait_limit_cycles, c->i8_stop_fill));
   count_launch();
   VT_CUDA(cudaGetLastError());
   return VT_OK;

@@ -202,7 +202,7 @@ i8gemm_umma_pair_wide_kernel(const __grid_constant__ CUtensorMap tmA, const __gr
       // serves as store buffers (192 KiB shared out between the warps), so that few stores wait for a buffer.
       uint8_t* wide = t + num_pairs >= num_tiles ? tiles + size_t(e) * W_WIDE_BUFS * EPI_BUF_BYTES : nullptr;
       epilogue_warp_tile<1, W_WIDE_BUFS>(t_row, &tmC, staging + e * EPI_BUF_BYTES, M, N, m0 + q * 32, n0, lane, store_policy, wide,
-                               nullptr, 0, 0, c_begin, c_end);
+                                         c_begin, c_end);
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive_remote(&ps->tmem_empty, 0);

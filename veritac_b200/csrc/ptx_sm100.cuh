@@ -18,7 +18,6 @@ enum : int {
   KSTAT_WAIT_EXPIRED_MMA = 102,       // MMA issuer gave up on a "full"/"tmem empty" barrier
   KSTAT_WAIT_EXPIRED_EPILOGUE = 103,  // epilogue gave up on a "tmem full" barrier
   KSTAT_WAIT_EXPIRED_DRAIN = 104,     // teardown gave up waiting for copies in flight
-  KSTAT_WAIT_EXPIRED_PEER = 105,      // gave up on a flag in global memory that another CTA sets
 };
 
 // ~2 s at 2 GHz; a healthy pipeline waits microseconds.
@@ -132,35 +131,6 @@ __device__ __forceinline__ float4 ld_shared_cluster_v4f(uint32_t cluster_addr) {
 // 32-bit store into the shared memory of a CTA of this cluster (address from mapa_shared).
 __device__ __forceinline__ void st_shared_cluster_u32(uint32_t cluster_addr, uint32_t v) {
   asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
-}
-
-// Flags in global memory that one CTA sets and another waits for.
-__device__ __forceinline__ void st_release_gpu(int* p, int v) {
-  asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ int ld_acquire_gpu(const int* p) {
-  int v;
-  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-// Bounded wait for a non-zero flag; same abort protocol as mbar_wait.
-__device__ __forceinline__ bool flag_wait(const int* flag, volatile int* abort_word, int code,
-                                          long long limit_cycles = kWaitLimitCycles) {
-  long long t0 = 0;
-#pragma unroll 1
-  for (uint32_t spin = 0;; ++spin) {
-    if (ld_acquire_gpu(flag) != 0) return true;
-    if ((spin & 0x3f) == 0x3f) {
-      if (*abort_word != 0) return false;
-      const long long now = clock64();
-      if (t0 == 0) {
-        t0 = now;
-      } else if (now - t0 > limit_cycles) {
-        atomicCAS(const_cast<int*>(abort_word), 0, code);
-        return false;
-      }
-    }
-  }
 }
 
 // Teardown wait used while aborting: ignores the abort word, shorter limit, no bookkeeping.
@@ -411,17 +381,6 @@ __device__ __forceinline__ void tmem_st_32x32b_x16(uint32_t taddr, const uint32_
       "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
       : "memory");
 }
-__device__ __forceinline__ void tmem_st_32x32b_x32(uint32_t taddr, const uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
-      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
-      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};" ::"r"(taddr),
-      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
-      "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]),
-      "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]),
-      "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
-      : "memory");
-}
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
@@ -432,13 +391,6 @@ __device__ __forceinline__ uint32_t cluster_cta_rank() {
 }
 __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-
-// 16-byte load that bypasses L1 (data another SM wrote during this kernel).
-__device__ __forceinline__ uint4 ld_global_cg_v4(const void* p) {
-  uint4 v;
-  asm volatile("ld.global.cg.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
-  return v;
 }
 
 // Streaming 16-byte store (C is written once and never re-read by the kernel).

@@ -86,10 +86,6 @@ DeviceCtx* ctx_for(int dev) {
   CTX_TRY(cudaMallocHost(&c->status_host, sizeof(int)));
   CTX_TRY(cudaMalloc(&c->tickets, kTicketCount * sizeof(int)));
   CTX_TRY(cudaMemset(c->tickets, 0, kTicketCount * sizeof(int)));
-  c->i8_flag_count = c->sm_count * 8;
-  CTX_TRY(cudaMalloc(&c->i8_flags, size_t(c->i8_flag_count) * sizeof(int)));
-  CTX_TRY(cudaMemset(c->i8_flags, 0, size_t(c->i8_flag_count) * sizeof(int)));
-  CTX_TRY(cudaMalloc(&c->i8_partials, size_t(c->sm_count) * 128 * 256 * sizeof(int32_t)));
   for (auto& ev : c->ev) CTX_TRY(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
   CTX_TRY(cudaEventCreateWithFlags(&c->staging_consumed, cudaEventDisableTiming));
 #undef CTX_TRY
@@ -148,7 +144,6 @@ int ctx_check_status(DeviceCtx* c, cudaStream_t s) {
   if (st != KSTAT_OK) {
     VT_CUDA(cudaMemsetAsync(c->status, 0, sizeof(int), s));
     VT_CUDA(cudaMemsetAsync(c->tickets, 0, kTicketCount * sizeof(int), s));   // an aborted kernel may have left counts behind
-    VT_CUDA(cudaMemsetAsync(c->i8_flags, 0, size_t(c->i8_flag_count) * sizeof(int), s));
     VT_CUDA(cudaStreamSynchronize(s));
     return fail(VT_ERR_DEVICE_WAIT, "a kernel gave up on a bounded device-side wait (status %d)", st);
   }
@@ -169,8 +164,6 @@ void ctx_destroy_all() {
     if (c->staging) cudaFreeHost(c->staging);
     if (c->staging_consumed) cudaEventDestroy(c->staging_consumed);
     if (c->tickets) cudaFree(c->tickets);
-    if (c->i8_flags) cudaFree(c->i8_flags);
-    if (c->i8_partials) cudaFree(c->i8_partials);
     for (auto& ev : c->ev)
       if (ev) cudaEventDestroy(ev);
     if (c->stream) cudaStreamDestroy(c->stream);

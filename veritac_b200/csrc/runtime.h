@@ -26,12 +26,7 @@ struct DeviceCtx {
   cudaStream_t copy_out = nullptr;     // device->host staging
   int* status = nullptr;               // device word kernels write a KSTAT_* code into
   int* status_host = nullptr;          // pinned mirror
-  int* tickets = nullptr;              // kTicketCount zeroed counters (per-slab arrival counts of the skinny kernel)
-  // int8 CTA-pair kernel: one 128 x 256 int32 partial accumulator per CTA and up to eight flags, one per epilogue warp (zero
-  // between launches), sized for one CTA per SM at context creation so that no launch ever allocates
-  void* i8_partials = nullptr;
-  int* i8_flags = nullptr;
-  int i8_flag_count = 0;
+  int* tickets = nullptr;              // kTicketCount zeroed counters (arrivals per slab of the skinny kernels, per tile of a K split)
   // Test hooks (vt_test_set_wait_hooks): how long a device-side wait may take, and the ring fill at which the odd
   // CTA of every int8 pair stops (-1: never).
   long long wait_limit_cycles = 4000000000LL;
@@ -125,8 +120,7 @@ cudaError_t launch_overlapped_cluster(void (*kernel)(KArgs...), unsigned grid, u
 // ---- kernel launchers (device pointers only) ------------------------------------------------
 // raster_mode: 0 row-major tiles, 1 column-major tiles, 2 grouped (group = tile-rows per sweep).
 // variant: VT_I8_B_AS_STORED (one CTA per 128 x 256 tile), VT_I8_CTA_PAIR (two CTAs per 256 x 256 tile),
-// VT_I8_CTA_PAIR_SHARED_TAIL (the same with the last partial wave of tiles shared along K), VT_I8_CTA_PAIR_WIDE (two
-// CTAs per 256 x 512 tile).
+// VT_I8_CTA_PAIR_WIDE (two CTAs per 256 x 512 tile).
 // ldb / ldc: row pitch of B and C in elements when they are sub-blocks of wider matrices (0 = N).
 int launch_i8gemm(DeviceCtx* c, const int8_t* A, const int8_t* B, int32_t* C, int64_t M, int64_t N, int64_t K,
                   int raster_mode, int group, int variant, cudaStream_t s, int64_t ldb = 0, int64_t ldc = 0);

@@ -211,7 +211,7 @@ sgemm_ffma_kernel(const float* __restrict__ A, const float* __restrict__ B, floa
   // its slice of all partial tiles in split order.
   ff_cp_async_wait<0>();
   __syncthreads();                        // everyone is done reading the ring
-  constexpr int kRowF4 = BN / 4, kTileF4 = BM * kRowF4;
+  constexpr int kRowF4 = BN / 4;
 #pragma unroll
   for (int j = 0; j < 8; ++j)
 #pragma unroll

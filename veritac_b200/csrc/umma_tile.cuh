@@ -46,144 +46,40 @@ __device__ __forceinline__ void tile_coords(const TileRaster& rs, int t, int& mi
 // `wide`, when given, is one further buffer per column chunk (4 KiB each, 1024-byte aligned) that nothing else uses any more: every
 // column chunk then gets a buffer of its own and no store waits for the one before it (the last tile of a
 // CTA, whose epilogue nothing overlaps, takes them from the idle operand ring).
-// `merge`, when given, points at this lane's first 16 bytes of `ncontrib` partial accumulators of the same
-// tile (the layout epilogue_warp_partial writes, `merge_stride` uint4 apart); they are added before the
-// store.  The loads of one chunk are issued while the chunk before it is added and stored.
 // A `wide` area of fewer buffers than chunks (kWide) is used round-robin: a chunk then waits for the store that
 // last read its buffer.
 // Returns once the accumulator has been read (the stores may still be in flight).
 template <int kBufs = 2, int kWide = 16>
-__device__ __forceinline__ void epilogue_store_chunk(const uint32_t (&r)[32], int c, int c_begin, const CUtensorMap* tmC,
-                                                     uint8_t* staging, int M, int N, int row0, int n0, int lane,
-                                                     uint64_t store_policy, uint8_t* wide) {
-  uint8_t* buf = wide ? wide + ((c - c_begin) % kWide) * EPI_BUF_BYTES : staging + (c & (kBufs - 1)) * EPI_BUF_BYTES;
-  if (!wide) {
-    if (lane == 0) tma_store_wait_read<kBufs - 1>();   // the store that last read this buffer is done with it
-    __syncwarp();
-  } else if (c - c_begin >= kWide) {
-    if (lane == 0) tma_store_wait_read<kWide - 1>();
-    __syncwarp();
-  }
-  const uint32_t base = smem_u32(buf) + uint32_t(lane) * 128u;
-#pragma unroll
-  for (int v = 0; v < 8; ++v)
-    st_shared_v4(base + (uint32_t(v ^ (lane & 7)) << 4), r[4 * v], r[4 * v + 1], r[4 * v + 2], r[4 * v + 3]);
-  fence_proxy_async_smem();
-  __syncwarp();
-  if (lane == 0) {
-    if (row0 < M && n0 + c * 32 < N) {
-      if (store_policy) tma_store_2d_hint(tmC, buf, n0 + c * 32, row0, store_policy);
-      else tma_store_2d(tmC, buf, n0 + c * 32, row0);
-    }
-    tma_store_commit();
-  }
-}
-
-template <int kBufs = 2, int kWide = 16>
 __device__ __forceinline__ void epilogue_warp_tile(uint32_t t_row, const CUtensorMap* tmC, uint8_t* staging, int M,
                                                    int N, int row0, int n0, int lane, uint64_t store_policy = 0,
-                                                   uint8_t* wide = nullptr, const uint4* merge = nullptr,
-                                                   int ncontrib = 0, size_t merge_stride = 0, int c_begin = 0,
-                                                   int c_end = BN / 32) {
-  if (ncontrib == 0) {
-#pragma unroll 1
-    for (int c = c_begin; c < c_end; ++c) {
-      uint32_t r[32];
-      tmem_ld_32x32b_x32(t_row + uint32_t(c * 32), r);
-      tmem_ld_wait();
-      epilogue_store_chunk<kBufs, kWide>(r, c, c_begin, tmC, staging, M, N, row0, n0, lane, store_policy, wide);
-    }
-    return;
-  }
-  // With partial sums to add, the loads from scratch memory (L2 hits, ~1 us each way) set the pace unless several
-  // are in flight: the (chunk, contributor) steps are walked with kDepth loads of 128 bytes per lane outstanding.
-  constexpr int kDepth = 3;
-  const int steps = (c_end - c_begin) * ncontrib;
-  auto source = [&](int t) {
-    const int c = c_begin + t / ncontrib, x = t - (t / ncontrib) * ncontrib;
-    return merge + size_t(x) * merge_stride + size_t(c) * 256;
-  };
-  uint4 ahead[kDepth][8];
-#pragma unroll
-  for (int d = 0; d < kDepth; ++d)
-    if (d < steps) {
-      const uint4* src = source(d);
-#pragma unroll
-      for (int v = 0; v < 8; ++v) ahead[d][v] = ld_global_cg_v4(src + v * 32);
-    }
-  uint32_t r[32];
-#pragma unroll 1
-  for (int t0 = 0; t0 < steps; t0 += kDepth) {
-#pragma unroll
-    for (int d = 0; d < kDepth; ++d) {
-      const int t = t0 + d;
-      if (t < steps) {
-        const int c = c_begin + t / ncontrib, x = t - (t / ncontrib) * ncontrib;
-        if (x == 0) {
-          tmem_ld_32x32b_x32(t_row + uint32_t(c * 32), r);
-          tmem_ld_wait();
-        }
-#pragma unroll
-        for (int v = 0; v < 8; ++v) {
-          r[4 * v] += ahead[d][v].x;
-          r[4 * v + 1] += ahead[d][v].y;
-          r[4 * v + 2] += ahead[d][v].z;
-          r[4 * v + 3] += ahead[d][v].w;
-        }
-        if (t + kDepth < steps) {
-          const uint4* src = source(t + kDepth);
-#pragma unroll
-          for (int v = 0; v < 8; ++v) ahead[d][v] = ld_global_cg_v4(src + v * 32);
-        }
-        if (x == ncontrib - 1)
-          epilogue_store_chunk<kBufs, kWide>(r, c, c_begin, tmC, staging, M, N, row0, n0, lane, store_policy, wide);
-      }
-    }
-  }
-}
-
-// Leaves one warp's 32 rows x 32 (c_end - c_begin) columns of an accumulator in scratch memory as a partial sum that
-// another CTA will add (epilogue_warp_tile's `merge`).  `slot` is this lane's first 16 bytes of the quarter's 32 KiB:
-// uint4 index ((chunk * 8 + v) * 32 + lane) holds columns [32 chunk + 4 v, +4) of the lane's row, so every
-// store instruction of the warp writes 512 contiguous bytes.
-__device__ __forceinline__ void epilogue_warp_partial(uint32_t t_row, uint4* slot, int c_begin = 0, int c_end = BN / 32) {
+                                                   uint8_t* wide = nullptr, int c_begin = 0, int c_end = BN / 32) {
 #pragma unroll 1
   for (int c = c_begin; c < c_end; ++c) {
     uint32_t r[32];
     tmem_ld_32x32b_x32(t_row + uint32_t(c * 32), r);
     tmem_ld_wait();
-#pragma unroll
-    for (int v = 0; v < 8; ++v) st_global_v4(slot + (c * 8 + v) * 32, r[4 * v], r[4 * v + 1], r[4 * v + 2], r[4 * v + 3]);
-  }
-}
-
-// Writes the sum of `ncontrib` partial accumulators (the layout epilogue_warp_partial leaves, `merge_stride` uint4
-// apart, `merge` = this lane's first 16 bytes of the first one) into one warp's 32 rows x 32 (c_end - c_begin)
-// columns of an accumulator in TMEM, so that MMAs issued afterwards accumulate on top of them.
-__device__ __forceinline__ void preload_warp_tile(uint32_t t_row, const uint4* merge, int ncontrib, size_t merge_stride,
-                                                  int c_begin, int c_end) {
-#pragma unroll 1
-  for (int c = c_begin; c < c_end; ++c) {
-    uint32_t r[32];
-#pragma unroll
-    for (int i = 0; i < 32; ++i) r[i] = 0u;
-#pragma unroll 1
-    for (int x = 0; x < ncontrib; ++x) {
-      const uint4* src = merge + size_t(x) * merge_stride + size_t(c) * 256;
-      uint4 cur[8];
-#pragma unroll
-      for (int v = 0; v < 8; ++v) cur[v] = ld_global_cg_v4(src + v * 32);
-#pragma unroll
-      for (int v = 0; v < 8; ++v) {
-        r[4 * v] += cur[v].x;
-        r[4 * v + 1] += cur[v].y;
-        r[4 * v + 2] += cur[v].z;
-        r[4 * v + 3] += cur[v].w;
-      }
+    uint8_t* buf = wide ? wide + ((c - c_begin) % kWide) * EPI_BUF_BYTES : staging + (c & (kBufs - 1)) * EPI_BUF_BYTES;
+    if (!wide) {
+      if (lane == 0) tma_store_wait_read<kBufs - 1>();   // the store that last read this buffer is done with it
+      __syncwarp();
+    } else if (c - c_begin >= kWide) {
+      if (lane == 0) tma_store_wait_read<kWide - 1>();
+      __syncwarp();
     }
-    tmem_st_32x32b_x32(t_row + uint32_t(c * 32), r);
+    const uint32_t base = smem_u32(buf) + uint32_t(lane) * 128u;
+#pragma unroll
+    for (int v = 0; v < 8; ++v)
+      st_shared_v4(base + (uint32_t(v ^ (lane & 7)) << 4), r[4 * v], r[4 * v + 1], r[4 * v + 2], r[4 * v + 3]);
+    fence_proxy_async_smem();
+    __syncwarp();
+    if (lane == 0) {
+      if (row0 < M && n0 + c * 32 < N) {
+        if (store_policy) tma_store_2d_hint(tmC, buf, n0 + c * 32, row0, store_policy);
+        else tma_store_2d(tmC, buf, n0 + c * 32, row0);
+      }
+      tma_store_commit();
+    }
   }
-  tmem_st_wait();
 }
 
 // Teardown of a CTA pair whose pipeline gave up, run by one thread of the even CTA after both CTAs have stopped

@@ -51,7 +51,7 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustain
 # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) of the dominant kernel, constants typed in
 # from ncu captures of these workloads on one GPU (a run of this script cannot measure them); None where no
 # capture was taken.
-NCU_TRAFFIC_BYTES = {"sgemm_skinny": 273.9e6, "sgemm_panel_128": 282.9e6, "sgemm_tall_16": 275.8e6, "i8_8192": 590.1e6, "i8_batched_32": 654.4e6, "i8_batched": 8 * 654.4e6}
+NCU_TRAFFIC_BYTES = {"sgemm_skinny": 273.9e6, "sgemm_panel_128": 282.9e6, "sgemm_tall_16": 275.8e6, "i8_8192": 496.1e6, "i8_batched_32": 654.4e6, "i8_batched": 8 * 654.4e6}
 
 WORKLOADS = {
     # name: (kind, M, N, K, batch)

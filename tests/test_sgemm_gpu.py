@@ -373,3 +373,50 @@ def test_automatic_choice_at_its_boundaries(native):
     assert nv.sgemm_auto_variant(limit + 128, 16, 1024) != nv.VT_SGEMM_TALL_TF32X3
     with pytest.raises(nv.NativeError):
         nv.sgemm_auto_variant(0, 16, 16)
+
+def test_device_calls_capture_into_a_cuda_graph(native):
+    """Device-pointer calls only enqueue work, so after one eager pass (which sizes the workspace and sets the
+    kernels' attributes) a sequence of them can be captured into a CUDA graph and replayed: the int8 pair kernel and
+    every fp32 family (32-wide with and without its K split, the pipelined kernel with its cluster split, the
+    streaming kernels for few rows and few columns, 3xTF32 with its lo-part pass), launched with programmatic
+    stream serialization and, for the split, as clusters.  Every replay must give the bits of the eager pass."""
+    import torch
+    gen = torch.Generator(device="cuda").manual_seed(9)
+    A8 = torch.randint(-128, 128, (1024, 2048), dtype=torch.int8, device="cuda", generator=gen)
+    B8 = torch.randint(-128, 128, (2048, 1536), dtype=torch.int8, device="cuda", generator=gen)
+    C8 = torch.zeros((1024, 1536), dtype=torch.int32, device="cuda")
+    cases = []
+    for (m, n, k) in ((256, 256, 256), (640, 640, 640), (16, 4096, 4096), (256, 256, 4096), (1024, 1024, 1024),
+                      (96, 2048, 2048), (2048, 16, 2048)):
+        cases.append((m, n, k, torch.rand((m, k), device="cuda", generator=gen) * 2 - 1,
+                      torch.rand((k, n), device="cuda", generator=gen) * 2 - 1, torch.zeros((m, n), device="cuda")))
+
+    def enqueue(handle):
+        native.i8gemm(A8, B8, C8, 1024, 1536, 2048, where=native.VT_DEVICE, stream=handle)
+        for (m, n, k, A, B, C) in cases:
+            native.sgemm(A, B, C, m, n, k, where=native.VT_DEVICE, stream=handle)
+
+    s = torch.cuda.Stream()
+    handle = int(s.cuda_stream)
+    with torch.cuda.stream(s):
+        enqueue(handle)
+    s.synchronize()
+    native.sync(0, handle)
+    want8, want = C8.clone(), [c[5].clone() for c in cases]
+    assert torch.equal(want8, (A8.double() @ B8.double()).to(torch.int32))
+    for (m, n, k, A, B, C) in cases:
+        assert relfro(C.cpu().numpy(), (A.double() @ B.double()).cpu().numpy()) <= TOL
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=s):
+        enqueue(handle)
+    for rep in range(3):
+        C8.fill_(-1)
+        for c in cases:
+            c[5].fill_(float("nan"))
+        torch.cuda.synchronize()
+        graph.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(C8, want8), rep
+        for c, w in zip(cases, want):
+            assert torch.equal(c[5], w), (c[:3], rep)
+    native.sync(0, handle)

@@ -21,7 +21,8 @@ no data-path collective.  `--scaling weak` gives every rank the whole shape inst
              timed region; peak from MEASURED_PEAKS.json (fallback stated if absent)
   also       the other named workloads, each timed like the headline (fp32 256^3 and 640^3, fp32 8192^3 by
              the automatic choice and by the FFMA kernel, fp32 16 x 8192 x 8192, the batched B-reuse int8
-             workload), short launches first, a quarter of a second apart
+             workload), short launches first, a quarter of a second apart; workloads of less than 30 us
+             per step also as one CUDA graph of the 20 calls (`graph_replay`)
   cpu_baseline  the oracle's OpenMP C restatement of the reference's CPU arithmetic, timed on this
              host's cores on a bounded sample of the same workload (N = 1 only)
 
@@ -497,6 +498,34 @@ class Job:
         nv.sync(ctx["dev"], ctx["st"])
         return ms, launches
 
+    def graph_ms(self, steps):
+        """ms per step with the `steps` calls captured once into a CUDA graph and replayed: what a launch-bound
+        workload costs when the host's per-call work (argument checks, tensor maps, the launch itself) is paid at
+        capture time.  CUDA events around one replay, max over ranks."""
+        torch, ctx = self.ctx["torch"], self.ctx
+        side = torch.cuda.Stream()
+        saved = ctx["st"]
+        ctx["st"] = int(side.cuda_stream)
+        try:
+            with torch.cuda.stream(side):
+                self.step()
+            side.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                for _ in range(steps):
+                    self.step()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            with torch.cuda.stream(side):
+                graph.replay()
+                e0.record()
+                graph.replay()
+                e1.record()
+            side.synchronize()
+            ctx["nv"].sync(ctx["dev"], ctx["st"])
+            return ctx["max"](e0.elapsed_time(e1)) / steps
+        finally:
+            ctx["st"] = saved
+
     def value(self, ms_per_step):
         """Whole-job throughput in T(FL)OPS; replicas count once (every rank does the same whole product)."""
         return 2.0 * self.total_rows * self.N * self.K / (ms_per_step * 1e-3) / 1e12
@@ -730,6 +759,10 @@ def run_gpu_arm(args, kind, M, N, K, batch, metric, unit):
                           "sharding": "replicas (too few rows to shard); value is one replica's" if j.replicas else
                                       ("batch dealt over the ranks" if j.kind == "i8b" else "M rows per rank") if world > 1 else "single GPU",
                           "roofline": {k: roof[k] for k in ("bound", "achieved", "peak", "unit", "frac")}}
+            if a_ms < 0.03:
+                # launch-bound: the same 20 calls as one CUDA graph
+                g_ms = j.graph_ms(steps)
+                also[name]["graph_replay"] = {"ms_per_step": g_ms, "value": j.value(g_ms)}
             if j.kind == "f32":
                 chosen = variant or nv.sgemm_auto_variant(j.rows, j.N, j.K, dev=ctx["dev"])
                 also[name]["kernel"] = nv.SGEMM_VARIANT_NAMES.get(chosen, str(chosen))

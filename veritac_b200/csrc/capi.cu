@@ -255,13 +255,14 @@ int choose_sgemm_variant(DeviceCtx* c, const float* dA, const float* dB, const f
   if (N <= 2 * SKINNY_UMMA_MAX_ROWS && K >= 256 && double(M) * double(K) >= 6.4e7 &&
       sgemm_tall_umma_supported(dA, dB, dC, M, N, K))
     return VT_SGEMM_TALL_TF32X3;
-  // Large products go to the tensor cores (3xTF32, measured ~1e-6 relative Frobenius error at any K) when that
-  // is clearly faster than the best FFMA tile kernel.  Its time is modelled as two launches (6 us), the pass that
+  // Products of 0.1 GFLOP and more go to the tensor cores (3xTF32, measured ~1e-6 relative Frobenius error at any K)
+  // when the model says that is faster than the best FFMA kernel.  Its time is modelled as two launches (6 us), the pass that
   // writes the lo parts and the write of C (8 bytes per element of A and B, 4 per element of C, at ~5.5 TB/s) and
   // K x 29 ns for every wave of 256x256 tiles over the 74 CTA pairs (measured on cubes of 896 to 1536, which is where
-  // the comparison is close; at 8192^3, under the power cap, a wave takes K x 34 ns).  Below ~0.5 GFLOP the two
-  // passes cost more than they save.
-  if (M >= 128 && N >= 16 && K >= 64 && double(M) * double(N) * double(K) >= 5.0e8 &&
+  // the comparison is close; at 8192^3, under the power cap, a wave takes K x 34 ns).  (A fixed floor of 0.5 GFLOP and a 10 % margin
+  // in favour of FFMA were dropped after an audit on 80 random mid-sized shapes: with them 596 x 2504 x 252 ran at 33.9 us
+  // against 18.1, and four shapes of 1-4 GFLOP 10-20 % behind.)
+  if (M >= 128 && N >= 16 && K >= 64 && double(M) * double(N) * double(K) >= 1.0e8 &&
       sgemm_tf32x3_supported(dA, dB, dC, M, N, K)) {
     int tile_variant;
     const double t_tile = sgemm_tile_choice(c, dA, dB, dC, M, N, K, &tile_variant);
@@ -270,7 +271,7 @@ int choose_sgemm_variant(DeviceCtx* c, const float* dA, const float* dB, const f
     const double waves = pair_tiles <= pairs ? 1.0 : double(int64_t((pair_tiles + pairs - 1) / pairs));
     const double t_tc = 6.0e-6 + ((double(M) * K + double(K) * N) * 8.0 + double(M) * N * 4.0) / 5.5e12 +
                         waves * double(K) * 2.9e-8;
-    if (t_tc < 0.9 * t_tile) return VT_SGEMM_TF32X3;
+    if (t_tc < t_tile) return VT_SGEMM_TF32X3;
   }
   return VT_SGEMM_AUTO;
 }

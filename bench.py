@@ -32,6 +32,7 @@ the same workload, and prints the same line shape with "impl": "reference".
 from __future__ import annotations
 
 import argparse
+import math
 import ctypes
 import json
 import os
@@ -882,6 +883,7 @@ def run_shape_grid(shapes):
           + " | ".join(names.values()) + " |")
     print("|---|---|---|---|---|---|---|" + "---|" * len(names))
     slower = 0
+    ratios = []
     for (m, n, k) in shapes:
         A = torch.rand((m, k), device="cuda") * 2 - 1
         B = torch.rand((k, n), device="cuda") * 2 - 1
@@ -900,12 +902,37 @@ def run_shape_grid(shapes):
         lib = timed(lambda: torch.matmul(A, B, out=C))
         best = min(cells, key=cells.get)
         slower += auto > 1.03 * lib
+        ratios.append((auto / cells[best], auto / lib))
         chosen = nv.SGEMM_VARIANT_NAMES.get(nv.sgemm_auto_variant(m, n, k), "?")
         print("| %d x %d x %d | %.4f ms | %s | %s %.4f | %.2f | %.4f | %.2f | "
               % (m, n, k, auto, chosen, names[best], cells[best], auto / cells[best], lib, auto / lib)
               + " | ".join("%.4f" % cells[v] if v in cells else "-" for v in names) + " |", flush=True)
     print("\nautomatic choice slower than cuBLAS by more than 3 %% on %d of %d shapes" % (slower, len(shapes)))
+    if ratios:
+        gm = lambda xs: math.exp(sum(math.log(x) for x in xs) / len(xs))
+        print("geometric mean of automatic / best single variant %.3f, of automatic / cuBLAS %.3f"
+              % (gm([r[0] for r in ratios]), gm([r[1] for r in ratios])))
     return 0
+
+
+def random_mid_shapes(seed, count):
+    """Seeded mid-sized fp32 shapes for `--shape-grid --random-shapes`: cubes of 160 to 1600, long-K products, wide and
+    tall ones; N and K multiples of 4."""
+    import numpy as np
+    rng = np.random.default_rng(seed)
+    shapes = []
+    for _ in range(count):
+        kind = rng.integers(0, 4)
+        if kind == 0:
+            m = n = k = 4 * int(rng.integers(40, 400))
+        elif kind == 1:
+            m, n, k = 4 * int(rng.integers(20, 300)), 4 * int(rng.integers(20, 300)), 4 * int(rng.integers(100, 4000))
+        elif kind == 2:
+            m, n, k = 4 * int(rng.integers(50, 800)), 4 * int(rng.integers(10, 200)), 4 * int(rng.integers(50, 1000))
+        else:
+            m, n, k = 4 * int(rng.integers(10, 600)), 4 * int(rng.integers(50, 800)), 4 * int(rng.integers(50, 1000))
+        shapes.append((m, n, k))
+    return shapes
 
 
 def metric_of(workload):
@@ -938,8 +965,13 @@ def main() -> int:
     ap.add_argument("--shape-grid", nargs="*", metavar="MxNxK", default=None,
                     help="instead of a bench line: time every fp32 kernel variant, the automatic choice and cuBLAS on "
                          "these shapes (no shapes: the built-in grid of 40) and print a markdown table")
+    ap.add_argument("--random-shapes", metavar="SEED:COUNT", default=None,
+                    help="with --shape-grid: COUNT seeded random mid-sized shapes instead of the built-in grid")
     args = ap.parse_args()
     if args.shape_grid is not None:
+        if args.random_shapes:
+            seed, count = (int(x) for x in args.random_shapes.split(":"))
+            return run_shape_grid(random_mid_shapes(seed, count))
         return run_shape_grid([tuple(int(x) for x in a.lower().split("x")) for a in args.shape_grid] or list(SHAPE_GRID))
     kind, M, N, K, batch = WORKLOADS[args.workload]
     metric, unit = metric_of(args.workload)

@@ -229,20 +229,22 @@ int choose_sgemm_variant(DeviceCtx* c, const float* dA, const float* dB, const f
   // (measured against the tile kernels and the 3xTF32 pair kernel: ahead from 1 Mi elements of B up to 32 rows,
   // from 4 Mi up to 256 rows, from 16 Mi up to 384 rows).
   if (M > 16 && M <= 3 * SKINNY_UMMA_MAX_ROWS && N >= 128 && K >= 512 &&
-      double(N) * double(K) >= (M <= 32 ? 1.0e6 : M <= 2 * SKINNY_UMMA_MAX_ROWS ? 4.0e6 : 1.6e7) &&
-      sgemm_skinny_umma_supported(dA, dB, dC, 1, N, K)) {
+      double(N) * double(K) >= (M <= 32 ? 1.0e6 : 4.0e6) && sgemm_skinny_umma_supported(dA, dB, dC, 1, N, K)) {
     // With few columns and a very long K every CTA holds a piece of the same few slabs, and one CTA per slab adds all
     // the partial tiles (128 x 128 x 65536: 148 of them, 0.15 ms, against 0.08 ms for the 32-wide FFMA kernel with
     // its own K split): the panel kernel's time is modelled as the stream of B (a panel of 16 rows at the rate of
     // the stream, one of 128 rows at half of it) plus that adding at 60 GB/s, and compared with the FFMA choice.
-    const int64_t rows = M < SKINNY_UMMA_MAX_ROWS ? M : SKINNY_UMMA_MAX_ROWS;
-    const int64_t panels = (M + SKINNY_UMMA_MAX_ROWS - 1) / SKINNY_UMMA_MAX_ROWS;
-    int ctas, slabs, max_parts;
-    sgemm_skinny_umma_plan(rows, N, K, c->sm_count, &ctas, &slabs, &max_parts);
-    const double stream = double(K) * double(N) * 4.0 / 5.0e12 * (1.0 + (rows > 16 ? double(rows - 16) / 112.0 : 0.0));
-    const double adding = max_parts > 1 ? double(max_parts) * double(rows) * 512.0 / 6.0e10 : 0.0;
+    double t_panel = 0;
+    for (int64_t m0 = 0; m0 < M; m0 += SKINNY_UMMA_MAX_ROWS) {      // one launch per panel of up to 128 rows
+      const int64_t rows = M - m0 < SKINNY_UMMA_MAX_ROWS ? M - m0 : SKINNY_UMMA_MAX_ROWS;
+      int ctas, slabs, max_parts;
+      sgemm_skinny_umma_plan(rows, N, K, c->sm_count, &ctas, &slabs, &max_parts);
+      const double stream = double(K) * double(N) * 4.0 / 5.0e12 * (1.0 + (rows > 16 ? double(rows - 16) / 112.0 : 0.0));
+      const double adding = max_parts > 1 ? double(max_parts) * double(rows) * 512.0 / 6.0e10 : 0.0;
+      t_panel += 6.0e-6 + stream + adding;
+    }
     int tile_variant;
-    if (double(panels) * (6.0e-6 + stream + adding) < sgemm_tile_choice(c, dA, dB, dC, M, N, K, &tile_variant))
+    if (t_panel < sgemm_tile_choice(c, dA, dB, dC, M, N, K, &tile_variant))
       return VT_SGEMM_PANEL_TF32X3;
   }
   // Few columns against a large A: the mirror image (measured ahead of the tile kernels and the 3xTF32 pair kernel
@@ -498,7 +500,23 @@ int vt_sgemm(int dev, const float* A, const float* B, float* C, int64_t M, int64
   }
   const bool skinny_ok = M <= 16 && N % 4 == 0 &&
                          ((reinterpret_cast<uintptr_t>(dB) | reinterpret_cast<uintptr_t>(dC)) & 15) == 0;
-  if (variant == VT_SGEMM_AUTO) variant = choose_sgemm_variant(c, dA, dB, dC, M, N, K);
+  if (variant == VT_SGEMM_AUTO) {
+    // The choice is a few models' worth of arithmetic, which a 5 us launch feels: the last shapes asked about on
+    // this device are remembered (with the alignment of their operands, which some kernels depend on).
+    const uint32_t align = uint32_t((reinterpret_cast<uintptr_t>(dA) | reinterpret_cast<uintptr_t>(dB) |
+                                     reinterpret_cast<uintptr_t>(dC)) & 15);
+    DeviceCtx::Choice* hit = nullptr;
+    for (auto& e : c->sgemm_choices)
+      if (e.variant != 0 && e.M == M && e.N == N && e.K == K && e.align == align) hit = &e;
+    if (hit) {
+      variant = hit->variant;
+    } else {
+      variant = choose_sgemm_variant(c, dA, dB, dC, M, N, K);
+      if (variant == VT_SGEMM_AUTO) sgemm_tile_choice(c, dA, dB, dC, M, N, K, &variant);
+      DeviceCtx::Choice& slot = c->sgemm_choices[c->sgemm_choice_next++ % 8];
+      slot.M = M; slot.N = N; slot.K = K; slot.align = align; slot.variant = variant;
+    }
+  }
   int rc;
   if (variant == VT_SGEMM_TALL_TF32X3) {
     if (!sgemm_tall_umma_supported(dA, dB, dC, M, N, K))

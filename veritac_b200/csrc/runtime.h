@@ -34,6 +34,10 @@ struct DeviceCtx {
   // pipelined FFMA kernel: clusters of 1..8 CTAs of each tile shape the device holds at once (filled on first use)
   int ffma_capacity[3][9] = {};
   bool ffma_capacity_known = false;
+  // the automatic fp32 choice for the last eight (shape, operand alignment) combinations asked about
+  struct Choice { int64_t M = 0, N = 0, K = 0; uint32_t align = 0; int variant = 0; };
+  Choice sgemm_choices[8];
+  unsigned sgemm_choice_next = 0;
   int sgemm_force_splits = 0;          // test hook (vt_test_set_sgemm_splits): K split of the FFMA tile kernels, 0 = automatic
   // grow-only device workspace for host-pointer calls and operand re-layouts
   void* ws[4] = {nullptr, nullptr, nullptr, nullptr};

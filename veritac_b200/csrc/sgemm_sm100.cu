@@ -693,14 +693,25 @@ double sgemm_tile_choice(DeviceCtx* c, const float* A, const float* B, const flo
     if (i == 2 && !small_ok) continue;
     const double tm = double((M + kTile[i] - 1) / kTile[i]), tn = double((N + kTile[i] - 1) / kTile[i]);
     const double work = 2.0 * tm * tn * kTile[i] * kTile[i] * double(K);
-    int splits = 1, per;
+    int splits = 1, per = int(K);
     if (i == 2 && tm * tn < 1e9) {
       splits = splits_for((long long)(tm * tn), int(K), 2 * sm_count, 2 * SS_KC, kMaxSplits, 0);
       split_ranges(int(K), SS_KC, &splits, &per);
+      if (per > K) per = int(K);
     }
     const double ctas = tm * tn * splits;
     const double busy = ctas < sm_count ? ctas / sm_count : 1.0;
-    const double t = 5.0e-6 + work / (kRate[i] * busy) * kBias[i] + (splits > 1 ? 4.0e-6 : 0.0);   // 5 us: what a launch costs beside its loop
+    double t = 5.0e-6 + work / (kRate[i] * busy) * kBias[i];      // 5 us: what a launch costs beside its loop
+    if (i == 2) {
+      // The 32-wide kernel does not overlap a burst's loads with its arithmetic, so what counts is how many bursts
+      // the busiest SM works through: one CTA alone on an SM takes 2.67 us per burst of 256 values of K, two CTAs
+      // sharing an SM 4.36 us for a burst each (measured; 212 x 716 x 2828 is 161 CTAs of 12 bursts, and the 13 SMs
+      // that hold two of them set its 56 us).  Two CTAs fit an SM; larger grids run in waves of 2 x SMs.
+      const double bursts = double(per) / SS_KC > 0.25 ? double(per) / SS_KC : 0.25;
+      const double slots = 2.0 * sm_count;
+      const double waves = ctas <= 4 * slots ? double(int64_t((ctas + slots - 1) / slots)) : ctas / slots + 0.5;
+      t = 5.0e-6 + bursts * (ctas <= sm_count ? 2.67e-6 : waves * 4.36e-6) + (splits > 1 ? 4.0e-6 : 0.0);
+    }
     if (best == 0 || t < best) {
       best = t;
       *variant = kVariant[i];

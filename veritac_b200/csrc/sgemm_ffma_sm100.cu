@@ -326,7 +326,9 @@ double sgemm_ffma_plan(DeviceCtx* c, int shape, int64_t M, int64_t N, int64_t K,
     const int s = int((steps_total + per - 1) / per);
     if (s != want && forced <= 0) continue;                  // the same split as a smaller `want`
     if (s > 1 && per < 2 && forced <= 0) continue;
-    const double capacity = double(c->ffma_capacity[shape][s]) * s;
+    // One cluster fewer than the occupancy query promises when K is split: a grid that needs every last one did not
+    // get them in one wave (45 clusters of three 128 x 128 CTAs, capacity 45: 85 us where one wave would be 64).
+    const double capacity = double(c->ffma_capacity[shape][s] - (s > 1 ? 1 : 0)) * s;
     const double reach = double(c->ffma_capacity[0][s]) * s;
     if (capacity <= 0 || reach <= 0) continue;
     const double ctas = tiles * s;

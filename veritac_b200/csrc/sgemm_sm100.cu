@@ -717,13 +717,15 @@ double sgemm_tile_choice(DeviceCtx* c, const float* A, const float* B, const flo
       *variant = kVariant[i];
     }
   }
+  double biased = best;
   if (sgemm_ffma_supported(A, B, C, N, K)) {
     static const int kPipe[3] = {VT_SGEMM_PIPE128, VT_SGEMM_PIPE64X128, VT_SGEMM_PIPE64};
     for (int shape = 0; shape < 3; ++shape) {
       int splits;
-      const double t = 1.1 * sgemm_ffma_plan(c, shape, M, N, K, 0, &splits);   // has to win by 10 %
-      if (t < best) {
-        best = t;
+      const double t = sgemm_ffma_plan(c, shape, M, N, K, 0, &splits);
+      if (1.05 * t < biased) {                // has to win by 5 % against the kernels before it ...
+        biased = 1.05 * t;
+        best = t;                             // ... but what the caller compares with other kernels is the estimate itself
         *variant = kPipe[shape];
       }
     }
